@@ -1,0 +1,127 @@
+/*
+ * vqg.h -- C ABI of the B200 (sm_100a) vector-quantised GEMM library, libvqg_b200.so.
+ *
+ * Plain C: device pointers, sizes and an opaque stream handle; no torch or pybind types.
+ * Every entry point returns a status code (VQG_OK == 0) and never throws, prints or
+ * falls back to a CPU path.  All pointers are DEVICE pointers unless stated otherwise.
+ *
+ * Two weight formats are understood (``layout``):
+ *
+ *   VQG_LAYOUT_BL   W[n, v*j + r] = codebook[n / rows_per_codebook][ idx[n, j] ][r]
+ *                   idx [N, K/v] (uint8 or uint16), codebook [G, C, v] fp16,
+ *                   Y[M, N] = X[M, K] * W^T            (the benchmark configurations)
+ *
+ *   VQG_LAYOUT_REF  Wdec[k, 2*n + r] = codebook[n / 4][ w[k, n] ][r]
+ *                   w [K, Nq] uint8, codebook [Nq/4, 256, 2] fp16,
+ *                   Y[M, 2*Nq] = X[M, K] * Wdec        (the reference's own format,
+ *                   reference bench.py:37-57 and strategy_1/src.cu:268-321)
+ *
+ * X and Y are fp16 row-major; accumulation is fp32; Y is rounded once to fp16.
+ */
+#ifndef VQG_H_
+#define VQG_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define VQG_API __attribute__((visibility("default")))
+#else
+#define VQG_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+enum {
+  VQG_OK = 0,
+  VQG_ERR_BAD_ARG = 1,        /* null pointer, non-positive size, misaligned pointer            */
+  VQG_ERR_UNSUPPORTED = 2,    /* a (v, C, index width, layout, path) combination not built      */
+  VQG_ERR_WORKSPACE = 3,      /* workspace missing or smaller than vqg_workspace_bytes()        */
+  VQG_ERR_LAUNCH = 4,         /* the CUDA runtime or driver refused a call                      */
+  VQG_ERR_DEVICE_TIMEOUT = 5, /* a bounded device-side wait ran out (see vqg_device_status)     */
+  VQG_ERR_NO_DEVICE = 6       /* no usable sm_100 device / driver                                */
+};
+
+enum { VQG_LAYOUT_BL = 0, VQG_LAYOUT_REF = 1 };
+
+/* kernel selection for vqg_gemm_path(); VQG_PATH_AUTO is what vqg_gemm() uses */
+enum {
+  VQG_PATH_AUTO = 0,
+  VQG_PATH_GENERIC = 1,  /* shape-agnostic CUDA-core kernel                                     */
+  VQG_PATH_DECODE = 2,   /* M <= 16: index streaming + codebook lookups + mma.sync, split-K     */
+  VQG_PATH_TENSOR = 3,   /* tcgen05 / TMEM / TMA warp-specialised kernel, fused dequant         */
+  VQG_PATH_TWO_PHASE = 4 /* dequantise to workspace, then the dense tcgen05 kernel              */
+};
+
+/* Library version (major*10000 + minor*100 + patch). */
+VQG_API int vqg_version(void);
+
+/* Static string for a status code.  (No reference counterpart: the reference checks no errors;
+ * strategy_3/naive/src.cu:42-54 prints cudaGetLastError and continues.) */
+VQG_API const char* vqg_status_string(int status);
+
+/* Bytes of scratch the given problem needs (0 if none).  The first
+ * vqg_workspace_counter_bytes() bytes hold arrival counters and must be zero when the
+ * workspace is first used (cudaMemset once after allocation); the library leaves them zero.
+ * Replaces the per-call temporaries of the reference (strategy_1/src.cu:351 allocates
+ * a [K, 2*Nq] matrix on every call). */
+VQG_API size_t vqg_workspace_bytes(int M, int N, int K, int v, int C, int idx_bytes,
+                           int rows_per_codebook, int layout, int path);
+VQG_API size_t vqg_workspace_counter_bytes(void);
+
+/* Y = X * dequant(idx, codebook)^T.  Replaces `torch::Tensor e2e_gemm(input, w, codebook)`
+ * (reference bind.cpp:3,7; host launchers strategy_2/bsz128/src.cu:255-316 and siblings).
+ *   N                  output columns (BL: rows of idx; REF: 2*Nq)
+ *   v, C               sub-vector length and codebook entries (REF: v=2, C=256)
+ *   idx_bytes          1 (uint8) or 2 (uint16)
+ *   rows_per_codebook  BL: output rows sharing a codebook, 0 = one codebook for the matrix
+ *                      REF: ignored (8 output columns per codebook)
+ *   stream             cudaStream_t (NULL = legacy default stream, as the reference uses) */
+VQG_API int vqg_gemm(const void* x, const void* idx, const void* codebook, void* y,
+             int M, int N, int K, int v, int C, int idx_bytes, int rows_per_codebook,
+             int layout, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same, with the kernel chosen by the caller (tests and benchmarks). */
+VQG_API int vqg_gemm_path(const void* x, const void* idx, const void* codebook, void* y,
+                  int M, int N, int K, int v, int C, int idx_bytes, int rows_per_codebook,
+                  int layout, int path, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Dequantised weights, bit-exact gather.  BL: w_out [N, K]; REF: w_out [K, N] (N = 2*Nq).
+ * Replaces `dequant_kernel` of the reference's two-phase variant (strategy_1/src.cu:268-321). */
+VQG_API int vqg_dequant(const void* idx, const void* codebook, void* w_out,
+                int N, int K, int v, int C, int idx_bytes, int rows_per_codebook,
+                int layout, void* stream);
+
+/* Dense fp16 GEMM with fp32 accumulation.  Replaces `torch::Tensor gemm(input, w)`
+ * (reference bind.cpp:4,8; ref_gemm/cublas_gemm_fp16.cu:15-48).
+ *   w_is_kn = 1: w is [K, N] row-major (the reference's convention);  0: w is [N, K]. */
+VQG_API int vqg_dense_gemm(const void* x, const void* w, void* y, int M, int N, int K, int w_is_kn,
+                   void* workspace, size_t workspace_bytes, void* stream);
+VQG_API size_t vqg_dense_workspace_bytes(int M, int N, int K, int w_is_kn);
+
+/* N-sharded multi-GPU mode (no reference counterpart: the reference is single-GPU, device 0
+ * is hard-coded at strategy_1/src.cu:343).  This rank owns output columns
+ * [rank*N_local, (rank+1)*N_local) of a Y with ld_y = nranks*N_local columns; idx/codebook are
+ * the rank's shard.  y_peers[r] (HOST array of nranks DEVICE pointers) is the base of the full
+ * Y buffer on rank r (peer-mapped); the kernel epilogue stores the rank's column block into
+ * every one of them.  y_peers[rank] must be local.  With nranks == 1 this is vqg_gemm with a
+ * leading dimension. */
+VQG_API int vqg_gemm_sharded(const void* x, const void* idx, const void* codebook,
+                     void* const* y_peers, int rank, int nranks,
+                     int M, int N_local, int K, int v, int C, int idx_bytes, int rows_per_codebook,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* Reads and clears the device-side status word of the current device: 0 if no bounded wait has
+ * run out since the last call, else a code naming the wait.  Synchronises the device. */
+VQG_API int vqg_device_status(int* code_out);
+
+/* Number of kernels this library has launched in the calling process (all streams). */
+VQG_API unsigned long long vqg_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VQG_H_ */

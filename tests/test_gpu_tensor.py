@@ -1,0 +1,83 @@
+"""The tcgen05 / TMEM / TMA kernels against the oracle: dense operand variant, fused-dequant
+variant, and the two-phase route (dequantise, then dense)."""
+import pytest
+import torch
+
+import vq_gemm_b200 as V
+from oracle import vq_oracle as O
+from tests._util import assert_within_tolerance, bits, load_golden, run_bl
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 64, 256), (128, 256, 256), (256, 512, 512), (100, 128, 96), (300, 1024, 1280)])
+def test_dense_gemm(M, K, N):
+    g = torch.Generator().manual_seed(M + K + N)
+    x = torch.randn(M, K, generator=g).half()
+    w = (torch.randn(K, N, generator=g) * 0.1).half()
+    y = V.gemm(x.cuda(), w.cuda()).cpu()
+    assert V.device_status() == 0
+    assert_within_tolerance(y, (x.float() @ w.float()).half())
+
+
+@pytest.mark.parametrize("M,K,N,v,rpc", [
+    (128, 64, 256, 4, 128),       # one tile, one K step
+    (128, 256, 256, 4, 128),      # one tile, wraps the 3-stage ring
+    (128, 512, 256, 8, 128),      # v = 8
+    (256, 1024, 512, 4, 128),     # 4 tiles
+    (200, 512, 384, 4, 128),      # ragged M, N = 1.5 tiles
+    (130, 128, 256, 8, 128),      # golden-sized
+    (64, 2048, 128, 4, 0),        # single codebook, half tile
+    (1024, 1024, 2048, 8, 256),   # 256 rows per codebook, many tiles per CTA? (64 tiles)
+    (4096, 512, 4864, 4, 128),    # more tiles than SMs: persistent loop + accumulator ping-pong
+])
+def test_fused_matches_oracle(M, K, N, v, rpc):
+    x, idx, cb = O.make_bl_inputs(M, K, N, v, 256, rpc, seed=M + K + N + v, cb_sigma=0.05)
+    y = run_bl(V, x, idx, cb, rpc, path="tensor")
+    assert_within_tolerance(y, O.vq_gemm_bl(x, idx, cb, rpc))
+
+
+def test_fused_small_codebook():
+    x, idx, cb = O.make_bl_inputs(128, 256, 256, 4, 37, 128, seed=2, cb_sigma=0.05)
+    assert_within_tolerance(run_bl(V, x, idx, cb, 128, path="tensor"), O.vq_gemm_bl(x, idx, cb, 128))
+
+
+def test_golden_fixture_through_tensor_path():
+    g = load_golden("bl_v8_c256_groups")
+    y = run_bl(V, g["x"], g["idx"], g["codebook"], 128, path="tensor")
+    assert_within_tolerance(y, g["y"])
+
+
+@pytest.mark.parametrize("M,K,N,v,C,rpc,dt", [
+    (256, 512, 512, 4, 256, 128, torch.uint8),
+    (128, 256, 256, 8, 4096, 0, torch.int16),
+])
+def test_two_phase(M, K, N, v, C, rpc, dt):
+    x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=3, idx_dtype=dt, cb_sigma=0.05)
+    y = run_bl(V, x, idx, cb, rpc, path="two_phase")
+    assert_within_tolerance(y, O.vq_gemm_bl(x, idx, cb, rpc))
+
+
+@pytest.mark.parametrize("tag", ["ref_small", "ref_two_tiles"])
+def test_reference_format_two_phase(tag):
+    g = load_golden(tag)
+    y = V.vq_gemm(g["x"].cuda(), g["w"].cuda(), g["codebook"].cuda(), layout="ref", path="two_phase").cpu()
+    assert V.device_status() == 0
+    assert_within_tolerance(y, g["y"], tag)
+
+
+def test_fused_deterministic():
+    x, idx, cb = O.make_bl_inputs(512, 1024, 1024, 4, 256, 128, seed=8)
+    xs, ids, cbs = x.cuda(), idx.cuda(), cb.cuda()
+    outs = [V.vq_gemm(xs, ids, cbs, layout="bl", path="tensor").cpu() for _ in range(5)]
+    for o in outs[1:]:
+        assert torch.equal(bits(outs[0]), bits(o))
+    assert V.device_status() == 0
+
+
+def test_fused_equals_two_phase_bitwise():
+    # both routes feed identical fp16 operands to the same MMA sequence
+    x, idx, cb = O.make_bl_inputs(256, 512, 512, 8, 256, 128, seed=10)
+    a = run_bl(V, x, idx, cb, 128, path="tensor")
+    b = run_bl(V, x, idx, cb, 128, path="two_phase")
+    assert torch.equal(bits(a), bits(b))

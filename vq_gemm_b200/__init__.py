@@ -1,0 +1,11 @@
+"""B200 (sm_100a) vector-quantised GEMM: Y[M,N] = X[M,K] @ dequant(idx, codebook)^T.
+
+The package is a thin host layer over ``libvqg_b200.so`` (C ABI in include/vqg.h).  It mirrors
+the reference extension's entry points -- ``e2e_gemm`` and ``gemm`` -- and adds ``vq_gemm`` and
+``dequant`` for the generalised weight format.  There is no CPU implementation.
+"""
+from .formats import CONFIGS, VQShape, infer_layout, make_inputs  # noqa: F401
+from .ops import dequant, device_status, e2e_gemm, gemm, launch_count, vq_gemm  # noqa: F401
+
+__all__ = ["e2e_gemm", "gemm", "vq_gemm", "dequant", "device_status", "launch_count", "CONFIGS", "VQShape",
+           "infer_layout", "make_inputs"]

@@ -1,0 +1,64 @@
+"""ctypes binding of ``libvqg_b200.so`` (the C ABI declared in include/vqg.h).
+
+Loading fails loudly: there is no Python or CPU substitute for the CUDA library.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_int, c_size_t, c_ulonglong, c_void_p, POINTER
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libvqg_b200.so")
+
+OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_LAUNCH, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE = range(7)
+LAYOUT_BL, LAYOUT_REF = 0, 1
+PATH_AUTO, PATH_GENERIC, PATH_DECODE, PATH_TENSOR, PATH_TWO_PHASE = range(5)
+PATHS = {"auto": PATH_AUTO, "generic": PATH_GENERIC, "decode": PATH_DECODE, "tensor": PATH_TENSOR,
+         "two_phase": PATH_TWO_PHASE}
+
+# name -> (restype, argtypes); mirrors include/vqg.h one to one
+SIGNATURES = {
+    "vqg_version": (c_int, []),
+    "vqg_status_string": (c_char_p, [c_int]),
+    "vqg_workspace_bytes": (c_size_t, [c_int] * 9),
+    "vqg_workspace_counter_bytes": (c_size_t, []),
+    "vqg_gemm": (c_int, [c_void_p] * 4 + [c_int] * 8 + [c_void_p, c_size_t, c_void_p]),
+    "vqg_gemm_path": (c_int, [c_void_p] * 4 + [c_int] * 9 + [c_void_p, c_size_t, c_void_p]),
+    "vqg_dequant": (c_int, [c_void_p] * 3 + [c_int] * 7 + [c_void_p]),
+    "vqg_dense_gemm": (c_int, [c_void_p] * 3 + [c_int] * 4 + [c_void_p, c_size_t, c_void_p]),
+    "vqg_dense_workspace_bytes": (c_size_t, [c_int] * 4),
+    "vqg_gemm_sharded": (c_int, [c_void_p] * 3 + [POINTER(c_void_p), c_int, c_int] + [c_int] * 7
+                         + [c_void_p, c_size_t, c_void_p]),
+    "vqg_device_status": (c_int, [POINTER(c_int)]),
+    "vqg_launch_count": (c_ulonglong, []),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Returns the loaded library; raises if it has not been built (python -m vq_gemm_b200.build)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python compile_kernels.py build_ext --inplace` "
+            "(or `python -m vq_gemm_b200.build`). There is no fallback path.")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library is stale
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def status_string(code: int) -> str:
+    return load().vqg_status_string(code).decode()
+
+
+def check(code: int, what: str) -> None:
+    if code != OK:
+        raise RuntimeError(f"{what}: {status_string(code)} (status {code})")

@@ -1,0 +1,250 @@
+// extern "C" surface of libvqg_b200.so: argument checks, kernel selection, workspace rules.
+// Declarations and the reference interfaces they replace are in include/vqg.h.
+#include <atomic>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace vqg {
+
+namespace {
+std::atomic<unsigned long long> g_launches{0};
+std::mutex g_mu;
+int* g_status[64] = {};
+}  // namespace
+
+void count_launch(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
+
+cudaError_t ensure_status_word() {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_status[dev]) return cudaSuccess;
+  int* p = nullptr;
+  e = cudaMalloc(&p, 256);
+  if (e != cudaSuccess) return e;
+  e = cudaMemset(p, 0, 256);
+  if (e != cudaSuccess) return e;
+  g_status[dev] = p;
+  return cudaSuccess;
+}
+
+int* device_status_ptr() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev >= 0 && dev < 64) ? g_status[dev] : nullptr;
+}
+
+namespace {
+
+bool aligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; }
+
+int check_common(const void* x, const void* idx, const void* cb, const void* y, int M, int N, int K, int v, int C,
+                 int idx_bytes, int layout) {
+  if (M < 0 || N < 0 || K < 0) return VQG_ERR_BAD_ARG;
+  if (layout != VQG_LAYOUT_BL && layout != VQG_LAYOUT_REF) return VQG_ERR_BAD_ARG;
+  if (M == 0 || N == 0) return VQG_OK;
+  if (!y || !aligned(y, 2)) return VQG_ERR_BAD_ARG;
+  if (K > 0 && (!x || !idx || !cb || !aligned(x, 2) || !aligned(cb, 2))) return VQG_ERR_BAD_ARG;
+  if (layout == VQG_LAYOUT_REF) {
+    if (v != 2 || C != 256 || idx_bytes != 1) return VQG_ERR_UNSUPPORTED;
+    if (N % 8 != 0) return VQG_ERR_BAD_ARG;  // 4 index columns (8 outputs) per codebook
+  } else {
+    if (v < 1 || C < 1) return VQG_ERR_BAD_ARG;
+    if (idx_bytes != 1 && idx_bytes != 2) return VQG_ERR_UNSUPPORTED;
+    if (K % v != 0) return VQG_ERR_BAD_ARG;
+    if (idx_bytes == 1 && C > 256) return VQG_ERR_BAD_ARG;
+    if (C > 65536) return VQG_ERR_BAD_ARG;
+    if (idx_bytes == 2 && !aligned(idx, 2)) return VQG_ERR_BAD_ARG;
+  }
+  return VQG_OK;
+}
+
+Problem make_problem(const void* x, const void* idx, const void* cb, void* y, int M, int N, int K, int v, int C,
+                     int idx_bytes, int rows_per_cb, long long ld_y) {
+  Problem p{};
+  p.x = static_cast<const __half*>(x);
+  p.idx = idx;
+  p.cb = static_cast<const __half*>(cb);
+  p.y = static_cast<__half*>(y);
+  p.M = M; p.N = N; p.K = K; p.v = v; p.C = C; p.idx_bytes = idx_bytes;
+  p.rows_per_cb = (rows_per_cb <= 0 || rows_per_cb > N) ? (N > 0 ? N : 1) : rows_per_cb;
+  p.ld_y = ld_y;
+  p.n_peers = 0;
+  return p;
+}
+
+int auto_path(const Problem& p, int layout) {
+  if (layout == VQG_LAYOUT_REF) {
+    return dense_supported(p.M, p.N, p.K) && p.M >= 32 ? VQG_PATH_TWO_PHASE : VQG_PATH_GENERIC;
+  }
+  if (p.K == 0) return VQG_PATH_GENERIC;
+  if (p.M <= 16 && decode_supported(p)) return VQG_PATH_DECODE;
+  if (p.M > 16 && tensor_supported(p)) return VQG_PATH_TENSOR;
+  if (p.M > 16 && dense_supported(p.M, p.N, p.K) && (p.v == 2 || p.v == 4 || p.v == 8)) return VQG_PATH_TWO_PHASE;
+  return VQG_PATH_GENERIC;
+}
+
+size_t two_phase_bytes(int N, int K) { return static_cast<size_t>(N) * K * 2; }
+
+int run(const Problem& p, int layout, int path, void* ws, size_t ws_bytes, cudaStream_t s) {
+  if (p.M == 0 || p.N == 0) return VQG_OK;
+  if (ensure_status_word() != cudaSuccess) return VQG_ERR_NO_DEVICE;
+  if (path == VQG_PATH_AUTO) path = auto_path(p, layout);
+  switch (path) {
+    case VQG_PATH_GENERIC:
+      return launch_generic(p, layout, s);
+    case VQG_PATH_DECODE:
+      if (layout != VQG_LAYOUT_BL) return VQG_ERR_UNSUPPORTED;
+      return launch_decode(p, ws, ws_bytes, s);
+    case VQG_PATH_TENSOR:
+      if (layout != VQG_LAYOUT_BL) return VQG_ERR_UNSUPPORTED;
+      return launch_tensor(p, s);
+    case VQG_PATH_TWO_PHASE: {
+      if (!dense_supported(p.M, p.N, p.K)) return VQG_ERR_UNSUPPORTED;
+      const size_t need = two_phase_bytes(p.N, p.K);
+      if (!ws || ws_bytes < need || !aligned(ws, 1024)) return VQG_ERR_WORKSPACE;
+      __half* w = static_cast<__half*>(ws);
+      int st;
+      if (layout == VQG_LAYOUT_BL)
+        st = launch_dequant_bl(p.idx, p.cb, w, p.N, p.K, p.v, p.C, p.idx_bytes, p.rows_per_cb, s);
+      else
+        st = launch_dequant_ref(static_cast<const uint8_t*>(p.idx), p.cb, w, p.N / 2, p.K, /*transposed=*/true, s);
+      if (st != VQG_OK) return st;
+      return launch_dense(p.x, w, p.y, p.M, p.N, p.K, p.ld_y, p.n_peers, p.peer_y, s);
+    }
+    default:
+      return VQG_ERR_BAD_ARG;
+  }
+}
+
+}  // namespace
+}  // namespace vqg
+
+using namespace vqg;
+
+extern "C" {
+
+int vqg_version(void) { return 100; }
+
+const char* vqg_status_string(int status) {
+  switch (status) {
+    case VQG_OK: return "ok";
+    case VQG_ERR_BAD_ARG: return "bad argument (null or misaligned pointer, negative size, K not a multiple of v)";
+    case VQG_ERR_UNSUPPORTED: return "unsupported combination of v, C, index width, layout or path";
+    case VQG_ERR_WORKSPACE: return "workspace missing, misaligned or smaller than vqg_workspace_bytes()";
+    case VQG_ERR_LAUNCH: return "CUDA runtime or driver call failed";
+    case VQG_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+    case VQG_ERR_NO_DEVICE: return "no usable CUDA device";
+    default: return "unknown status";
+  }
+}
+
+size_t vqg_workspace_counter_bytes(void) { return kCounterBytes; }
+
+size_t vqg_workspace_bytes(int M, int N, int K, int v, int C, int idx_bytes, int rows_per_codebook, int layout,
+                           int path) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  // pointers only matter for alignment checks; use aligned dummies
+  void* dummy = reinterpret_cast<void*>(static_cast<uintptr_t>(1024));
+  Problem p = make_problem(dummy, dummy, dummy, dummy, M, N, K, v, C, idx_bytes, rows_per_codebook, N);
+  if (path == VQG_PATH_AUTO) path = auto_path(p, layout);
+  if (path == VQG_PATH_DECODE) return decode_workspace_bytes(p);
+  if (path == VQG_PATH_TWO_PHASE) return two_phase_bytes(N, K);
+  return 0;
+}
+
+int vqg_gemm_path(const void* x, const void* idx, const void* codebook, void* y, int M, int N, int K, int v, int C,
+                  int idx_bytes, int rows_per_codebook, int layout, int path, void* workspace,
+                  size_t workspace_bytes, void* stream) {
+  const int st = check_common(x, idx, codebook, y, M, N, K, v, C, idx_bytes, layout);
+  if (st != VQG_OK) return st;
+  Problem p = make_problem(x, idx, codebook, y, M, N, K, v, C, idx_bytes, rows_per_codebook, N);
+  return run(p, layout, path, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int vqg_gemm(const void* x, const void* idx, const void* codebook, void* y, int M, int N, int K, int v, int C,
+             int idx_bytes, int rows_per_codebook, int layout, void* workspace, size_t workspace_bytes, void* stream) {
+  return vqg_gemm_path(x, idx, codebook, y, M, N, K, v, C, idx_bytes, rows_per_codebook, layout, VQG_PATH_AUTO,
+                       workspace, workspace_bytes, stream);
+}
+
+int vqg_dequant(const void* idx, const void* codebook, void* w_out, int N, int K, int v, int C, int idx_bytes,
+                int rows_per_codebook, int layout, void* stream) {
+  if (N < 0 || K < 0) return VQG_ERR_BAD_ARG;
+  if (N == 0 || K == 0) return VQG_OK;
+  if (!idx || !codebook || !w_out) return VQG_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (layout == VQG_LAYOUT_REF) {
+    if (v != 2 || C != 256 || idx_bytes != 1 || N % 8 != 0) return VQG_ERR_UNSUPPORTED;
+    return launch_dequant_ref(static_cast<const uint8_t*>(idx), static_cast<const __half*>(codebook),
+                              static_cast<__half*>(w_out), N / 2, K, false, s);
+  }
+  if (layout != VQG_LAYOUT_BL) return VQG_ERR_BAD_ARG;
+  if (v < 1 || C < 1 || K % v != 0) return VQG_ERR_BAD_ARG;
+  if (idx_bytes == 1 && C > 256) return VQG_ERR_BAD_ARG;
+  if (!aligned(w_out, 16) || !aligned(codebook, 16)) return VQG_ERR_BAD_ARG;
+  const int rpc = (rows_per_codebook <= 0 || rows_per_codebook > N) ? N : rows_per_codebook;
+  return launch_dequant_bl(idx, static_cast<const __half*>(codebook), static_cast<__half*>(w_out), N, K, v, C,
+                           idx_bytes, rpc, s);
+}
+
+size_t vqg_dense_workspace_bytes(int M, int N, int K, int w_is_kn) {
+  (void)M;
+  return w_is_kn ? static_cast<size_t>(N) * K * 2 : 0;
+}
+
+int vqg_dense_gemm(const void* x, const void* w, void* y, int M, int N, int K, int w_is_kn, void* workspace,
+                   size_t workspace_bytes, void* stream) {
+  if (M < 0 || N < 0 || K < 0) return VQG_ERR_BAD_ARG;
+  if (M == 0 || N == 0) return VQG_OK;
+  if (!x || !w || !y) return VQG_ERR_BAD_ARG;
+  if (!dense_supported(M, N, K)) return VQG_ERR_UNSUPPORTED;
+  if (ensure_status_word() != cudaSuccess) return VQG_ERR_NO_DEVICE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const __half* w_nk = static_cast<const __half*>(w);
+  if (w_is_kn) {
+    if (!workspace || workspace_bytes < vqg_dense_workspace_bytes(M, N, K, 1) || !aligned(workspace, 1024))
+      return VQG_ERR_WORKSPACE;
+    const int st = launch_transpose(static_cast<const __half*>(w), static_cast<__half*>(workspace), K, N, s);
+    if (st != VQG_OK) return st;
+    w_nk = static_cast<const __half*>(workspace);
+  }
+  return launch_dense(static_cast<const __half*>(x), w_nk, static_cast<__half*>(y), M, N, K, N, 0, nullptr, s);
+}
+
+int vqg_gemm_sharded(const void* x, const void* idx, const void* codebook, void* const* y_peers, int rank,
+                     int nranks, int M, int N_local, int K, int v, int C, int idx_bytes, int rows_per_codebook,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+  if (nranks < 1 || nranks > 8 || rank < 0 || rank >= nranks || !y_peers) return VQG_ERR_BAD_ARG;
+  for (int r = 0; r < nranks; ++r)
+    if (!y_peers[r]) return VQG_ERR_BAD_ARG;
+  const long long ld = static_cast<long long>(nranks) * N_local;
+  const size_t col0 = static_cast<size_t>(rank) * N_local;
+  void* y_local = static_cast<__half*>(y_peers[rank]) + col0;
+  const int st = check_common(x, idx, codebook, y_local, M, N_local, K, v, C, idx_bytes, VQG_LAYOUT_BL);
+  if (st != VQG_OK) return st;
+  Problem p = make_problem(x, idx, codebook, y_local, M, N_local, K, v, C, idx_bytes, rows_per_codebook, ld);
+  for (int r = 0; r < nranks; ++r)
+    if (r != rank) p.peer_y[p.n_peers++] = static_cast<__half*>(y_peers[r]) + col0;
+  return run(p, VQG_LAYOUT_BL, VQG_PATH_AUTO, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int vqg_device_status(int* code_out) {
+  if (!code_out) return VQG_ERR_BAD_ARG;
+  *code_out = 0;
+  int* p = device_status_ptr();
+  if (!p) return VQG_OK;  // nothing has run on this device yet
+  if (cudaDeviceSynchronize() != cudaSuccess) return VQG_ERR_LAUNCH;
+  int v = 0;
+  if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return VQG_ERR_LAUNCH;
+  if (v != 0) cudaMemset(p, 0, sizeof(int));
+  *code_out = v;
+  return v == 0 ? VQG_OK : VQG_ERR_DEVICE_TIMEOUT;
+}
+
+unsigned long long vqg_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

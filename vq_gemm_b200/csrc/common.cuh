@@ -1,0 +1,73 @@
+// Shared declarations of the sm_100a VQ-GEMM kernels: problem descriptor, launcher
+// prototypes, the device status word and small PTX helpers.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/vqg.h"
+
+namespace vqg {
+
+// One VQ-GEMM problem, BL layout (see include/vqg.h).  ld_y lets the output live inside a
+// wider matrix (column shard of a gathered Y).
+struct Problem {
+  const __half* x;      // [M, K]
+  const void* idx;      // [N, K/v] uint8 or uint16
+  const __half* cb;     // [G, C, v]
+  __half* y;            // [M, ld_y], columns [0, N) written
+  int M, N, K;
+  int v, C, idx_bytes;
+  int rows_per_cb;      // >= 1; N when one codebook serves the matrix
+  long long ld_y;
+  // multi-GPU epilogue: additional copies of the output block (peer-mapped), may be 0
+  int n_peers;
+  __half* peer_y[8];
+};
+
+// Device status word: 0 = fine; otherwise the code of the first bounded wait that ran out.
+enum DeviceStatus : int {
+  DS_OK = 0,
+  DS_TMA_FULL_TIMEOUT = 1,   // consumer waited for a TMA-filled stage
+  DS_STAGE_EMPTY_TIMEOUT = 2,// producer waited for a free stage
+  DS_B_READY_TIMEOUT = 3,    // MMA warp waited for dequantised B
+  DS_ACC_FULL_TIMEOUT = 4,   // epilogue waited for the accumulator
+  DS_ACC_EMPTY_TIMEOUT = 5,  // MMA warp waited for the epilogue to drain TMEM
+  DS_SPLITK_TIMEOUT = 6,
+  DS_DEQUANT_SYNC_TIMEOUT = 7,
+};
+int* device_status_ptr();          // device address of the status word of the current device
+cudaError_t ensure_status_word();  // allocates it on first use (per device)
+
+void count_launch(int n = 1);
+
+// ---- launchers (each returns a VQG_* status) -------------------------------------------
+int launch_dequant_bl(const void* idx, const __half* cb, __half* w, int N, int K, int v, int C,
+                      int idx_bytes, int rows_per_cb, cudaStream_t s);
+int launch_dequant_ref(const uint8_t* w, const __half* cb, __half* out, int Nq, int K, bool transposed,
+                       cudaStream_t s);
+int launch_generic(const Problem& p, int layout, cudaStream_t s);
+
+bool decode_supported(const Problem& p);
+size_t decode_workspace_bytes(const Problem& p);
+int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s);
+
+bool tensor_supported(const Problem& p);
+int launch_tensor(const Problem& p, cudaStream_t s);
+bool dense_supported(int M, int N, int K);
+// Y[M,N] = X[M,K] * W[N,K]^T, all fp16, fp32 accumulate (tcgen05).
+int launch_dense(const __half* x, const __half* w_nk, __half* y, int M, int N, int K, long long ld_y,
+                 int n_peers, __half* const* peer_y, cudaStream_t s);
+int launch_transpose(const __half* in, __half* out, int rows, int cols, cudaStream_t s);
+
+constexpr size_t kCounterBytes = 64 * 1024;  // arrival counters at the head of a workspace
+
+inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? VQG_OK : VQG_ERR_LAUNCH; }
+
+// ---- device helpers ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+}  // namespace vqg

@@ -1,0 +1,238 @@
+// Bit-exact dequantisation kernels (pure gathers; HBM-bound) and the shape-agnostic
+// CUDA-core VQ-GEMM used for shapes none of the specialised kernels accept.
+//
+//   BL  : W[n, v*j + r]       = cb[n / rows_per_cb][ idx[n, j] ][r]   -> W    [N, K]
+//   REF : Wdec[k, 2*n + r]    = cb[n / 4][ w[k, n] ][r]               -> Wdec [K, 2*Nq]
+//         (reference strategy_1/src.cu:268-321 computes the same matrix)
+//   REF transposed            : WdecT [2*Nq, K]  (K-major operand for the dense tensor kernel)
+#include "common.cuh"
+
+namespace vqg {
+
+template <int V> struct Entry;
+template <> struct Entry<2> { using T = uint32_t; };
+template <> struct Entry<4> { using T = uint2; };
+template <> struct Entry<8> { using T = uint4; };
+
+// One block = 16 consecutive rows of one codebook group (rows_per_cb % 16 == 0) or, when that
+// does not hold, a single row.  The codebook is staged in shared memory when it fits.
+template <int V, typename IdxT, bool SMEM_CB>
+__global__ void __launch_bounds__(256) dequant_bl_kernel(const IdxT* __restrict__ idx,
+                                                         const __half* __restrict__ cb,
+                                                         __half* __restrict__ w, int N, int K, int C,
+                                                         int rows_per_cb, int rows_per_block) {
+  using E = typename Entry<V>::T;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int J = K / V;
+  const int row0 = blockIdx.x * rows_per_block;
+  const int group = row0 / rows_per_cb;
+  const E* cbg = reinterpret_cast<const E*>(cb) + static_cast<size_t>(group) * C;
+  const E* table = cbg;
+  if (SMEM_CB) {
+    E* s = reinterpret_cast<E*>(smem_raw);
+    for (int i = threadIdx.x; i < C; i += blockDim.x) s[i] = cbg[i];
+    __syncthreads();
+    table = s;
+  }
+  const int rows = min(rows_per_block, N - row0);
+  const long long total = static_cast<long long>(rows) * J;
+  const IdxT* ip = idx + static_cast<size_t>(row0) * J;
+  E* op = reinterpret_cast<E*>(w + static_cast<size_t>(row0) * K);
+  for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+    op[i] = table[ip[i]];
+  }
+}
+
+int launch_dequant_bl(const void* idx, const __half* cb, __half* w, int N, int K, int v, int C,
+                      int idx_bytes, int rows_per_cb, cudaStream_t s) {
+  if (N == 0 || K == 0) return VQG_OK;
+  const bool single = rows_per_cb >= N;
+  int rpb = (single || rows_per_cb % 16 == 0) ? 16 : 1;
+  // fewer, larger blocks for large matrices (the codebook is staged once per block)
+  while (rpb >= 16 && (single || rows_per_cb % (rpb * 2) == 0) && (N / (rpb * 2)) >= 148 * 16) rpb *= 2;
+  const int blocks = (N + rpb - 1) / rpb;
+  const size_t cb_bytes = static_cast<size_t>(C) * v * 2;
+  const bool use_smem = cb_bytes <= 96 * 1024;
+  const size_t smem = use_smem ? cb_bytes : 0;
+#define VQG_DQ(V_, T_)                                                                              \
+  do {                                                                                              \
+    if (use_smem) {                                                                                 \
+      auto k = dequant_bl_kernel<V_, T_, true>;                                                     \
+      if (smem > 48 * 1024)                                                                         \
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+      k<<<blocks, 256, smem, s>>>(static_cast<const T_*>(idx), cb, w, N, K, C, rows_per_cb, rpb);   \
+    } else {                                                                                        \
+      dequant_bl_kernel<V_, T_, false>                                                              \
+          <<<blocks, 256, 0, s>>>(static_cast<const T_*>(idx), cb, w, N, K, C, rows_per_cb, rpb);   \
+    }                                                                                               \
+  } while (0)
+  if (idx_bytes == 1) {
+    if (v == 2) VQG_DQ(2, uint8_t); else if (v == 4) VQG_DQ(4, uint8_t); else if (v == 8) VQG_DQ(8, uint8_t);
+    else return VQG_ERR_UNSUPPORTED;
+  } else if (idx_bytes == 2) {
+    if (v == 2) VQG_DQ(2, uint16_t); else if (v == 4) VQG_DQ(4, uint16_t); else if (v == 8) VQG_DQ(8, uint16_t);
+    else return VQG_ERR_UNSUPPORTED;
+  } else {
+    return VQG_ERR_UNSUPPORTED;
+  }
+#undef VQG_DQ
+  count_launch();
+  return cuda_status(cudaGetLastError());
+}
+
+// REF layout, natural orientation: one thread per (k, n); 4-byte gathers, 4-byte stores that
+// coalesce along n.
+__global__ void __launch_bounds__(256) dequant_ref_kernel(const uint8_t* __restrict__ w,
+                                                          const __half* __restrict__ cb,
+                                                          __half* __restrict__ out, int Nq, int K) {
+  const uint32_t* table = reinterpret_cast<const uint32_t*>(cb);
+  uint32_t* o = reinterpret_cast<uint32_t*>(out);
+  const long long total = static_cast<long long>(K) * Nq;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int n = static_cast<int>(i % Nq);
+    o[i] = __ldg(table + (static_cast<size_t>(n >> 2) << 8) + w[i]);
+  }
+}
+
+// REF layout, transposed output WdecT[2n + r, k]: a 64(k) x 64(n) tile goes through shared
+// memory so that both the index reads (along n) and the weight writes (along k) coalesce.
+__global__ void __launch_bounds__(256) dequant_ref_t_kernel(const uint8_t* __restrict__ w,
+                                                            const __half* __restrict__ cb,
+                                                            __half* __restrict__ out, int Nq, int K) {
+  __shared__ __half tile[128][66];
+  const uint32_t* table = reinterpret_cast<const uint32_t*>(cb);
+  const int n0 = blockIdx.x * 64, k0 = blockIdx.y * 64;
+  for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+    const int kk = e >> 6, nn = e & 63;
+    const int k = k0 + kk, n = n0 + nn;
+    uint32_t pair = 0;
+    if (k < K && n < Nq) pair = __ldg(table + (static_cast<size_t>(n >> 2) << 8) + w[static_cast<size_t>(k) * Nq + n]);
+    __half2 h = *reinterpret_cast<__half2*>(&pair);
+    tile[2 * nn][kk] = __low2half(h);
+    tile[2 * nn + 1][kk] = __high2half(h);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < 128 * 64; e += 256) {
+    const int r = e >> 6, kk = e & 63;
+    const int row = 2 * n0 + r, k = k0 + kk;
+    if (row < 2 * Nq && k < K) out[static_cast<size_t>(row) * K + k] = tile[r][kk];
+  }
+}
+
+int launch_dequant_ref(const uint8_t* w, const __half* cb, __half* out, int Nq, int K, bool transposed,
+                       cudaStream_t s) {
+  if (Nq == 0 || K == 0) return VQG_OK;
+  if (transposed) {
+    dim3 grid((Nq + 63) / 64, (K + 63) / 64);
+    dequant_ref_t_kernel<<<grid, 256, 0, s>>>(w, cb, out, Nq, K);
+  } else {
+    const long long total = static_cast<long long>(K) * Nq;
+    const long long want = (total + 255) / 256;
+    const int blocks = static_cast<int>(want < 148LL * 32 ? want : 148LL * 32);
+    dequant_ref_kernel<<<blocks, 256, 0, s>>>(w, cb, out, Nq, K);
+  }
+  count_launch();
+  return cuda_status(cudaGetLastError());
+}
+
+// fp16 matrix transpose (for `gemm(input, w)` with w given as [K, N]).
+__global__ void __launch_bounds__(256) transpose_kernel(const __half* __restrict__ in, __half* __restrict__ out,
+                                                        int rows, int cols) {
+  __shared__ __half tile[64][66];
+  const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+  for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+    const int rr = e >> 6, cc = e & 63;
+    if (r0 + rr < rows && c0 + cc < cols) tile[rr][cc] = in[static_cast<size_t>(r0 + rr) * cols + c0 + cc];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+    const int cc = e >> 6, rr = e & 63;
+    if (r0 + rr < rows && c0 + cc < cols) out[static_cast<size_t>(c0 + cc) * rows + r0 + rr] = tile[rr][cc];
+  }
+}
+
+int launch_transpose(const __half* in, __half* out, int rows, int cols, cudaStream_t s) {
+  if (rows == 0 || cols == 0) return VQG_OK;
+  dim3 grid((cols + 63) / 64, (rows + 63) / 64);
+  transpose_kernel<<<grid, 256, 0, s>>>(in, out, rows, cols);
+  count_launch();
+  return cuda_status(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------------------
+// Shape-agnostic VQ-GEMM on CUDA cores: 64x64 output tile, 32-wide K steps, 4x4 per thread.
+// Accepts any M, N, K (K % v == 0), any C, both layouts.  Not a performance path.
+// ---------------------------------------------------------------------------------------------
+template <int LAYOUT>
+__global__ void __launch_bounds__(256) generic_vq_gemm_kernel(Problem p) {
+  __shared__ float xs[32][65];
+  __shared__ float ws[32][65];
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4] = {};
+  const int J = p.K / p.v;
+  const uint8_t* idx8 = static_cast<const uint8_t*>(p.idx);
+  const uint16_t* idx16 = static_cast<const uint16_t*>(p.idx);
+  for (int k0 = 0; k0 < p.K; k0 += 32) {
+    for (int e = threadIdx.x; e < 64 * 32; e += 256) {
+      const int r = e >> 5, kk = e & 31;
+      const int k = k0 + kk;
+      float xv = 0.f, wv = 0.f;
+      if (k < p.K) {
+        if (m0 + r < p.M) xv = __half2float(p.x[static_cast<size_t>(m0 + r) * p.K + k]);
+        const int n = n0 + r;
+        if (n < p.N) {
+          if (LAYOUT == VQG_LAYOUT_BL) {
+            const size_t ii = static_cast<size_t>(n) * J + k / p.v;
+            const int c = p.idx_bytes == 1 ? idx8[ii] : idx16[ii];
+            const int g = n / p.rows_per_cb;
+            wv = __half2float(p.cb[(static_cast<size_t>(g) * p.C + c) * p.v + (k % p.v)]);
+          } else {
+            const int nq = n >> 1, Nq = p.N >> 1;
+            const int c = idx8[static_cast<size_t>(k) * Nq + nq];
+            wv = __half2float(p.cb[((static_cast<size_t>(nq >> 2) << 8) + c) * 2 + (n & 1)]);
+          }
+        }
+      }
+      xs[kk][r] = xv;
+      ws[kk][r] = wv;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < 32; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = xs[kk][ty * 4 + i]; b[i] = ws[kk][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= p.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= p.N) continue;
+      const __half h = __float2half_rn(acc[i][j]);
+      p.y[static_cast<size_t>(m) * p.ld_y + n] = h;
+      for (int q = 0; q < p.n_peers; ++q) p.peer_y[q][static_cast<size_t>(m) * p.ld_y + n] = h;
+    }
+  }
+}
+
+int launch_generic(const Problem& p, int layout, cudaStream_t s) {
+  if (p.M == 0 || p.N == 0) return VQG_OK;
+  dim3 grid((p.N + 63) / 64, (p.M + 63) / 64);
+  if (layout == VQG_LAYOUT_BL) generic_vq_gemm_kernel<VQG_LAYOUT_BL><<<grid, 256, 0, s>>>(p);
+  else generic_vq_gemm_kernel<VQG_LAYOUT_REF><<<grid, 256, 0, s>>>(p);
+  count_launch();
+  return cuda_status(cudaGetLastError());
+}
+
+}  // namespace vqg

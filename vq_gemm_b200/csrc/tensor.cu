@@ -1,0 +1,539 @@
+// Compute-bound VQ-GEMM for sm_100a: TMA + mbarrier pipeline, tcgen05.mma with fp32
+// accumulators in tensor memory, dequantisation fused into the B-operand producer.
+//
+// One persistent 448-thread CTA per SM works on 128(M) x 256(N) output tiles, 64 K values per
+// pipeline stage:
+//
+//   warp 0        TMA producer: X tile [128 x 64] fp16 -> shared memory (SWIZZLE_128B), mbarrier
+//                 expect-tx.  In the dense variant it also loads the W tile [256 x 64].
+//   warp 1        allocates tensor memory, issues tcgen05.mma (one lane), commits stage-free and
+//                 accumulator-ready mbarriers.
+//   warps 2..5    epilogue: tcgen05.ld -> fp16 -> global (and peer copies in the N-sharded mode),
+//                 overlapped with the next tile's main loop through two 256-column accumulators.
+//   warps 6..13   dequant (VQ variant): thread r owns weight row n0 + r.  It streams the row's
+//                 indices from global memory in 64-byte granules (one granule ahead), looks every
+//                 index up in a replicated, bank-conflict-free shared-memory image of the row
+//                 group's codebook, and stores 16-byte chunks straight into the K-major
+//                 SWIZZLE_128B layout the MMA descriptors describe (a length-v sub-vector is a
+//                 contiguous 8- or 16-byte run of one operand row).  fence.proxy.async, then arrive.
+//
+// Every wait is bounded: when a wait runs out, the kernel records which one in the device status
+// word, all roles leave their loops, tensor memory is released and the kernel returns.
+//
+// Replaces the fused kernels of the reference (strategy_2/bsz128/src.cu:213-253,
+// strategy_2/bsz512/src.cu:203-246, strategy_3/naive/src.cu:250-317,
+// strategy_3/wasp/src.cu:321-387), which use cp.async + ldmatrix + mma.sync with fp16 accumulators.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace vqg {
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kThreads = 448;
+constexpr int kDequantWarp0 = 6;
+constexpr int kDequantThreads = 256;
+constexpr uint32_t kABytes = BM * BK * 2;  // 16 KiB
+constexpr uint32_t kBBytes = BN * BK * 2;  // 32 KiB
+constexpr uint32_t kImageBytes = 32 * 1024;
+constexpr uint32_t kTmemCols = 512;
+constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
+
+struct TensorParams {
+  const unsigned char* idx;  // [N, K/v] uint8
+  const __half* cb;          // [G, C, v]
+  __half* y;
+  int* status;
+  int M, N, K, C;
+  int rows_per_cb;
+  long long ld_y;
+  int m_tiles, n_tiles;
+  int n_peers;
+  __half* peer_y[8];
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (after recording `code`) when the limit is reached or when another
+// role has already recorded a failure.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try(bar, parity)) return true;
+    if ((++spins & 63u) == 0) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// K-major, SWIZZLE_128B operand tile whose rows are 128 bytes: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);       // start address
+  d |= static_cast<uint64_t>(1) << 16;                            // leading byte offset (unused for SW128 K-major)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                            // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                            // SWIZZLE_128B
+  return d;
+}
+// kind::f16, A = B = fp16, D = fp32, both K-major, M = 128, N = 256
+constexpr uint32_t kIdesc = (1u << 4) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int STAGES>
+struct SmemLayout {
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kImages = STAGES * kStageBytes;
+  static constexpr uint32_t kBars = kImages + 2 * kImageBytes;
+  // barriers: a_full[S], b_full[S], empty[S], acc_full[2], acc_empty[2], dequant-group sync;
+  // then the TMEM base word
+  static constexpr uint32_t kTmemSlot = kBars + (3 * STAGES + 5) * 8;
+  static constexpr uint32_t kTotal = kTmemSlot + 16;
+};
+
+// V: sub-vector length (4 or 8).  DENSE: B comes from a second tensor map instead of the dequant warps.
+template <int V, bool DENSE, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+vq_tensor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                 const TensorParams p) {
+  using L = SmemLayout<STAGES>;
+  extern __shared__ unsigned char smem_dyn[];
+  // SWIZZLE_128B tiles need 1024-byte alignment
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_dyn + (base - raw);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ksteps = p.K / BK;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  auto a_addr = [&](int s) { return base + s * L::kStageBytes; };
+  auto b_addr = [&](int s) { return base + s * L::kStageBytes + kABytes; };
+  auto bar_a_full = [&](int s) { return base + L::kBars + 8 * s; };
+  auto bar_b_full = [&](int s) { return base + L::kBars + 8 * (STAGES + s); };
+  auto bar_empty = [&](int s) { return base + L::kBars + 8 * (2 * STAGES + s); };
+  auto bar_acc_full = [&](int a) { return base + L::kBars + 8 * (3 * STAGES + a); };
+  auto bar_acc_empty = [&](int a) { return base + L::kBars + 8 * (3 * STAGES + 2 + a); };
+  const uint32_t bar_dq = base + L::kBars + 8 * (3 * STAGES + 4);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kTmemSlot);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_a_full(s), 1);
+      mbar_init(bar_b_full(s), kDequantThreads / 32);
+      mbar_init(bar_empty(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_acc_full(a), 1);
+      mbar_init(bar_acc_empty(a), 4);
+    }
+    mbar_init(bar_dq, kDequantThreads);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(base + L::kTmemSlot),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
+        for (int kt = 0; kt < ksteps; ++kt) {
+          if (!(ok = mbar_wait(bar_empty(stage), phase ^ 1, p.status, DS_STAGE_EMPTY_TIMEOUT))) break;
+          mbar_expect_tx(bar_a_full(stage), DENSE ? (kABytes + kBBytes) : kABytes);
+          tma_load_2d(a_addr(stage), &tmap_x, kt * BK, m0, bar_a_full(stage));
+          if (DENSE) tma_load_2d(b_addr(stage), &tmap_w, kt * BK, n0, bar_a_full(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ---------------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        if (!(ok = mbar_wait(bar_acc_empty(acc), acc_phase ^ 1, p.status, DS_ACC_EMPTY_TIMEOUT))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kt = 0; kt < ksteps; ++kt) {
+          if (!(ok = mbar_wait(bar_a_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
+          if (!DENSE) {
+            if (!(ok = mbar_wait(bar_b_full(stage), phase, p.status, DS_B_READY_TIMEOUT))) break;
+          }
+          tc_fence_after();
+          const uint64_t ad = make_desc(a_addr(stage));
+          const uint64_t bd = make_desc(b_addr(stage));
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // +32 bytes per 16-wide K slice inside the 128-byte swizzle atom: +2 in address units of 16 B
+            tc_mma_f16(d_tmem, ad + 2 * k, bd + 2 * k, kIdesc, (kt | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(bar_empty(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(bar_acc_full(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else if (warp < kDequantWarp0) {
+    // ------------------------------- epilogue -----------------------------------------------
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
+      if (!(ok = mbar_wait(bar_acc_full(acc), acc_phase, p.status, DS_ACC_FULL_TIMEOUT))) break;
+      tc_fence_after();
+      const int m = m0 + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_row + c * 32, r);
+        const int n = n0 + c * 32;
+        if (m < p.M && n < p.N) {
+          uint4 o[4];
+          uint32_t* ow = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            __half2 h = __floats2half2_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+            ow[i] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          const size_t off = static_cast<size_t>(m) * p.ld_y + n;
+          uint4* dst = reinterpret_cast<uint4*>(p.y + off);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) dst[i] = o[i];
+          for (int q = 0; q < p.n_peers; ++q) {
+            uint4* pd = reinterpret_cast<uint4*>(p.peer_y[q] + off);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pd[i] = o[i];
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  } else if (!DENSE) {
+    // ------------------------------- dequant warps ------------------------------------------
+    constexpr int ENTRY_LOG2 = (V == 4) ? 3 : 4;       // bytes per codebook entry
+    constexpr int REPS = 128 >> ENTRY_LOG2;             // replicas filling a 128-byte line
+    constexpr int WPS = (BK / V) / 4;                   // index words per K step (uint8 indices)
+    constexpr int GSTEPS = 16 / WPS;                    // K steps per 64-byte granule
+    const int r = threadIdx.x - kDequantWarp0 * 32;     // B-tile row owned by this thread
+    const int half = r >> 7;                            // which 128-row codebook image
+    const int J = p.K / V;                              // index bytes per weight row
+    unsigned char* images = base_ptr + L::kImages;
+    const uint32_t img = base + L::kImages + half * kImageBytes + ((lane & (REPS - 1)) << ENTRY_LOG2);
+    const uint32_t row_off = static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128);
+    const uint32_t rx = static_cast<uint32_t>(r & 7);
+
+    int stage = 0;
+    uint32_t phase = 0;
+    int cur_nblk = -1;
+    bool ok = true;
+    uint32_t dq_phase = 0;
+    // bounded rendezvous of the 256 dequant threads (a plain named barrier could wait for ever on a
+    // thread that has already left after a recorded failure)
+    auto dq_sync = [&]() -> bool {
+      mbar_arrive(bar_dq);
+      const bool done = mbar_wait(bar_dq, dq_phase, p.status, DS_DEQUANT_SYNC_TIMEOUT);
+      dq_phase ^= 1;
+      return done;
+    };
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const int n_blk = tile / p.m_tiles;
+      const int n = n_blk * BN + r;
+      const bool row_valid = n < p.N;
+      if (n_blk != cur_nblk) {
+        cur_nblk = n_blk;
+        // every thread has finished the previous tile's lookups -> rebuild both images
+        if (!(ok = dq_sync())) break;
+        for (int h = 0; h < 2; ++h) {
+          int grow = n_blk * BN + h * 128;
+          if (grow >= p.N) grow = p.N - 1;
+          const int group = grow / p.rows_per_cb;
+          const unsigned char* src = reinterpret_cast<const unsigned char*>(p.cb) + (static_cast<size_t>(group) * p.C << ENTRY_LOG2);
+          unsigned char* dst = images + h * kImageBytes;
+          if (V == 4) {
+            for (int u = r; u < p.C * (REPS / 2); u += kDequantThreads) {
+              const uint2 e = __ldg(reinterpret_cast<const uint2*>(src) + u / (REPS / 2));
+              reinterpret_cast<uint4*>(dst)[u] = make_uint4(e.x, e.y, e.x, e.y);
+            }
+          } else {
+            for (int u = r; u < p.C * REPS; u += kDequantThreads)
+              reinterpret_cast<uint4*>(dst)[u] = __ldg(reinterpret_cast<const uint4*>(src) + u / REPS);
+          }
+        }
+        if (!(ok = dq_sync())) break;
+      }
+
+      const unsigned char* row_ptr = p.idx + static_cast<size_t>(row_valid ? n : 0) * J;
+      uint32_t cur[16], nxt[16];
+      auto load_granule = [&](int gi, uint32_t (&dst)[16]) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 t = make_uint4(0, 0, 0, 0);
+          const int byte0 = gi * 64 + q * 16;
+          if (row_valid && byte0 + 16 <= J) t = __ldg(reinterpret_cast<const uint4*>(row_ptr + byte0));
+          dst[4 * q] = t.x; dst[4 * q + 1] = t.y; dst[4 * q + 2] = t.z; dst[4 * q + 3] = t.w;
+        }
+      };
+      const int ngran = (ksteps + GSTEPS - 1) / GSTEPS;
+      load_granule(0, nxt);
+      for (int gi = 0; ok && gi < ngran; ++gi) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) cur[i] = nxt[i];
+        if (gi + 1 < ngran) load_granule(gi + 1, nxt);
+#pragma unroll
+        for (int st = 0; st < GSTEPS; ++st) {
+          const int kt = gi * GSTEPS + st;
+          if (kt >= ksteps) break;
+          if (!(ok = mbar_wait(bar_empty(stage), phase ^ 1, p.status, DS_STAGE_EMPTY_TIMEOUT))) break;
+          const uint32_t dst_row = b_addr(stage) + row_off;
+          if (V == 4) {
+#pragma unroll
+            for (int w = 0; w < WPS; ++w) {
+              const uint32_t word = cur[st * WPS + w];
+#pragma unroll
+              for (int hh = 0; hh < 2; ++hh) {
+                const uint32_t c0 = (word >> (16 * hh)) & 0xffu, c1 = (word >> (16 * hh + 8)) & 0xffu;
+                uint32_t e0x, e0y, e1x, e1y;
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(e0x), "=r"(e0y) : "r"(img + (c0 << 7)));
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(e1x), "=r"(e1y) : "r"(img + (c1 << 7)));
+                const uint32_t chunk = static_cast<uint32_t>(2 * w + hh);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst_row + ((chunk ^ rx) << 4)), "r"(e0x),
+                             "r"(e0y), "r"(e1x), "r"(e1y)
+                             : "memory");
+              }
+            }
+          } else {
+#pragma unroll
+            for (int w = 0; w < WPS; ++w) {
+              const uint32_t word = cur[st * WPS + w];
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                const uint32_t c0 = (word >> (8 * b)) & 0xffu;
+                uint32_t e[4];
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(e[0]), "=r"(e[1]), "=r"(e[2]), "=r"(e[3]) : "r"(img + (c0 << 7)));
+                const uint32_t chunk = static_cast<uint32_t>(4 * w + b);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst_row + ((chunk ^ rx) << 4)), "r"(e[0]),
+                             "r"(e[1]), "r"(e[2]), "r"(e[3])
+                             : "memory");
+              }
+            }
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_b_full(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  }
+
+  // ------------------------------- teardown --------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeFn>(f);
+  }();
+  return fn;
+}
+
+// fp16 row-major [rows, cols] matrix, box [box_rows x 64 cols], 128-byte swizzle, zero fill.
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int box_rows) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int sm_count() {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+
+template <typename K>
+int launch_common(K kernel, size_t smem, const CUtensorMap& mx, const CUtensorMap& mw, TensorParams& tp, cudaStream_t s) {
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+    return VQG_ERR_LAUNCH;
+  const int tiles = tp.m_tiles * tp.n_tiles;
+  const int sms = sm_count();
+  const int grid = tiles < sms ? tiles : sms;
+  kernel<<<grid, kThreads, smem, s>>>(mx, mw, tp);
+  count_launch();
+  return cuda_status(cudaGetLastError());
+}
+
+bool common_shape_ok(int M, int N, int K, const void* x, const void* y, long long ld_y) {
+  if (M < 1 || N < 1 || K < BK || K % BK != 0) return false;
+  if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(y) % 16) return false;
+  if (N % 32 != 0 || ld_y % 8 != 0) return false;
+  return true;
+}
+
+}  // namespace
+
+bool tensor_supported(const Problem& p) {
+  if (!common_shape_ok(p.M, p.N, p.K, p.x, p.y, p.ld_y)) return false;
+  if (!(p.v == 4 || p.v == 8) || p.idx_bytes != 1 || p.C < 1 || p.C > 256) return false;
+  if ((p.K / p.v) % 16 != 0) return false;  // 16-byte index loads per row
+  if (reinterpret_cast<uintptr_t>(p.idx) % 16 || reinterpret_cast<uintptr_t>(p.cb) % 16) return false;
+  const bool single = p.rows_per_cb >= p.N;
+  if (!single && p.rows_per_cb % 128 != 0) return false;
+  return true;
+}
+
+int launch_tensor(const Problem& p, cudaStream_t s) {
+  if (!tensor_supported(p)) return VQG_ERR_UNSUPPORTED;
+  CUtensorMap mx;
+  if (!make_map(&mx, p.x, p.M, p.K, BM)) return VQG_ERR_LAUNCH;
+  TensorParams tp{};
+  tp.idx = static_cast<const unsigned char*>(p.idx);
+  tp.cb = p.cb;
+  tp.y = p.y;
+  tp.status = device_status_ptr();
+  tp.M = p.M; tp.N = p.N; tp.K = p.K; tp.C = p.C;
+  tp.rows_per_cb = p.rows_per_cb >= p.N ? p.N : p.rows_per_cb;
+  tp.ld_y = p.ld_y;
+  tp.m_tiles = (p.M + BM - 1) / BM;
+  tp.n_tiles = (p.N + BN - 1) / BN;
+  tp.n_peers = p.n_peers;
+  for (int i = 0; i < 8; ++i) tp.peer_y[i] = p.peer_y[i];
+  constexpr int S = 3;
+  const size_t smem = SmemLayout<S>::kTotal + 1024;
+  if (p.v == 4) return launch_common(vq_tensor_kernel<4, false, S>, smem, mx, mx, tp, s);
+  return launch_common(vq_tensor_kernel<8, false, S>, smem, mx, mx, tp, s);
+}
+
+bool dense_supported(int M, int N, int K) { return M >= 1 && N >= 1 && K >= BK && K % BK == 0 && N % 32 == 0; }
+
+int launch_dense(const __half* x, const __half* w_nk, __half* y, int M, int N, int K, long long ld_y, int n_peers,
+                 __half* const* peer_y, cudaStream_t s) {
+  if (!common_shape_ok(M, N, K, x, y, ld_y) || reinterpret_cast<uintptr_t>(w_nk) % 16) return VQG_ERR_UNSUPPORTED;
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w_nk, N, K, BN)) return VQG_ERR_LAUNCH;
+  TensorParams tp{};
+  tp.y = y;
+  tp.status = device_status_ptr();
+  tp.M = M; tp.N = N; tp.K = K; tp.C = 0;
+  tp.rows_per_cb = N;
+  tp.ld_y = ld_y;
+  tp.m_tiles = (M + BM - 1) / BM;
+  tp.n_tiles = (N + BN - 1) / BN;
+  tp.n_peers = n_peers;
+  for (int i = 0; i < n_peers && i < 8; ++i) tp.peer_y[i] = peer_y[i];
+  constexpr int S = 3;
+  const size_t smem = SmemLayout<S>::kTotal + 1024;
+  return launch_common(vq_tensor_kernel<4, true, S>, smem, mx, mw, tp, s);
+}
+
+}  // namespace vqg

@@ -1,0 +1,176 @@
+"""Host-side mirror of the reference's extension module (bind.cpp:3-8) on top of the C ABI.
+
+    e2e_gemm(input, w, codebook) -> o      same positional signature as the reference
+    gemm(input, w) -> o                    dense fp16 product, w given as [K, N]
+    vq_gemm(x, indices, codebook, ...)     generalised entry point (both weight formats)
+    dequant(indices, codebook, ...)        bit-exact dequantised weights
+
+All tensors must be CUDA tensors on one device; the output is allocated by the callee on that
+device (the reference hard-codes device 0, strategy_1/src.cu:343) and the launch goes to torch's
+current stream (the reference uses the legacy default stream).  Errors raise ``RuntimeError``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .formats import infer_layout
+
+_workspaces: dict = {}
+
+
+def _ws(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
+    """Cached, zero-initialised scratch per (device, stream); grown geometrically.  The library
+    keeps the counter region zero between calls."""
+    if nbytes == 0:
+        return None
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    cur = _workspaces.get(key)
+    if cur is None or cur.numel() < nbytes:
+        cur = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = cur
+    return cur
+
+
+def _require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("vq_gemm_b200 has no CPU path: all tensors must be CUDA tensors")
+        if t.device != dev:
+            raise RuntimeError("all tensors must be on the same CUDA device")
+        if not t.is_contiguous():
+            raise RuntimeError("tensors must be contiguous")
+    return dev
+
+
+def _idx_bytes(indices: torch.Tensor) -> int:
+    if indices.dtype == torch.uint8:
+        return 1
+    if indices.dtype in (torch.int16, torch.uint16):
+        return 2
+    raise RuntimeError(f"indices must be uint8 or (u)int16, got {indices.dtype}")
+
+
+def _stream_ptr(dev) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def vq_gemm(x: torch.Tensor, indices: torch.Tensor, codebook: torch.Tensor, *, rows_per_codebook: Optional[int] = None,
+            layout: str = "auto", path: str = "auto", out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Y = X @ dequant(indices, codebook)^T, fp16 in and out, fp32 accumulation."""
+    lib = _lib.load()
+    dev = _require_cuda(x, indices, codebook)
+    if x.dtype != torch.float16 or codebook.dtype != torch.float16:
+        raise RuntimeError("x and codebook must be float16")
+    if layout == "auto":
+        layout = infer_layout(x, indices, codebook)
+    M, K = x.shape
+    ib = _idx_bytes(indices)
+    if layout == "bl":
+        N = indices.shape[0]
+        cb3 = codebook if codebook.dim() == 3 else codebook.unsqueeze(0)
+        G, C, v = cb3.shape
+        if indices.shape[1] * v != K:
+            raise RuntimeError(f"indices [N, K/v] = {tuple(indices.shape)} does not match K={K}, v={v}")
+        if rows_per_codebook is None:
+            if G == 1:
+                rows_per_codebook = 0
+            elif N % G == 0:
+                rows_per_codebook = N // G
+            else:
+                raise RuntimeError("cannot infer rows_per_codebook: N is not a multiple of the number of codebooks")
+        need_groups = 1 if rows_per_codebook <= 0 else -(-N // rows_per_codebook)
+        if G < need_groups:
+            raise RuntimeError(f"{G} codebooks given, {need_groups} needed")
+        lay = _lib.LAYOUT_BL
+    elif layout == "ref":
+        Kw, Nq = indices.shape
+        if Kw != K or codebook.dim() != 3 or tuple(codebook.shape) != (Nq // 4, 256, 2) or Nq % 4 or ib != 1:
+            raise RuntimeError("reference format needs w [K, Nq] uint8 and codebook [Nq/4, 256, 2]")
+        N, v, C, rows_per_codebook = 2 * Nq, 2, 256, 0
+        lay = _lib.LAYOUT_REF
+    else:
+        raise RuntimeError(f"unknown layout {layout!r}")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=dev)
+    elif tuple(out.shape) != (M, N) or out.dtype != torch.float16 or not out.is_contiguous() or out.device != dev:
+        raise RuntimeError("out must be a contiguous float16 [M, N] tensor on the inputs' device")
+    pth = _lib.PATHS[path]
+    with torch.cuda.device(dev):
+        nbytes = lib.vqg_workspace_bytes(M, N, K, v, C, ib, rows_per_codebook, lay, pth)
+        ws = _ws(dev, nbytes)
+        st = lib.vqg_gemm_path(x.data_ptr(), indices.data_ptr(), codebook.data_ptr(), out.data_ptr(), M, N, K, v, C, ib,
+                               rows_per_codebook, lay, pth, ws.data_ptr() if ws is not None else None,
+                               ws.numel() if ws is not None else 0, _stream_ptr(dev))
+    _lib.check(st, "vq_gemm")
+    return out
+
+
+def e2e_gemm(input: torch.Tensor, w: torch.Tensor, codebook: torch.Tensor) -> torch.Tensor:
+    """Drop-in for the reference's ``e2e_gemm`` (bind.cpp:3,7).  Accepts the reference's format
+    (w [K, Nq] uint8, codebook [Nq/4, 256, 2]) and, by shape, the generalised one."""
+    return vq_gemm(input, w, codebook)
+
+
+def gemm(input: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """Drop-in for the reference's ``gemm`` (bind.cpp:4,8): input [M, K] @ w [K, N], fp16."""
+    lib = _lib.load()
+    dev = _require_cuda(input, w)
+    if input.dtype != torch.float16 or w.dtype != torch.float16:
+        raise RuntimeError("gemm expects float16 tensors")
+    M, K = input.shape
+    if w.dim() != 2 or w.shape[0] != K:
+        raise RuntimeError("gemm expects w [K, N]")
+    N = w.shape[1]
+    out = torch.empty((M, N), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        ws = _ws(dev, lib.vqg_dense_workspace_bytes(M, N, K, 1))
+        st = lib.vqg_dense_gemm(input.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, 1,
+                                ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                                _stream_ptr(dev))
+    _lib.check(st, "gemm")
+    return out
+
+
+def dequant(indices: torch.Tensor, codebook: torch.Tensor, *, rows_per_codebook: Optional[int] = None,
+            layout: str = "bl") -> torch.Tensor:
+    """Dequantised weights: ``[N, K]`` for the generalised format, ``[K, 2*Nq]`` for the reference's."""
+    lib = _lib.load()
+    dev = _require_cuda(indices, codebook)
+    if codebook.dtype != torch.float16:
+        raise RuntimeError("codebook must be float16")
+    ib = _idx_bytes(indices)
+    if layout == "bl":
+        cb3 = codebook if codebook.dim() == 3 else codebook.unsqueeze(0)
+        G, C, v = cb3.shape
+        N, J = indices.shape
+        K = J * v
+        if rows_per_codebook is None:
+            rows_per_codebook = 0 if G == 1 else N // G
+        out = torch.empty((N, K), dtype=torch.float16, device=dev)
+        args = (N, K, v, C, ib, rows_per_codebook, _lib.LAYOUT_BL)
+    elif layout == "ref":
+        K, Nq = indices.shape
+        out = torch.empty((K, 2 * Nq), dtype=torch.float16, device=dev)
+        args = (2 * Nq, K, 2, 256, ib, 0, _lib.LAYOUT_REF)
+    else:
+        raise RuntimeError(f"unknown layout {layout!r}")
+    with torch.cuda.device(dev):
+        st = lib.vqg_dequant(indices.data_ptr(), codebook.data_ptr(), out.data_ptr(), *args, _stream_ptr(dev))
+    _lib.check(st, "dequant")
+    return out
+
+
+def device_status() -> int:
+    """Reads and clears the device status word (0 = no bounded wait has run out)."""
+    code = ctypes.c_int(0)
+    _lib.load().vqg_device_status(ctypes.byref(code))
+    return code.value
+
+
+def launch_count() -> int:
+    return int(_lib.load().vqg_launch_count())

@@ -1,0 +1,384 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 VQ-GEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One JSON line on stdout (rank 0).  A *step* is one product Y = X @ dequant(idx, codebook)^T on
+the workload's synthetic inputs (seeded; X ~ N(0,1) fp16, codebook ~ N(0, 0.02) fp16, uniform
+indices).  The default workload is the Llama-3-70B MLP up-projection shape (M=2048, K=8192,
+N=28672, v=8, C=256, one codebook per 128 rows, 1 bit/weight): it fits one GPU and is the shape
+that is N-sharded over 2/4/8 GPUs, so the same workload is timed at every N (strong scaling:
+each rank owns N/G output columns and the fp16 output is assembled on every rank).
+
+``value``      TFLOP/s (2*M*N*K per step) with inputs resident in HBM, CUDA events, max over ranks.
+``e2e``        the same metric through the public Python entry point with HOST inputs: every step
+               copies X, indices and codebooks from pinned host memory, runs the product and
+               copies the rank's output columns back to pinned host memory.
+``roofline``   the dominant kernel against the measured dense 16-bit tensor peak (or HBM peak for
+               the M <= 16 workloads), from CUDA-event time of the kernel alone.
+``shapes``     (N=1 only) the other single-GPU configurations, each with its own roofline, and
+               cuBLAS fp16 (torch.matmul) on pre-dequantised weights for the prefill shapes.
+``cpu_baseline`` the torch CPU oracle (gather + fp32-accumulated matmul) on a bounded sample.
+
+``--impl reference`` times the reference's torch path restated for CPU (oracle/vq_oracle.py) on
+the host cores, same metric and workload, bounded sample per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"], "tflops_sustained": d.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0.0, set()
+        for r in self.rows:
+            try:
+                clk, mxc, pw = float(r[0]), float(r[1]), float(r[2])
+            except Exception:
+                continue
+            mx = max(mx, mxc)
+            if pw > 250.0:  # under load
+                sm.append(clk)
+                for name, flag in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                    if flag.lower().startswith("active"):
+                        reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples_under_load": len(sm)}
+
+
+def _events():
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def _time_loop(fn, steps, warmup, barrier=None, counter=None):
+    """W untimed steps, then exactly `steps` steps between a barrier + synchronize on both sides,
+    timed with CUDA events on the launching stream.  Returns ms per step (and, with `counter`,
+    the number of library kernel launches inside the timed region)."""
+    for _ in range(warmup):
+        fn()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    c0 = counter() if counter else 0
+    e0, e1 = _events()
+    e0.record()
+    for i in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    ms = e0.elapsed_time(e1) / steps
+    return (ms, counter() - c0) if counter else ms
+
+
+def _single_shape(V, shape, peaks, steps, warmup):
+    """One single-GPU configuration: kernel time over a ring of index buffers larger than L2."""
+    from vq_gemm_b200.formats import make_inputs
+    x, idx, cb = make_inputs(shape, seed=0, device="cuda")
+    ring = 1
+    if shape.bound == "hbm":
+        ring = max(2, int(400e6 // shape.bytes_idx) + 1)
+    idxs = [idx] + [idx.clone() for _ in range(ring - 1)]
+    out = torch.empty((shape.M, shape.N), dtype=torch.float16, device="cuda")
+    state = {"i": 0}
+
+    def step():
+        V.vq_gemm(x, idxs[state["i"] % ring], cb, rows_per_codebook=shape.rows_per_codebook, layout="bl", out=out)
+        state["i"] += 1
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    # CUDA-graph replay of `ring` launches removes host launch gaps for the microsecond kernels
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g):
+            for i in range(ring):
+                V.vq_gemm(x, idxs[i], cb, rows_per_codebook=shape.rows_per_codebook, layout="bl", out=out)
+    torch.cuda.current_stream().wait_stream(side)
+    reps = max(3, steps // ring)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = _events()
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / (reps * ring)
+    res = {"workload": shape.name, "M": shape.M, "K": shape.K, "N": shape.N, "v": shape.v, "C": shape.C,
+           "us_per_launch": ms * 1e3, "tflops": shape.flops / ms / 1e9, "gbs_compressed": shape.bytes_algorithmic / ms / 1e6,
+           "ring_buffers": ring, "timing": "cuda-graph replay, CUDA events"}
+    if shape.bound == "hbm":
+        a = shape.bytes_algorithmic / ms / 1e6
+        res["roofline"] = {"bound": "hbm", "achieved": a, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                           "frac": a / peaks["hbm_gbs"], "frac_of_nominal_8000": a / 8000.0}
+    else:
+        a = shape.flops / ms / 1e9
+        res["roofline"] = {"bound": "tensor", "achieved": a, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                           "frac": a / peaks["tflops"], "frac_of_nominal_2250": a / 2250.0}
+        # cuBLAS fp16 on pre-dequantised weights (the reference's ref_gemm comparator)
+        w = V.dequant(idx, cb, rows_per_codebook=shape.rows_per_codebook)
+        wt = w.t()
+        for _ in range(3):
+            torch.matmul(x, wt)
+        torch.cuda.synchronize()
+        n = max(5, min(steps, 30))
+        e0.record()
+        for _ in range(n):
+            torch.matmul(x, wt)
+        e1.record()
+        torch.cuda.synchronize()
+        cms = e0.elapsed_time(e1) / n
+        res["cublas_fp16_dequantised"] = {"tflops": shape.flops / cms / 1e9, "us": cms * 1e3,
+                                          "speedup_vs_cublas": cms / ms}
+        del w, wt
+    return res
+
+
+def _cpu_sample(shape, seconds_budget=20.0):
+    """Torch CPU oracle on a column block of the workload (full M and K)."""
+    from oracle import vq_oracle as O
+    from vq_gemm_b200.formats import make_inputs
+    rpc = shape.rows_per_codebook
+    n_rows = shape.N
+    if rpc > 0:
+        n_rows = min(shape.N, max(rpc, (shape.N // 8) // rpc * rpc))
+    x, idx, cb = make_inputs(shape, seed=0, n_rows=n_rows if rpc > 0 else None)
+    t0 = time.perf_counter()
+    O.vq_gemm_bl(x, idx, cb, rpc)
+    first = time.perf_counter() - t0
+    iters = max(1, min(5, int(seconds_budget / max(first, 1e-3)) - 1))
+    t0 = time.perf_counter()
+    for _ in range(iters):
+        O.vq_gemm_bl(x, idx, cb, rpc)
+    dt = (time.perf_counter() - t0) / iters
+    flops = 2.0 * shape.M * idx.shape[0] * shape.K
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "host_cpus": os.cpu_count(), "seconds_per_sample": dt,
+            "sample": f"{idx.shape[0]} of {shape.N} output columns, full M={shape.M} and K={shape.K}; "
+                      f"torch gather + fp32 matmul + fp16 cast, {iters} iterations"}
+
+
+def run_reference(args, shape):
+    """The reference's torch path on the host cores (CPU restatement), bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import vq_oracle as O
+    from vq_gemm_b200.formats import make_inputs
+    rpc = shape.rows_per_codebook
+    n_rows = min(shape.N, max(rpc, (shape.N // 32) // max(rpc, 1) * max(rpc, 1))) if rpc > 0 else shape.N
+    x, idx, cb = make_inputs(shape, seed=0, n_rows=n_rows if rpc > 0 else None)
+    for _ in range(args.warmup):
+        O.vq_gemm_bl(x, idx, cb, rpc)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.vq_gemm_bl(x, idx, cb, rpc)
+    dt = (time.perf_counter() - t0) / args.steps
+    flops = 2.0 * shape.M * idx.shape[0] * shape.K
+    val = flops / dt / 1e12
+    sample = f"{idx.shape[0]} of {shape.N} output columns per step, full M and K"
+    print(json.dumps({
+        "impl": "reference", "metric": "vq_gemm_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": shape.name, "M": shape.M, "K": shape.K, "N": shape.N, "v": shape.v, "C": shape.C,
+                   "rows_per_codebook": rpc, "note": "reference torch path (index gather + fp32-accumulated matmul) on host cores"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c5_mlp70b")
+    ap.add_argument("--mode", default="peer", choices=["peer", "nccl"], help="how the N-sharded output is assembled")
+    ap.add_argument("--no-shapes", action="store_true", help="skip the per-configuration table")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    from vq_gemm_b200.formats import CONFIGS, make_inputs
+    shape = CONFIGS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, shape)
+        return
+
+    import torch.distributed as dist
+    import vq_gemm_b200 as V
+    from vq_gemm_b200.sharded import ShardedVQGemm, partition
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world and world == 1 and args.gpus > 1:
+        raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    barrier = (lambda: dist.barrier()) if world > 1 else None
+    peaks = _peaks()
+
+    rpc = shape.rows_per_codebook
+    row0, n_local = partition(shape.N, world, rank, rpc)
+    x_h, idx_h, cb_h = make_inputs(shape, seed=0, n_rows=n_local if rpc > 0 else None, row0=row0)
+    x_h, idx_h, cb_h = x_h.pin_memory(), idx_h.pin_memory(), cb_h.pin_memory()
+    x, idx, cb = x_h.to(dev), idx_h.to(dev), cb_h.to(dev)
+    op = ShardedVQGemm(shape.M, shape.N, mode=args.mode, device=dev)
+
+    # clock warm-up: the SM clock idles at a few hundred MHz
+    a = torch.randn(4096, 4096, device=dev, dtype=torch.float16)
+    t0 = time.time()
+    while time.time() - t0 < 0.5:
+        a @ a
+    torch.cuda.synchronize()
+
+    def step():
+        op(x, idx, cb, rpc)
+
+    with ClockSampler(local) as clocks:
+        ms, launches = _time_loop(step, args.steps, args.warmup, barrier, counter=V.launch_count)
+
+        # kernel alone (no barriers, local columns only) for the roofline
+        def kernel_only():
+            V.vq_gemm(x, idx, cb, rows_per_codebook=rpc, layout="bl", out=kout)
+        kout = torch.empty((shape.M, n_local), dtype=torch.float16, device=dev)
+        kms = _time_loop(kernel_only, max(10, args.steps // 2), 3, None)
+
+        # end to end: host inputs in, host output out, every step
+        y_h = torch.empty((shape.M, n_local), dtype=torch.float16).pin_memory()
+        xd, idxd, cbd = torch.empty_like(x), torch.empty_like(idx), torch.empty_like(cb)
+
+        def e2e_step():
+            xd.copy_(x_h, non_blocking=True)
+            idxd.copy_(idx_h, non_blocking=True)
+            cbd.copy_(cb_h, non_blocking=True)
+            y = op(xd, idxd, cbd, rpc)
+            y_h.copy_(y[:, row0:row0 + n_local], non_blocking=True)
+        e2e_steps = max(5, args.steps // 4)
+        ems = _time_loop(e2e_step, e2e_steps, 3, barrier)
+    status = V.device_status()
+
+    def reduce_max(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms, kms, ems = reduce_max(ms), reduce_max(kms), reduce_max(ems)
+    h2d = x_h.numel() * 2 + idx_h.numel() * idx_h.element_size() + cb_h.numel() * 2
+    d2h = y_h.numel() * 2
+    flops = shape.flops
+    kflops = 2.0 * shape.M * n_local * shape.K
+    if shape.bound == "tensor":
+        ach = kflops / kms / 1e9
+        roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"],
+                "traffic": None, "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                "frac_of_sustained": ach / peaks["tflops_sustained"] if peaks["tflops_sustained"] else None,
+                "frac_of_nominal_2250": ach / 2250.0, "kernel": "vq_tensor_kernel", "kernel_us": kms * 1e3}
+    else:
+        b = shape.bytes_algorithmic / world
+        ach = b / kms / 1e6
+        roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                "traffic": None, "peak_source": peaks["source"], "kernel": "vq_decode_kernel", "kernel_us": kms * 1e3}
+
+    line = {
+        "metric": "vq_gemm_tflops", "value": flops / ms / 1e9, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": shape.name, "M": shape.M, "K": shape.K, "N": shape.N, "v": shape.v, "C": shape.C,
+                   "rows_per_codebook": rpc, "idx_bytes": shape.idx_bytes, "parallelism": f"N-sharded x{world}",
+                   "gather": args.mode if world > 1 else "none",
+                   "l2": "working set (indices + X + Y = 180 MB) larger than the 126 MB L2"},
+        "e2e": {"value": flops / ems / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ems, "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "roofline": roof,
+        "clocks": clocks.summary(),
+        "device_status": status,
+    }
+    if world == 1 and rank == 0 and not args.no_shapes:
+        shapes = []
+        for name in ("c1_cpu_ref", "c2_decode", "c3_small_batch", "c4_prefill"):
+            try:
+                shapes.append(_single_shape(V, CONFIGS[name], peaks, max(args.steps, 200), args.warmup))
+            except Exception as e:  # keep the headline line even if a side measurement fails
+                shapes.append({"workload": name, "error": repr(e)})
+        line["shapes"] = shapes
+    if rank == 0:
+        if world == 1:
+            try:
+                line["cpu_baseline"] = _cpu_sample(shape)
+            except Exception as e:
+                line["cpu_baseline"] = {"error": repr(e)}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,47 @@
+"""Worker for tests/test_gpu_sharded.py (one process per GPU, started by torch.distributed.run)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import vq_gemm_b200 as V  # noqa: E402
+from oracle import vq_oracle as O  # noqa: E402
+from vq_gemm_b200.sharded import ShardedVQGemm, shard_weights  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    ok = True
+    for (M, K, N, v, C, rpc) in [(256, 512, 1024, 4, 256, 128), (4, 1024, 512, 8, 256, 128), (512, 1024, 2048, 8, 256, 128)]:
+        x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=5)
+        single = V.vq_gemm(x.to(dev), idx.to(dev), cb.to(dev), rows_per_codebook=rpc, layout="bl")
+        idx_l, cb_l = shard_weights(idx, cb, world, rank, rpc)
+        for mode in ("peer", "nccl"):
+            op = ShardedVQGemm(M, N, mode=mode, device=dev)
+            for _ in range(3):
+                y = op(x.to(dev), idx_l.to(dev), cb_l.to(dev), rpc)
+            torch.cuda.synchronize()
+            same = bool(torch.equal(y.view(torch.int16), single.view(torch.int16)))
+            tol = O.check_tolerance(y.cpu(), O.vq_gemm_bl(x, idx, cb, rpc))["ok"]
+            if not (same and tol):
+                ok = False
+                print(f"rank {rank}: MISMATCH mode={mode} shape={(M, K, N, v)} bitwise={same} tol={tol}", flush=True)
+    ok = ok and V.device_status() == 0
+    t = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("SHARDED_OK" if int(t.item()) == 1 else "SHARDED_FAIL", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if int(t.item()) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()

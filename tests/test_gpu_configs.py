@@ -1,0 +1,52 @@
+"""The five benchmark configurations at full size.  The CPU oracle covers the whole output for the
+small ones and a seeded subset of rows and columns for the large ones; on top of that, the
+size-independent properties: bit-exact dequantisation, determinism, exact linearity under
+power-of-two scaling of X, and agreement between the fused and the two-phase route."""
+import pytest
+import torch
+
+import vq_gemm_b200 as V
+from oracle import vq_oracle as O
+from tests._util import assert_within_tolerance, bits
+from vq_gemm_b200.formats import CONFIGS, make_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", ["c1_cpu_ref", "c2_decode", "c3_small_batch"])
+def test_small_batch_configs_full_oracle(name):
+    s = CONFIGS[name]
+    x, idx, cb = make_inputs(s, seed=0)
+    y = V.vq_gemm(x.cuda(), idx.cuda(), cb.cuda(), rows_per_codebook=s.rows_per_codebook, layout="bl")
+    torch.cuda.synchronize()
+    assert V.device_status() == 0
+    assert_within_tolerance(y.cpu(), O.vq_gemm_bl(x, idx, cb, s.rows_per_codebook), name)
+    y2 = V.vq_gemm(x.cuda(), idx.cuda(), cb.cuda(), rows_per_codebook=s.rows_per_codebook, layout="bl")
+    assert torch.equal(bits(y), bits(y2))
+
+
+@pytest.mark.parametrize("name", ["c4_prefill", "c5_mlp70b"])
+def test_large_configs_subset_oracle_and_properties(name):
+    s = CONFIGS[name]
+    x, idx, cb = make_inputs(s, seed=0)
+    xd, idd, cbd = x.cuda(), idx.cuda(), cb.cuda()
+    y = V.vq_gemm(xd, idd, cbd, rows_per_codebook=s.rows_per_codebook, layout="bl")
+    torch.cuda.synchronize()
+    assert V.device_status() == 0
+    g = torch.Generator().manual_seed(1)
+    rows = torch.randperm(s.M, generator=g)[:64].sort().values
+    cols = torch.cat([torch.randperm(s.N, generator=g)[:1024], torch.tensor([0, 127, 128, s.N - 1])]).unique()
+    sub = O.vq_gemm_bl_rows(x, idx, cb, s.rows_per_codebook, rows, cols)
+    assert_within_tolerance(y.cpu()[rows][:, cols], sub, name)
+    # determinism
+    y2 = V.vq_gemm(xd, idd, cbd, rows_per_codebook=s.rows_per_codebook, layout="bl")
+    assert torch.equal(bits(y), bits(y2))
+    # exact linearity under scaling of X by 2
+    y4 = V.vq_gemm((xd.float() * 2).half(), idd, cbd, rows_per_codebook=s.rows_per_codebook, layout="bl")
+    assert torch.equal(bits((y.float() * 2).half()), bits(y4))
+    # fused route == dequantise-then-dense route, bit for bit
+    y3 = V.vq_gemm(xd, idd, cbd, rows_per_codebook=s.rows_per_codebook, layout="bl", path="two_phase")
+    assert torch.equal(bits(y), bits(y3))
+    # dequantised weights bit-exact on a slab of rows
+    w = V.dequant(idd[:4096], cbd[:32], rows_per_codebook=128).cpu()
+    assert torch.equal(bits(w), bits(O.dequant_bl_layout(idx[:4096], cb[:32], 128)))

@@ -1,0 +1,61 @@
+"""N-sharded mode on real GPUs: with 2 ranks, both ways of assembling Y (fused peer stores over
+NVLink, NCCL all-gather + re-layout) must equal the single-GPU result bit for bit.  Runs as child
+processes; skipped on a single-GPU box (the world-size-1 path is covered below)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import vq_gemm_b200 as V
+from oracle import vq_oracle as O
+from tests._util import ROOT, assert_within_tolerance, bits
+
+pytestmark = pytest.mark.gpu
+
+
+def test_world_size_one_is_the_plain_product():
+    import ctypes
+    from vq_gemm_b200 import _lib
+    x, idx, cb = O.make_bl_inputs(130, 256, 512, 4, 256, 128, seed=2)
+    xd, idd, cbd = x.cuda(), idx.cuda(), cb.cuda()
+    y = torch.zeros(130, 512, dtype=torch.float16, device="cuda")
+    arr = (ctypes.c_void_p * 1)(y.data_ptr())
+    st = _lib.load().vqg_gemm_sharded(xd.data_ptr(), idd.data_ptr(), cbd.data_ptr(), arr, 0, 1, 130, 512, 256, 4, 256, 1,
+                                      128, None, 0, torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    torch.cuda.synchronize()
+    assert torch.equal(bits(y), bits(V.vq_gemm(xd, idd, cbd, rows_per_codebook=128, layout="bl")))
+    assert_within_tolerance(y.cpu(), O.vq_gemm_bl(x, idx, cb, 128))
+
+
+def test_column_block_with_leading_dimension():
+    # a rank's block written into a wider Y (emulates rank 1 of 2 on one GPU, no peers)
+    import ctypes
+    from vq_gemm_b200 import _lib
+    x, idx, cb = O.make_bl_inputs(64, 512, 512, 8, 256, 128, seed=3)
+    full = O.vq_gemm_bl(x, idx, cb, 128)
+    y = torch.zeros(64, 512, dtype=torch.float16, device="cuda")
+    other = torch.zeros_like(y)
+    for rank in range(2):
+        idx_l, cb_l = idx[rank * 256:(rank + 1) * 256].contiguous().cuda(), cb[rank * 2:(rank + 1) * 2].contiguous().cuda()
+        ptrs = [other.data_ptr(), other.data_ptr()]
+        ptrs[rank] = y.data_ptr()
+        arr = (ctypes.c_void_p * 2)(*ptrs)
+        st = _lib.load().vqg_gemm_sharded(x.cuda().data_ptr(), idx_l.data_ptr(), cb_l.data_ptr(), arr, rank, 2, 64, 256, 512,
+                                          8, 256, 1, 128, None, 0, torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+        torch.cuda.synchronize()
+    # y holds both blocks (each call wrote its own block locally); `other` received both as the "peer"
+    assert_within_tolerance(y.cpu(), full)
+    assert torch.equal(bits(y), bits(other))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_ranks_equal_single_gpu():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29511", os.path.join(ROOT, "tests", "_sharded_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert p.returncode == 0 and "SHARDED_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]

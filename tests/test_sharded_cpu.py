@@ -1,0 +1,78 @@
+"""Host-side logic of the N-sharded mode on CPU: partition arithmetic, weight sharding, and a
+world-size-2 gloo run in which each rank computes its column block (with the oracle standing in
+for the CUDA kernel) and the all-gathered blocks are interleaved into the full Y."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import vq_oracle as O
+from vq_gemm_b200.sharded import interleave_blocks, partition, shard_weights
+
+
+def test_partition():
+    assert partition(28672, 8, 3, 128) == (3 * 3584, 3584)
+    assert partition(28672, 1, 0, 128) == (0, 28672)
+    assert partition(1024, 2, 1, 0) == (512, 512)
+    with pytest.raises(ValueError):
+        partition(11008, 4, 0, 128)      # 86 groups do not split 4 ways
+    with pytest.raises(ValueError):
+        partition(1024, 2, 2, 128)
+    assert partition(11008, 2, 1, 128) == (5504, 5504)
+    assert partition(768, 2, 0, 192) == (0, 384)   # block must hold whole 192-row groups and 128-column units
+
+
+def test_shard_weights_cover_the_matrix():
+    _, idx, cb = O.make_bl_inputs(1, 64, 1024, 4, 256, 128, seed=0)
+    parts = [shard_weights(idx, cb, 4, r, 128) for r in range(4)]
+    assert torch.equal(torch.cat([p[0] for p in parts]), idx)
+    assert torch.equal(torch.cat([p[1] for p in parts]), cb)
+    i0, c0 = shard_weights(idx, cb[:1], 2, 1, 0)    # single codebook: replicated
+    assert i0.shape[0] == 512 and c0.shape[0] == 1
+
+
+def test_interleave_blocks():
+    g = torch.arange(2 * 3 * 4).reshape(2, 3, 4)
+    y = interleave_blocks(g)
+    assert y.shape == (3, 8)
+    assert torch.equal(y[:, :4], g[0]) and torch.equal(y[:, 4:], g[1])
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, M, K, N, v, C, rpc, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=11)
+    idx_l, cb_l = shard_weights(idx, cb, world, rank, rpc)
+    block = O.vq_gemm_bl(x, idx_l, cb_l, rpc)                 # stand-in for the CUDA kernel
+    gathered = torch.empty(world, M, N // world, dtype=torch.float16)
+    dist.all_gather_into_tensor(gathered, block)
+    y = interleave_blocks(gathered)
+    full = O.vq_gemm_bl(x, idx, cb, rpc)
+    q.put((rank, bool(torch.equal(y.view(torch.int16), full.view(torch.int16)))))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("rpc", [128, 0])
+def test_two_rank_gather_equals_single_rank(rpc):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, 5, 64, 512, 4, 256, rpc, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert res == [(0, True), (1, True)]

@@ -1,0 +1,126 @@
+"""N-sharded multi-GPU VQ-GEMM: each rank owns a block of output columns (rows of the index
+matrix and the codebooks of those rows), X is replicated, and every rank ends up with the whole
+Y[M, N].  One process per GPU, ``torch.distributed`` for the plumbing.
+
+Two ways of assembling Y:
+
+``mode="peer"``   Y lives in symmetric memory (one [M, N] buffer per rank, peer-mapped over
+                  NVLink).  The GEMM epilogue stores each finished tile into every rank's buffer
+                  with ordinary global stores (``vqg_gemm_sharded``), so the exchange overlaps the
+                  main loop; a device-side barrier across ranks ends the step.  No TMA and no
+                  multicast touch peer memory.
+``mode="nccl"``   each rank computes its [M, N/G] block, NCCL all-gathers the blocks into
+                  [G, M, N/G] and a re-layout copy interleaves them into [M, N].
+
+The reference has no multi-GPU code (device 0 is hard-coded, strategy_1/src.cu:343).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+def partition(N: int, world: int, rank: int, rows_per_codebook: int = 0, align: int = 128) -> Tuple[int, int]:
+    """Column block ``(row0, n_local)`` of rank ``rank``: equal blocks, each a whole number of
+    codebook groups and of ``align`` columns.  Raises if N does not split that way."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError("bad rank / world size")
+    unit = math.lcm(align, rows_per_codebook) if rows_per_codebook > 0 else align
+    if N % (world * unit):
+        raise ValueError(f"N={N} does not split into {world} blocks of a multiple of {unit} columns")
+    n_local = N // world
+    return rank * n_local, n_local
+
+
+def shard_weights(idx: torch.Tensor, codebook: torch.Tensor, world: int, rank: int, rows_per_codebook: int):
+    """Slices a full (idx [N, K/v], codebook [G, C, v]) pair down to the rank's block."""
+    N = idx.shape[0]
+    row0, n_local = partition(N, world, rank, rows_per_codebook)
+    if rows_per_codebook <= 0:
+        return idx[row0:row0 + n_local].contiguous(), codebook  # one codebook: every rank holds it
+    g0 = row0 // rows_per_codebook
+    return (idx[row0:row0 + n_local].contiguous(),
+            codebook[g0:g0 + n_local // rows_per_codebook].contiguous())
+
+
+def interleave_blocks(gathered: torch.Tensor) -> torch.Tensor:
+    """[G, M, n_local] (what an all-gather of column blocks yields) -> [M, G*n_local]."""
+    G, M, n_local = gathered.shape
+    return gathered.permute(1, 0, 2).reshape(M, G * n_local)
+
+
+class ShardedVQGemm:
+    """Holds the per-rank output buffers and runs the sharded product.
+
+    Collective construction: every rank of ``group`` must create it with the same M and N."""
+
+    def __init__(self, M: int, N: int, *, group: Optional[dist.ProcessGroup] = None, mode: str = "peer",
+                 device: Optional[torch.device] = None):
+        if mode not in ("peer", "nccl"):
+            raise ValueError("mode must be 'peer' or 'nccl'")
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.M, self.N, self.mode = M, N, mode
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        if N % self.world:
+            raise ValueError("N must be a multiple of the world size")
+        self.n_local = N // self.world
+        self._hdl = None
+        if self.world == 1:
+            self.y = torch.empty((M, N), dtype=torch.float16, device=self.device)
+            self._ptrs = [self.y.data_ptr()]
+        elif mode == "peer":
+            import torch.distributed._symmetric_memory as symm_mem
+            self.y = symm_mem.empty((M, N), dtype=torch.float16, device=self.device)
+            self._hdl = symm_mem.rendezvous(self.y, self.group)
+            self._ptrs = [int(p) for p in self._hdl.buffer_ptrs]
+            if self._ptrs[self.rank] != self.y.data_ptr():
+                raise RuntimeError("symmetric memory: local buffer pointer mismatch")
+        else:
+            self.y = torch.empty((M, N), dtype=torch.float16, device=self.device)
+            self._block = torch.empty((M, self.n_local), dtype=torch.float16, device=self.device)
+            self._gathered = torch.empty((self.world, M, self.n_local), dtype=torch.float16, device=self.device)
+        self._ws = None
+
+    def _workspace(self, nbytes: int):
+        if nbytes == 0:
+            return None, 0
+        if self._ws is None or self._ws.numel() < nbytes:
+            self._ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        return self._ws.data_ptr(), self._ws.numel()
+
+    def __call__(self, x: torch.Tensor, idx_local: torch.Tensor, cb_local: torch.Tensor, rows_per_codebook: int = 0):
+        """x [M, K] (replicated), idx_local [N/G, K/v], cb_local: the block's codebooks.  Returns
+        the rank's full Y[M, N]; valid after the call on the current stream."""
+        lib = _lib.load()
+        M, K = x.shape
+        if M != self.M or idx_local.shape[0] != self.n_local:
+            raise RuntimeError("shapes do not match the buffers this object was built for")
+        cb3 = cb_local if cb_local.dim() == 3 else cb_local.unsqueeze(0)
+        _, C, v = cb3.shape
+        ib = 1 if idx_local.dtype == torch.uint8 else 2
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        if self.mode == "peer" or self.world == 1:
+            ws_ptr, ws_n = self._workspace(
+                lib.vqg_workspace_bytes(M, self.n_local, K, v, C, ib, rows_per_codebook, _lib.LAYOUT_BL, _lib.PATH_AUTO))
+            arr = (ctypes.c_void_p * self.world)(*self._ptrs)
+            if self._hdl is not None:
+                self._hdl.barrier()  # every rank has finished reading the previous step's Y
+            st = lib.vqg_gemm_sharded(x.data_ptr(), idx_local.data_ptr(), cb_local.data_ptr(), arr, self.rank,
+                                      self.world, M, self.n_local, K, v, C, ib, rows_per_codebook, ws_ptr, ws_n, stream)
+            _lib.check(st, "vqg_gemm_sharded")
+            if self._hdl is not None:
+                self._hdl.barrier()  # every rank's stores into this rank's buffer have landed
+            return self.y
+        from .ops import vq_gemm
+        vq_gemm(x, idx_local, cb_local, rows_per_codebook=rows_per_codebook, layout="bl", out=self._block)
+        dist.all_gather_into_tensor(self._gathered, self._block, group=self.group)
+        self.y.copy_(interleave_blocks(self._gathered))
+        return self.y

@@ -57,7 +57,7 @@ def _worker(rank, world, port, M, K, N, v, C, rpc, q):
     idx_l, cb_l = shard_weights(idx, cb, world, rank, rpc)
     block = O.vq_gemm_bl(x, idx_l, cb_l, rpc)                 # stand-in for the CUDA kernel
     gathered = torch.empty(world, M, N // world, dtype=torch.float16)
-    dist.all_gather_into_tensor(gathered, block)
+    dist.all_gather_into_tensor(gathered.view(world * M, N // world), block)
     y = interleave_blocks(gathered)
     full = O.vq_gemm_bl(x, idx, cb, rpc)
     q.put((rank, bool(torch.equal(y.view(torch.int16), full.view(torch.int16)))))

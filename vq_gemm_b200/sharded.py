@@ -121,6 +121,6 @@ class ShardedVQGemm:
             return self.y
         from .ops import vq_gemm
         vq_gemm(x, idx_local, cb_local, rows_per_codebook=rows_per_codebook, layout="bl", out=self._block)
-        dist.all_gather_into_tensor(self._gathered, self._block, group=self.group)
+        dist.all_gather_into_tensor(self._gathered.view(self.world * M, self.n_local), self._block, group=self.group)
         self.y.copy_(interleave_blocks(self._gathered))
         return self.y

@@ -42,8 +42,11 @@ def test_large_configs_subset_oracle_and_properties(name):
     y2 = V.vq_gemm(xd, idd, cbd, rows_per_codebook=s.rows_per_codebook, layout="bl")
     assert torch.equal(bits(y), bits(y2))
     # exact linearity under scaling of X by 2
+    # (outputs in the fp16 subnormal range round on a fixed grid, so they are compared by distance)
     y4 = V.vq_gemm((xd.float() * 2).half(), idd, cbd, rows_per_codebook=s.rows_per_codebook, layout="bl")
-    assert torch.equal(bits((y.float() * 2).half()), bits(y4))
+    normal = y.abs() >= 2.0 ** -13
+    assert torch.equal((y.float() * 2).half()[normal], y4[normal])
+    assert float((y.float() * 2 - y4.float()).abs().max()) <= 2.0 ** -23
     # fused route == dequantise-then-dense route, bit for bit
     y3 = V.vq_gemm(xd, idd, cbd, rows_per_codebook=s.rows_per_codebook, layout="bl", path="two_phase")
     assert torch.equal(bits(y), bits(y3))

@@ -60,4 +60,6 @@ def test_decode_linearity_in_x():
     x, idx, cb = O.make_bl_inputs(4, 4096, 1024, 4, 256, 128, seed=6)
     y1 = run_bl(V, x, idx, cb, 128, path="decode")
     y2 = run_bl(V, (x.float() * 2).half(), idx, cb, 128, path="decode")
-    assert torch.equal(bits((y1.float() * 2).half()), bits(y2))
+    normal = y1.abs() >= 2.0 ** -13   # fp16-subnormal outputs round on a fixed grid
+    assert torch.equal((y1.float() * 2).half()[normal], y2[normal])
+    assert float((y1.float() * 2 - y2.float()).abs().max()) <= 2.0 ** -23

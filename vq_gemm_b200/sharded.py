@@ -64,9 +64,12 @@ class ShardedVQGemm:
                  device: Optional[torch.device] = None):
         if mode not in ("peer", "nccl"):
             raise ValueError("mode must be 'peer' or 'nccl'")
-        self.group = group if group is not None else dist.group.WORLD
-        self.world = dist.get_world_size(self.group)
-        self.rank = dist.get_rank(self.group)
+        if dist.is_available() and dist.is_initialized():
+            self.group = group if group is not None else dist.group.WORLD
+            self.world = dist.get_world_size(self.group)
+            self.rank = dist.get_rank(self.group)
+        else:  # single process: behaves as a world of one
+            self.group, self.world, self.rank = None, 1, 0
         self.M, self.N, self.mode = M, N, mode
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         if N % self.world:

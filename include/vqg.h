@@ -63,9 +63,11 @@ VQG_API int vqg_version(void);
  * strategy_3/naive/src.cu:42-54 prints cudaGetLastError and continues.) */
 VQG_API const char* vqg_status_string(int status);
 
-/* Bytes of scratch the given problem needs (0 if none).  The first
+/* Bytes of scratch the given problem needs (0 if none).  In every workspace the first
  * vqg_workspace_counter_bytes() bytes hold arrival counters and must be zero when the
- * workspace is first used (cudaMemset once after allocation); the library leaves them zero.
+ * workspace is first used (cudaMemset once after allocation); the library leaves them zero and
+ * puts every other payload behind them, so one buffer can serve any sequence of calls that
+ * do not overlap on the GPU.
  * Replaces the per-call temporaries of the reference (strategy_1/src.cu:351 allocates
  * a [K, 2*Nq] matrix on every call). */
 VQG_API size_t vqg_workspace_bytes(int M, int N, int K, int v, int C, int idx_bytes,

@@ -54,9 +54,9 @@ def test_workspace_sizes(lib):
     assert lib.vqg_workspace_bytes(1, 11008, 4096, 4, 256, 1, 128, 0, 0) == 0
     assert lib.vqg_workspace_bytes(16, 8192, 8192, 8, 4096, 2, 0, 0, 0) == cb + 2 * 16 * 8192 * 4
     # two-phase: one fp16 copy of the dequantised weights
-    assert lib.vqg_workspace_bytes(256, 512, 256, 4, 256, 1, 128, 0, _lib.PATH_TWO_PHASE) == 512 * 256 * 2
+    assert lib.vqg_workspace_bytes(256, 512, 256, 4, 256, 1, 128, 0, _lib.PATH_TWO_PHASE) == cb + 512 * 256 * 2
     assert lib.vqg_workspace_bytes(0, 0, 0, 4, 256, 1, 0, 0, 0) == 0
-    assert lib.vqg_dense_workspace_bytes(128, 256, 64, 1) == 256 * 64 * 2
+    assert lib.vqg_dense_workspace_bytes(128, 256, 64, 1) == cb + 256 * 64 * 2
     assert lib.vqg_dense_workspace_bytes(128, 256, 64, 0) == 0
 
 

@@ -87,7 +87,9 @@ int auto_path(const Problem& p, int layout) {
   return VQG_PATH_GENERIC;
 }
 
-size_t two_phase_bytes(int N, int K) { return static_cast<size_t>(N) * K * 2; }
+// Every workspace starts with the counter region (kept zero by the split-K kernel); payloads of all
+// paths live behind it so that one cached buffer can serve any sequence of calls.
+size_t two_phase_bytes(int N, int K) { return kCounterBytes + static_cast<size_t>(N) * K * 2; }
 
 int run(const Problem& p, int layout, int path, void* ws, size_t ws_bytes, cudaStream_t s) {
   if (p.M == 0 || p.N == 0) return VQG_OK;
@@ -106,7 +108,7 @@ int run(const Problem& p, int layout, int path, void* ws, size_t ws_bytes, cudaS
       if (!dense_supported(p.M, p.N, p.K)) return VQG_ERR_UNSUPPORTED;
       const size_t need = two_phase_bytes(p.N, p.K);
       if (!ws || ws_bytes < need || !aligned(ws, 1024)) return VQG_ERR_WORKSPACE;
-      __half* w = static_cast<__half*>(ws);
+      __half* w = reinterpret_cast<__half*>(static_cast<unsigned char*>(ws) + kCounterBytes);
       int st;
       if (layout == VQG_LAYOUT_BL)
         st = launch_dequant_bl(p.idx, p.cb, w, p.N, p.K, p.v, p.C, p.idx_bytes, p.rows_per_cb, s);
@@ -193,7 +195,7 @@ int vqg_dequant(const void* idx, const void* codebook, void* w_out, int N, int K
 
 size_t vqg_dense_workspace_bytes(int M, int N, int K, int w_is_kn) {
   (void)M;
-  return w_is_kn ? static_cast<size_t>(N) * K * 2 : 0;
+  return w_is_kn ? kCounterBytes + static_cast<size_t>(N) * K * 2 : 0;
 }
 
 int vqg_dense_gemm(const void* x, const void* w, void* y, int M, int N, int K, int w_is_kn, void* workspace,
@@ -208,9 +210,10 @@ int vqg_dense_gemm(const void* x, const void* w, void* y, int M, int N, int K, i
   if (w_is_kn) {
     if (!workspace || workspace_bytes < vqg_dense_workspace_bytes(M, N, K, 1) || !aligned(workspace, 1024))
       return VQG_ERR_WORKSPACE;
-    const int st = launch_transpose(static_cast<const __half*>(w), static_cast<__half*>(workspace), K, N, s);
+    __half* wt = reinterpret_cast<__half*>(static_cast<unsigned char*>(workspace) + kCounterBytes);
+    const int st = launch_transpose(static_cast<const __half*>(w), wt, K, N, s);
     if (st != VQG_OK) return st;
-    w_nk = static_cast<const __half*>(workspace);
+    w_nk = wt;
   }
   return launch_dense(static_cast<const __half*>(x), w_nk, static_cast<__half*>(y), M, N, K, N, 0, nullptr, s);
 }

@@ -42,7 +42,8 @@ enum {
   VQG_ERR_WORKSPACE = 3,      /* workspace missing or smaller than vqg_workspace_bytes()        */
   VQG_ERR_LAUNCH = 4,         /* the CUDA runtime or driver refused a call                      */
   VQG_ERR_DEVICE_TIMEOUT = 5, /* a bounded device-side wait ran out (see vqg_device_status)     */
-  VQG_ERR_NO_DEVICE = 6       /* no usable sm_100 device / driver                                */
+  VQG_ERR_NO_DEVICE = 6,      /* no usable sm_100 device / driver                                */
+  VQG_ERR_TOO_LARGE = 7       /* problem needs more scratch than the built-in static buffer has */
 };
 
 enum { VQG_LAYOUT_BL = 0, VQG_LAYOUT_REF = 1 };
@@ -115,6 +116,33 @@ VQG_API int vqg_gemm_sharded(const void* x, const void* idx, const void* codeboo
                      void* const* y_peers, int rank, int nranks,
                      int M, int N_local, int K, int v, int C, int idx_bytes, int rows_per_codebook,
                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* Small-batch product (M <= 16) for callers that must not allocate device memory.  (This entry
+ * point has no counterpart in the reference.)
+ *
+ * Who needs it: host programs that hand the whole of the GPU's memory to their own pool when
+ * they start (inference servers commonly do), so that a cudaMalloc made later from inside a
+ * plugin fails or eats into memory the host believes it owns; and callers on a latency-critical
+ * path, because cudaMalloc and cudaFree synchronise the whole device.  vqg_gemm() needs a
+ * caller-allocated workspace when K > 4096 (split-K partial sums); this variant of the same
+ * kernel keeps that scratch in a fixed array of VQG_NOALLOC_SCRATCH_BYTES inside the library
+ * image instead -- every GPU that loads the library holds those bytes until the process exits.
+ * The call itself makes no cudaMalloc / cudaFree and calls no allocating library routine.
+ *
+ * Limits and rules:
+ *   - same shapes as the decode path of vqg_gemm (BL layout, M <= 16, K % 256 == 0, N % 16 == 0);
+ *     anything else returns VQG_ERR_UNSUPPORTED -- there is no other kernel behind this entry;
+ *   - the scratch a problem needs is 64 KiB + ceil(K/4096) * M * N * 4 bytes when K > 4096 and
+ *     nothing otherwise; beyond VQG_NOALLOC_SCRATCH_BYTES the call returns VQG_ERR_TOO_LARGE;
+ *   - the first call on each device looks up the device address of the array (the device must be
+ *     current); make that first call before any stream capture on that device;
+ *   - all calls on a device share the one array and it keeps the previous call's contents (the
+ *     call re-zeroes the counters it needs on `stream`): two calls that overlap on the GPU -- on
+ *     different streams, or from different threads -- race.  Serialise them. */
+#define VQG_NOALLOC_SCRATCH_BYTES (4u << 20)
+VQG_API int vqg_gemm_small_batch_noalloc(const void* x, const void* idx, const void* codebook, void* y,
+                                 int M, int N, int K, int v, int C, int idx_bytes,
+                                 int rows_per_codebook, void* stream);
 
 /* Reads and clears the device-side status word of the current device: 0 if no bounded wait has
  * run out since the last call, else a code naming the wait.  Synchronises the device. */

@@ -39,11 +39,11 @@ def test_no_torch_or_python_dependency():
 
 def test_status_strings(lib):
     seen = set()
-    for code in range(7):
+    for code in range(8):
         s = _lib.status_string(code)
         assert s and s != "unknown status"
         seen.add(s)
-    assert len(seen) == 7
+    assert len(seen) == 8
     assert _lib.status_string(99) == "unknown status"
     assert lib.vqg_version() >= 100
 

@@ -11,7 +11,7 @@ from ctypes import c_char_p, c_int, c_size_t, c_ulonglong, c_void_p, POINTER
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libvqg_b200.so")
 
-OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_LAUNCH, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE = range(7)
+OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_LAUNCH, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE = range(8)
 LAYOUT_BL, LAYOUT_REF = 0, 1
 PATH_AUTO, PATH_GENERIC, PATH_DECODE, PATH_TENSOR, PATH_TWO_PHASE = range(5)
 PATHS = {"auto": PATH_AUTO, "generic": PATH_GENERIC, "decode": PATH_DECODE, "tensor": PATH_TENSOR,
@@ -30,6 +30,7 @@ SIGNATURES = {
     "vqg_dense_workspace_bytes": (c_size_t, [c_int] * 4),
     "vqg_gemm_sharded": (c_int, [c_void_p] * 3 + [POINTER(c_void_p), c_int, c_int] + [c_int] * 7
                          + [c_void_p, c_size_t, c_void_p]),
+    "vqg_gemm_small_batch_noalloc": (c_int, [c_void_p] * 4 + [c_int] * 7 + [c_void_p]),
     "vqg_device_status": (c_int, [POINTER(c_int)]),
     "vqg_launch_count": (c_ulonglong, []),
 }

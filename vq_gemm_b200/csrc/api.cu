@@ -140,6 +140,7 @@ const char* vqg_status_string(int status) {
     case VQG_ERR_LAUNCH: return "CUDA runtime or driver call failed";
     case VQG_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
     case VQG_ERR_NO_DEVICE: return "no usable CUDA device";
+    case VQG_ERR_TOO_LARGE: return "problem needs more scratch than the library's built-in static buffer holds";
     default: return "unknown status";
   }
 }
@@ -233,6 +234,16 @@ int vqg_gemm_sharded(const void* x, const void* idx, const void* codebook, void*
   for (int r = 0; r < nranks; ++r)
     if (r != rank) p.peer_y[p.n_peers++] = static_cast<__half*>(y_peers[r]) + col0;
   return run(p, VQG_LAYOUT_BL, VQG_PATH_AUTO, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int vqg_gemm_small_batch_noalloc(const void* x, const void* idx, const void* codebook, void* y, int M, int N, int K,
+                                 int v, int C, int idx_bytes, int rows_per_codebook, void* stream) {
+  const int st = check_common(x, idx, codebook, y, M, N, K, v, C, idx_bytes, VQG_LAYOUT_BL);
+  if (st != VQG_OK) return st;
+  if (M == 0 || N == 0) return VQG_OK;
+  if (M > 16) return VQG_ERR_UNSUPPORTED;
+  Problem p = make_problem(x, idx, codebook, y, M, N, K, v, C, idx_bytes, rows_per_codebook, N);
+  return launch_decode_static(p, static_cast<cudaStream_t>(stream));
 }
 
 int vqg_device_status(int* code_out) {

@@ -52,6 +52,7 @@ int launch_generic(const Problem& p, int layout, cudaStream_t s);
 bool decode_supported(const Problem& p);
 size_t decode_workspace_bytes(const Problem& p);
 int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s);
+int launch_decode_static(const Problem& p, cudaStream_t s);  // scratch in a static device array
 
 bool tensor_supported(const Problem& p);
 int launch_tensor(const Problem& p, cudaStream_t s);

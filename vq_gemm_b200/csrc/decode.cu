@@ -21,6 +21,8 @@
 //
 // There is no reference counterpart: the reference requires M % 128 == 0
 // (strategy_1/src.cu:221).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace vqg {
@@ -386,6 +388,79 @@ int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s) {
   if (!k) return VQG_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return VQG_ERR_LAUNCH;
+  k<<<grid, kThreads, smem, s>>>(d);
+  count_launch();
+  return cuda_status(cudaGetLastError());
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant: the split-K scratch (arrival counters + fp32 partial sums) lives in a
+// fixed array inside the library image instead of a caller-provided workspace.  Every GPU that
+// loads the library carries these kStaticScratchBytes until the process exits.
+//
+// `g_static_scratch` below is a device symbol: in host code its name is only a stand-in and must
+// not be handed to a kernel.  The device address is looked up once per device with
+// cudaGetSymbolAddress (with that device current) and that pointer is what the kernel receives.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr size_t kStaticScratchBytes = static_cast<size_t>(VQG_NOALLOC_SCRATCH_BYTES);
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+std::mutex g_static_mu;
+unsigned char* g_static_ptr[64] = {};
+
+// Device address of the static scratch on the current device; looked up on the first call per device.
+int static_scratch_ptr(unsigned char** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return VQG_ERR_NO_DEVICE;
+  if (dev < 0 || dev >= 64) return VQG_ERR_NO_DEVICE;
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    unsigned char* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) return VQG_ERR_LAUNCH;
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return VQG_OK;
+}
+}  // namespace
+
+int launch_decode_static(const Problem& p, cudaStream_t s) {
+  DecodeParams d{};
+  size_t smem;
+  if (!fill_params(p, d, smem)) return VQG_ERR_UNSUPPORTED;
+  const size_t need = d.nchunks > 1 ? kCounterBytes + static_cast<size_t>(d.nchunks) * p.M * p.N * sizeof(float) : 0;
+  if (need > kStaticScratchBytes) return VQG_ERR_TOO_LARGE;
+  if (static_cast<size_t>(d.nrbg) * sizeof(int) > kCounterBytes) return VQG_ERR_TOO_LARGE;
+  unsigned char* scratch = nullptr;
+  const int st = static_scratch_ptr(&scratch);
+  if (st != VQG_OK) return st;
+  if (d.nchunks > 1) {
+    // the array keeps whatever the previous call left: the arrival counters must start at zero
+    if (cudaMemsetAsync(scratch, 0, static_cast<size_t>(d.nrbg) * sizeof(int), s) != cudaSuccess) return VQG_ERR_LAUNCH;
+    d.ws_counter = reinterpret_cast<int*>(scratch);
+    d.ws_partial = reinterpret_cast<float*>(scratch + kCounterBytes);
+  }
+  d.status = nullptr;
+
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long items = static_cast<long long>(d.nchunks) * d.nrbg;
+  const int grid = static_cast<int>(items < sms ? items : sms);
+  const int MB = p.M <= 8 ? 1 : 2;
+  using KernelT = void (*)(const DecodeParams);
+  KernelT k = nullptr;
+#define VQG_PICK(V_, IB_)                                                   \
+  if (p.v == V_ && p.idx_bytes == IB_)                                      \
+    k = (MB == 1) ? vq_decode_kernel<V_, IB_, 1> : vq_decode_kernel<V_, IB_, 2>;
+  VQG_PICK(4, 1) VQG_PICK(8, 1) VQG_PICK(4, 2) VQG_PICK(8, 2)
+#undef VQG_PICK
+  if (!k) return VQG_ERR_UNSUPPORTED;
+  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+    return VQG_ERR_LAUNCH;
   k<<<grid, kThreads, smem, s>>>(d);
   count_launch();
   return cuda_status(cudaGetLastError());

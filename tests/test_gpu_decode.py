@@ -22,7 +22,9 @@ pytestmark = pytest.mark.gpu
     (2, 4096 + 256, 32, 4, 256, 0, torch.uint8),    # second chunk holds a single slice
     (4, 1024, 64, 4, 100, 0, torch.uint8),          # C not a power of two
     (1, 768, 80, 4, 256, 0, torch.uint8),           # 3 slices: warps left idle
-    (7, 1024, 64, 4, 300, 32, torch.int16),         # v = 4 with uint16 indices
+    (7, 1024, 64, 8, 300, 32, torch.int16),         # small codebook behind uint16 indices
+    (4, 2048, 128, 4, 256, 128, torch.uint8),       # largest batch of the two-columns-per-row form
+    (12, 1024, 96, 8, 256, 32, torch.uint8),        # batch rows above 8 with v = 8
 ])
 def test_decode_matches_oracle(M, K, N, v, C, rpc, dt):
     x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=M * 131 + N, idx_dtype=dt, cb_sigma=0.05)
@@ -35,6 +37,13 @@ def test_decode_is_what_auto_picks_for_small_m():
     a = run_bl(V, x, idx, cb, 128, path="auto")
     d = run_bl(V, x, idx, cb, 128, path="decode")
     assert torch.equal(bits(a), bits(d))
+
+
+def test_uint16_indices_with_v4_go_to_the_generic_kernel():
+    x, idx, cb = O.make_bl_inputs(3, 512, 64, 4, 300, 0, seed=2, idx_dtype=torch.int16, cb_sigma=0.05)
+    with pytest.raises(RuntimeError, match="unsupported"):
+        V.vq_gemm(x.cuda(), idx.cuda(), cb.cuda(), layout="bl", path="decode")
+    assert_within_tolerance(run_bl(V, x, idx, cb, 0, path="auto"), O.vq_gemm_bl(x, idx, cb, 0))
 
 
 def test_decode_rejects_unsupported_shapes():

@@ -4,20 +4,27 @@
 // and costs one shared-memory codebook lookup.  The kernel is persistent (one 512-thread CTA per
 // SM) and works on items of 16 output rows x up to 4096 K values:
 //
-//   * indices are streamed with 64-/128-bit loads straight into registers, two items ahead
-//     of use (register ring), so ~32 KiB per SM are in flight;
+//   * indices are streamed with 64-/128-bit loads straight into registers, one batch (2-3 items)
+//     ahead of use, so tens of KiB per SM are in flight;
 //   * the codebook of the item's group sits in shared memory as a REPLICATED image: entry c,
 //     replica r at byte  c*(R*2v) + r*2v , lane uses replica lane % R.  With R = 64/v
 //     (C <= 256) a warp-wide lookup touches every bank exactly once per wavefront;
-//   * a looked-up entry IS an mma.sync A fragment: with the K values of an m16n8k16 step
-//     permuted so that thread (g, t) owns 4 consecutive K values of rows g and g+8, the 8
-//     (v=4) or 16 (v=8) bytes of an entry drop into the fragment registers without any
-//     conversion or shuffle.  X is the B operand (batch padded to 8 or 16 columns) and lives
-//     in registers for the whole kernel; accumulation is fp32 in the tensor core;
+//   * looked-up entries go into mma.sync.m16n8k16 operand registers AS THEY ARRIVE -- no
+//     conversion, shuffle or register move -- and accumulation is fp32 in the tensor core.  Every
+//     thread (g, t) of a warp owns weight row n0+g and the 64 K values [64t, 64t+64) of the
+//     warp's 256-wide K slice.  Two operand arrangements:
+//       form 1 (M <= 4)  16 bytes of codebook data (one v=8 entry, or two consecutive v=4 entries)
+//         are the 4 registers of an A fragment: MMA row g sees K pairs {0-1, 4-5} of them, MMA row
+//         g+8 sees pairs {2-3, 6-7}.  X is the B operand with two columns per batch row m:
+//         column 2m carries X for the pairs of row g, column 2m+1 those of row g+8, so that
+//         y[n0+g][m] = D[g][2m] + D[g+8][2m+1].  One MMA per 16 codebook bytes.
+//       form 2 (M <= 16) a v=4 entry (or half a v=8 entry) is the 2-register B fragment of
+//         column g; X (batch rows g and g+8) is the A operand.  One MMA per 8 codebook bytes.
+//     The X fragments are loaded once and stay in registers;
 //   * each warp owns a 256-wide K slice; the 16 partial tiles of a CTA are summed in a fixed
-//     order through shared memory (deterministic), and K > 4096 adds a split-K step through a
-//     caller-provided workspace in which the last-arriving CTA of a row block sums the chunks
-//     in chunk order (also deterministic).
+//     order through shared memory (deterministic), one barrier per batch, and K > 4096 adds a
+//     split-K step through a caller-provided workspace in which the last-arriving CTA of a row
+//     block sums the chunks in chunk order (also deterministic).
 //
 // There is no reference counterpart: the reference requires M % 128 == 0
 // (strategy_1/src.cu:221).
@@ -32,8 +39,6 @@ namespace {
 constexpr int kThreads = 512;
 constexpr int kWarps = 16;
 constexpr int kSliceK = 256;     // K values per warp slice
-constexpr int kRedStride = 20;   // floats per batch column in the reduction buffer (16 rows + pad)
-constexpr int kPrefetch = 3;     // index register ring depth
 
 struct DecodeParams {
   const __half* x;
@@ -51,6 +56,12 @@ struct DecodeParams {
   int rl;              // 16-row blocks processed side by side by one CTA
   int nrbg;            // N / (16 * rl)
   int rep_log2;        // log2 of codebook replicas
+  int nslots;          // resident codebook images (1 or 2)
+  int items_q, items_r; // items per CTA: q, and one more for the first r CTAs
+  int ipg;             // items per codebook group
+  int lpo;             // lanes per output in the cross-warp reduction (power of two)
+  int lpo_log2;
+  int inv_m, inv_rl;   // ceil(65536 / M), ceil(65536 / rl): t / M == (t * inv_m) >> 16 for t < 4096
   int n_peers;
   __half* peer_y[8];
 };
@@ -63,6 +74,20 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Shared-memory loads by 32-bit address.  Not volatile, so the compiler may schedule them freely;
+// `epoch` is a fake input that changes whenever the codebook image is rebuilt, which keeps a load
+// from being moved across the barrier that publishes the new image.
+__device__ __forceinline__ uint2 lds64(uint32_t addr, uint32_t epoch) {
+  uint2 r;
+  asm("ld.shared.v2.u32 {%0,%1}, [%2];  // %3" : "=r"(r.x), "=r"(r.y) : "r"(addr), "r"(epoch));
+  return r;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr, uint32_t epoch) {
+  uint4 r;
+  asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];  // %5" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr), "r"(epoch));
+  return r;
+}
+
 template <int WORDS>
 struct IdxRegs { uint32_t w[WORDS]; };
 
@@ -72,245 +97,431 @@ __device__ __forceinline__ void load_idx(IdxRegs<WORDS>& r, const void* p) {
     uint2 t = __ldcs(reinterpret_cast<const uint2*>(p));
     r.w[0] = t.x; r.w[1] = t.y;
   } else {
-#pragma unroll
-    for (int i = 0; i < WORDS / 4; ++i) {
-      uint4 t = __ldcs(reinterpret_cast<const uint4*>(p) + i);
-      r.w[4 * i] = t.x; r.w[4 * i + 1] = t.y; r.w[4 * i + 2] = t.z; r.w[4 * i + 3] = t.w;
-    }
+    uint4 t = __ldcs(reinterpret_cast<const uint4*>(p));
+    r.w[0] = t.x; r.w[1] = t.y; r.w[2] = t.z; r.w[3] = t.w;
   }
 }
 
-// V: sub-vector length (4 or 8); IB: index bytes (1 or 2); MB: batch tiles of 8 (1 or 2).
-template <int V, int IB, int MB>
+template <int IB>
+__device__ __forceinline__ uint32_t idx_at(const uint32_t* w, int i) {
+  if constexpr (IB == 1) return __byte_perm(w[i >> 2], 0, 0x4440 + (i & 3));
+  else return __byte_perm(w[i >> 1], 0, (i & 1) ? 0x4432 : 0x4410);
+}
+
+// V: sub-vector length (4 or 8); IB: index bytes (1 or 2; 2 only with V = 8);
+// FORM: 1 (M <= 4), 2 (M <= 8), 3 (M <= 16; form 2 with batch rows g+8 live);
+// REPL: codebook image replicated to fill 128-byte lines (conflict-free) or stored once.
+//
+// Items are processed in batches of up to PFB consecutive items of one K chunk.  While a batch is
+// being computed the index loads of the next batch are in flight; a batch ends with ONE block-wide
+// barrier and a parallel, fixed-order reduction of the 16 warps' partial tiles.  Up to two codebook
+// images (groups of even / odd number) are resident, so a batch may straddle a group boundary.
+//
+// Shared memory:  [image slot 0][image slot 1 (if it fits)][ X staging | reduction buffers ]
+template <int V, int IB, int FORM, bool REPL>
 __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodeParams p) {
-  constexpr int IPT = 64 / V;              // indices per thread per row per item
-  constexpr int WORDS = IPT * IB / 4;      // 32-bit words of indices per row
+  constexpr int UB = (IB == 1 && V == 8) ? 8 : 16;  // index bytes per thread and 8-row unit (= 64 K values)
+  constexpr int WORDS = UB / 4;
+  constexpr int NIDX = UB / IB;                      // indices per thread and unit
   constexpr int ENTRY_LOG2 = (V == 4) ? 3 : 4;
-  constexpr int STEPS = 16;                // mma k-steps per item ( = IPT * V / 4 )
-  constexpr int NB = 8 * MB;               // padded batch
+  constexpr int REP_LOG2 = REPL ? (7 - ENTRY_LOG2) : 0;  // replicas fill a 128-byte line, or none at all
+  constexpr int ENTRY_SHIFT = ENTRY_LOG2 + REP_LOG2;
+  constexpr int PFB = (FORM == 1) ? 6 : (FORM == 2 ? 3 : 2);  // items per batch
+  constexpr int XR = (FORM == 1) ? 16 : (FORM == 2 ? 32 : 64);  // X fragment registers per thread
+  constexpr int XSLOT = XR + 4;                      // staging words per thread (16-byte aligned, bank-spread)
+  static_assert(NIDX * V == 64, "a thread-unit spans 64 K values");
   extern __shared__ __align__(16) unsigned char smem[];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
   const int J = p.K / V;
 
-  const size_t img_bytes = (static_cast<size_t>(p.C) << (ENTRY_LOG2 + p.rep_log2));
-  unsigned char* img = smem;
-  float* red = reinterpret_cast<float*>(smem + img_bytes);  // [2][kWarps][NB][kRedStride]
-  __shared__ int s_last;
+  const uint32_t img_bytes = static_cast<uint32_t>(p.C) << ENTRY_SHIFT;
+  unsigned char* work = smem + static_cast<size_t>(p.nslots) * img_bytes;   // staging, then reduction buffers
+  float* red = reinterpret_cast<float*>(work);                              // [2][kWarps][warp_stride]
+  uint32_t* stage = reinterpret_cast<uint32_t*>(work);                      // [kWarps][32][XSLOT]
+  const int unit_floats = p.M * 8;                           // [m][8 rows]
+  const int warp_stride = PFB * 2 * unit_floats + 2;         // +2: slices land in different banks, 8-byte aligned
+  __shared__ int s_last[PFB];
 
-  const uint32_t img_base = smem_u32(img) + ((lane & ((1 << p.rep_log2) - 1)) << ENTRY_LOG2);
-  const int entry_shift = ENTRY_LOG2 + p.rep_log2;
+  // this lane's replica inside an image (32-bit shared address of slot 0)
+  const uint32_t img_lane = smem_u32(smem) + ((lane & ((1 << REP_LOG2) - 1)) << ENTRY_LOG2);
+  uint32_t epoch = 0;
 
-  // static contiguous partition of the items, chunk-major so X stays in registers
-  const long long items_total = static_cast<long long>(p.nchunks) * p.nrbg;
-  const int it_begin = static_cast<int>(items_total * blockIdx.x / gridDim.x);
-  const int it_end = static_cast<int>(items_total * (blockIdx.x + 1) / gridDim.x);
-  const int n_items = it_end - it_begin;
-  if (n_items <= 0) return;
+  // static contiguous partition of the items (chunk-major so X stays in registers); the host supplies
+  // quotient and remainder so that no 64-bit division runs on the device
+  const int bid = blockIdx.x;
+  const int it_begin = bid * p.items_q + min(bid, p.items_r);
+  const int it_end = it_begin + p.items_q + (bid < p.items_r ? 1 : 0);
+  if (it_end <= it_begin) return;
 
   // warp role inside a chunk: (slice, row lane)
   const int nsl_full = min(kWarps, p.nslices);
-  const int wsl = warp % nsl_full;   // slice of this warp inside the chunk
-  const int wrl = warp / nsl_full;   // row lane of this warp
+  const int wsl = warp % nsl_full;
+  const int wrl = warp / nsl_full;
   const bool role_ok = wrl < p.rl;
+  const unsigned char* idx_lane = static_cast<const unsigned char*>(p.idx) +
+      (static_cast<size_t>(wrl * 16 + g) * J + static_cast<size_t>(t4) * NIDX) * IB;
+  const size_t row8_bytes = static_cast<size_t>(8) * J * IB;
+  const size_t item_bytes = static_cast<size_t>(p.rl) * 16 * J * IB;   // rows of one item
 
-  uint32_t xf[MB][STEPS][2];
-  int cur_chunk = -1, cur_group = -1;
-  bool active = false;               // this warp has a slice in the current chunk
+  uint32_t xf[XR];
+  int loaded_chunk = -1;
+  int slot_group0 = -1, slot_group1 = -1;   // which group each image slot holds
+  bool active = false;
 
-  IdxRegs<WORDS> ring[kPrefetch][2];
-
-  auto item_coords = [&](int it, int& chunk, int& rbg) {
-    chunk = it / p.nrbg;
-    rbg = it - chunk * p.nrbg;
+  struct Batch { int cnt, chunk, rbg, gpos, group; };  // group/gpos: codebook group of the first item, position in it
+  auto make_batch = [&](int it, int chunk, int rbg, int gpos, int group) {
+    Batch b;
+    b.chunk = chunk; b.rbg = rbg; b.gpos = gpos; b.group = group;
+    int c = it_end - it;
+    c = min(c, PFB);
+    c = min(c, p.nrbg - rbg);
+    c = min(c, p.nslots * p.ipg - gpos);   // a batch touches at most `nslots` consecutive groups
+    b.cnt = c > 0 ? c : 0;
+    return b;
   };
-  auto issue_loads = [&](int it, IdxRegs<WORDS> (&dst)[2]) {
-    int chunk, rbg;
-    item_coords(it, chunk, rbg);
-    const int slice = chunk * kWarps + wsl;
+
+  IdxRegs<WORDS> cur[PFB][2];
+  auto issue_loads = [&](const Batch& b, IdxRegs<WORDS> (&dst)[PFB][2]) {
+    const int slice = b.chunk * kWarps + wsl;
     if (role_ok && slice < p.nslices) {
-      const int row = (rbg * p.rl + wrl) * 16 + g;
-      const size_t off = (static_cast<size_t>(row) * J + static_cast<size_t>(slice) * (kSliceK / V) + t4 * IPT) * IB;
-      const unsigned char* base = static_cast<const unsigned char*>(p.idx);
-      load_idx<WORDS>(dst[0], base + off);
-      load_idx<WORDS>(dst[1], base + off + static_cast<size_t>(8) * J * IB);
+      const unsigned char* base = idx_lane + static_cast<size_t>(slice) * (kSliceK / V) * IB +
+                                  static_cast<size_t>(b.rbg) * item_bytes;
+#pragma unroll
+      for (int s = 0; s < PFB; ++s) {
+        if (s < b.cnt) {
+          load_idx<WORDS>(dst[s][0], base + s * item_bytes);
+          load_idx<WORDS>(dst[s][1], base + s * item_bytes + row8_bytes);
+        }
+      }
     }
   };
 
+  // Builds the image of `group` in slot `slot` (no barriers inside).
+  auto build_image = [&](int group, int slot) {
+    unsigned char* img = smem + static_cast<size_t>(slot) * img_bytes;
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.cb) +
+                               (static_cast<size_t>(group) * p.C << ENTRY_LOG2);
+    if constexpr (V == 4 && REPL) {   // one 16-byte store = two replicas of an 8-byte entry
+      const int units = p.C << (REP_LOG2 - 1);
+      for (int u0 = 0; u0 < units; u0 += 4 * kThreads) {
+        uint2 e[4];
 #pragma unroll
-  for (int s = 0; s < kPrefetch - 1; ++s)
-    if (s < n_items) issue_loads(it_begin + s, ring[s]);
+        for (int j = 0; j < 4; ++j) {
+          const int u = u0 + j * kThreads + tid;
+          if (u < units) e[j] = __ldg(reinterpret_cast<const uint2*>(src) + (u >> (REP_LOG2 - 1)));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int u = u0 + j * kThreads + tid;
+          if (u < units) reinterpret_cast<uint4*>(img)[u] = make_uint4(e[j].x, e[j].y, e[j].x, e[j].y);
+        }
+      }
+    } else if constexpr (V == 4) {
+      for (int u = tid; u < p.C; u += kThreads)
+        reinterpret_cast<uint2*>(img)[u] = __ldg(reinterpret_cast<const uint2*>(src) + u);
+    } else {
+      const int units = p.C << REP_LOG2;
+      for (int u0 = 0; u0 < units; u0 += 4 * kThreads) {
+        uint4 e[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int u = u0 + j * kThreads + tid;
+          if (u < units) e[j] = __ldg(reinterpret_cast<const uint4*>(src) + (u >> REP_LOG2));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int u = u0 + j * kThreads + tid;
+          if (u < units) reinterpret_cast<uint4*>(img)[u] = e[j];
+        }
+      }
+    }
+  };
 
-  for (int it0 = 0; it0 < n_items; it0 += kPrefetch) {
+  // Loads the chunk's X (M rows x up to 4096 K values) with coalesced 16-byte loads and scatters every
+  // piece into the staging slot of the thread(s) that own it, already in fragment-register order; then
+  // each thread reads its XR registers back with 16-byte loads.  Two barriers; the staging area is
+  // the same memory as the reduction buffers.
+  auto load_x_fragments = [&](int chunk) {
+    const int nsl = min(kWarps, p.nslices - chunk * kWarps);
+    const int kc8 = nsl * (kSliceK / 8);                       // 16-byte pieces per batch row
+    const __half* xbase = p.x + static_cast<size_t>(chunk) * kWarps * kSliceK;
+    __syncthreads();                                           // reduction buffers are no longer read
+    // rows in groups of four (four independent loads in flight per thread), pieces strided over the CTA
+#pragma unroll 1
+    for (int m0 = 0; m0 < p.M; m0 += 4) {
+#pragma unroll 1
+      for (int kg = tid; kg < kc8; kg += kThreads) {
+        uint4 v[4];
 #pragma unroll
-    for (int s = 0; s < kPrefetch; ++s) {
-      const int li = it0 + s;
-      if (li >= n_items) break;
-      const int it = it_begin + li;
-      if (li + kPrefetch - 1 < n_items) issue_loads(it + kPrefetch - 1, ring[(s + kPrefetch - 1) % kPrefetch]);
-
-      int chunk, rbg;
-      item_coords(it, chunk, rbg);
-      const int group = (rbg * p.rl * 16) / p.rows_per_cb;
-
-      if (chunk != cur_chunk) {  // (re)load this warp's X fragments: 64 consecutive K values per batch row
-        cur_chunk = chunk;
-        const int slice = chunk * kWarps + wsl;
-        active = role_ok && slice < p.nslices;
-        if (active) {
+        for (int j = 0; j < 4; ++j)
+          if (m0 + j < p.M) v[j] = __ldg(reinterpret_cast<const uint4*>(xbase + static_cast<size_t>(m0 + j) * p.K) + kg);
+        const int slice = kg >> 5, tt = (kg >> 3) & 3, i2 = kg & 7;   // owner warp slice, t4, position
 #pragma unroll
-          for (int mb = 0; mb < MB; ++mb) {
-            const int m = mb * 8 + g;
-            const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m) * p.K + slice * kSliceK + t4 * 64);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              uint4 vv = make_uint4(0, 0, 0, 0);
-              if (m < p.M) vv = __ldg(src + q);
-              xf[mb][2 * q][0] = vv.x; xf[mb][2 * q][1] = vv.y;
-              xf[mb][2 * q + 1][0] = vv.z; xf[mb][2 * q + 1][1] = vv.w;
+        for (int j = 0; j < 4; ++j) {
+          const int m = m0 + j;
+          if (m >= p.M) continue;
+          // all row lanes of a slice need the same X
+#pragma unroll 1
+          for (int lr = 0; lr < p.rl; ++lr) {
+            uint32_t* wbase = stage + static_cast<size_t>(lr * nsl_full + slice) * 32 * XSLOT;
+            if constexpr (FORM == 1) {
+              // lanes g = 2m (pairs 0, 2 of the 8-group) and g = 2m + 1 (pairs 1, 3)
+              uint32_t* d0 = wbase + ((2 * m) * 4 + tt) * XSLOT + 2 * i2;
+              uint32_t* d1 = wbase + ((2 * m + 1) * 4 + tt) * XSLOT + 2 * i2;
+              *reinterpret_cast<uint2*>(d0) = make_uint2(v[j].x, v[j].z);
+              *reinterpret_cast<uint2*>(d1) = make_uint2(v[j].y, v[j].w);
+            } else if constexpr (FORM == 2) {
+              // lane g = m: groups 2*i2, 2*i2+1 -> registers 4*i2 .. 4*i2+3 in order
+              *reinterpret_cast<uint4*>(wbase + (m * 4 + tt) * XSLOT + 4 * i2) = v[j];
+            } else {
+              // lane g = m & 7, upper row selects registers +1: group i -> regs 4i+u (pair 0), 4i+2+u (pair 1)
+              uint32_t* d = wbase + ((m & 7) * 4 + tt) * XSLOT + 8 * i2 + (m >> 3);
+              d[0] = v[j].x; d[2] = v[j].y; d[4] = v[j].z; d[6] = v[j].w;
             }
           }
         }
       }
-      if (group != cur_group) {  // rebuild the replicated codebook image
-        __syncthreads();         // everyone is done looking up in the old image
-        cur_group = group;
-        const int reps = 1 << p.rep_log2;
-        const unsigned char* src = reinterpret_cast<const unsigned char*>(p.cb) +
-                                   (static_cast<size_t>(group) * p.C << ENTRY_LOG2);
-        if constexpr (V == 4) {
-          if (reps >= 2) {       // one 16-byte store = two replicas of an 8-byte entry
-            const int units = (p.C * reps) >> 1;
-            for (int u = tid; u < units; u += kThreads) {
-              const int c = u / (reps >> 1);
-              const uint2 e = __ldg(reinterpret_cast<const uint2*>(src) + c);
-              reinterpret_cast<uint4*>(img)[u] = make_uint4(e.x, e.y, e.x, e.y);
-            }
-          } else {
-            for (int u = tid; u < p.C; u += kThreads)
-              reinterpret_cast<uint2*>(img)[u] = __ldg(reinterpret_cast<const uint2*>(src) + u);
-          }
-        } else {
-          const int units = p.C * reps;
-          for (int u = tid; u < units; u += kThreads)
-            reinterpret_cast<uint4*>(img)[u] = __ldg(reinterpret_cast<const uint4*>(src) + (u >> p.rep_log2));
+    }
+    __syncthreads();
+    const uint4* mine4 = reinterpret_cast<const uint4*>(stage + static_cast<size_t>(warp * 32 + lane) * XSLOT);
+    const bool live = (FORM == 1) ? ((g >> 1) < p.M) : (g < p.M);
+#pragma unroll
+    for (int j = 0; j < XR / 4; ++j) {
+      uint4 t = make_uint4(0, 0, 0, 0);
+      if (live && role_ok && wsl < nsl) t = mine4[j];
+      xf[4 * j] = t.x; xf[4 * j + 1] = t.y; xf[4 * j + 2] = t.z; xf[4 * j + 3] = t.w;
+    }
+    if constexpr (FORM == 3) {
+      if (g + 8 >= p.M) {   // upper batch row absent: its registers were never written
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { xf[4 * i + 1] = 0; xf[4 * i + 3] = 0; }
+      }
+    }
+    __syncthreads();                                           // staging is free to become reduction buffers
+  };
+
+  int it = it_begin;
+  Batch nb;
+  {
+    int chunk0 = 0, rbg0 = it;
+    while (rbg0 >= p.nrbg) { rbg0 -= p.nrbg; ++chunk0; }
+    const int group0 = rbg0 / p.ipg;
+    nb = make_batch(it, chunk0, rbg0, rbg0 - group0 * p.ipg, group0);
+  }
+  int parity = 0;
+  bool first_batch = true;
+
+  while (nb.cnt > 0) {
+    const Batch b = nb;
+    // all index loads of the batch go out first; everything up to the first lookup overlaps them
+    issue_loads(b, cur);
+    it += b.cnt;
+    {
+      int rbg = b.rbg + b.cnt, chunk = b.chunk, gpos = b.gpos + b.cnt, group = b.group;
+      while (gpos >= p.ipg) { gpos -= p.ipg; ++group; }
+      if (rbg >= p.nrbg) { rbg = 0; gpos = 0; group = 0; ++chunk; }
+      nb = make_batch(it, chunk, rbg, gpos, group);
+    }
+
+    if (b.chunk != loaded_chunk) {
+      loaded_chunk = b.chunk;
+      active = role_ok && (b.chunk * kWarps + wsl) < p.nslices;
+      if constexpr (FORM == 1) {
+        // B fragment of column g = (batch row g/2, pair selector g%2): for each group q of 8 K values,
+        // register 0 = pair {0-1} or {2-3}, register 1 = pair {4-5} or {6-7}.  16 scattered 4-byte loads
+        // per thread are cheap enough here (M <= 4) and need no barrier.
+        const int m = g >> 1, h = g & 1;
+        const int kt = (b.chunk * kWarps + wsl) * kSliceK + t4 * 64;
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.x + static_cast<size_t>(m) * p.K + kt) + h;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          uint32_t v0 = 0, v1 = 0;
+          if (active && m < p.M) { v0 = __ldg(src + 4 * q); v1 = __ldg(src + 4 * q + 2); }
+          xf[2 * q] = v0; xf[2 * q + 1] = v1;
         }
+      } else {
+        load_x_fragments(b.chunk);
+      }
+    }
+    const int g_first = b.group;
+    const int g_last = b.group + ((b.gpos + b.cnt - 1 >= p.ipg) ? 1 : 0);   // a batch touches at most two groups
+    {
+      const bool need0 = (p.nslots == 1) ? (slot_group0 != g_first)
+                                         : ((((g_first & 1) == 0) && slot_group0 != g_first) ||
+                                            (((g_last & 1) == 0) && slot_group0 != g_last));
+      const bool need1 = (p.nslots == 2) && ((((g_first & 1) == 1) && slot_group1 != g_first) ||
+                                             (((g_last & 1) == 1) && slot_group1 != g_last));
+      if (need0 || need1) {
+        if (!first_batch) __syncthreads();   // everyone is done looking up in the old images
+        if (need0) { slot_group0 = (p.nslots == 1 || (g_first & 1) == 0) ? g_first : g_last; build_image(slot_group0, 0); }
+        if (need1) { slot_group1 = ((g_first & 1) == 1) ? g_first : g_last; build_image(slot_group1, 1); }
         __syncthreads();
+        asm volatile("add.u32 %0, %0, 1;" : "+r"(epoch));
       }
+    }
 
-      float acc[MB][4];
+    first_batch = false;
+    float* rb = red + static_cast<size_t>(parity) * (kWarps * warp_stride);
+    parity ^= 1;
+    float* mine = rb + warp * warp_stride;
 #pragma unroll
-      for (int mb = 0; mb < MB; ++mb) { acc[mb][0] = acc[mb][1] = acc[mb][2] = acc[mb][3] = 0.f; }
-
-      if (active) {
-        const IdxRegs<WORDS>& r0 = ring[s][0];
-        const IdxRegs<WORDS>& r1 = ring[s][1];
+    for (int s = 0; s < PFB; ++s) {
+      if (s < b.cnt) {
+        // image of this item's group
+        const int grp = b.group + ((b.gpos + s >= p.ipg) ? 1 : 0);
+        const uint32_t img_s = img_lane + ((p.nslots == 2 && (grp & 1)) ? img_bytes : 0u);
 #pragma unroll
-        for (int i = 0; i < IPT; ++i) {
-          uint32_t c0, c1;
-          if constexpr (IB == 1) {
-            c0 = (r0.w[i >> 2] >> (8 * (i & 3))) & 0xffu;
-            c1 = (r1.w[i >> 2] >> (8 * (i & 3))) & 0xffu;
-          } else {
-            c0 = (r0.w[i >> 1] >> (16 * (i & 1))) & 0xffffu;
-            c1 = (r1.w[i >> 1] >> (16 * (i & 1))) & 0xffffu;
-          }
-          const uint32_t a_lo = img_base + (c0 << entry_shift);
-          const uint32_t a_hi = img_base + (c1 << entry_shift);
-          if constexpr (V == 4) {
-            uint32_t e0x, e0y, e1x, e1y;
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(e0x), "=r"(e0y) : "r"(a_lo));
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(e1x), "=r"(e1y) : "r"(a_hi));
+        for (int u = 0; u < 2; ++u) {
+          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+          float acc2[4] = {0.f, 0.f, 0.f, 0.f};  // second, independent accumulation chain
+          if (active) {
+            const uint32_t* w = cur[s][u].w;
+            if constexpr (FORM == 1) {
+              if constexpr (V == 4) {
+                uint2 e[16];
 #pragma unroll
-            for (int mb = 0; mb < MB; ++mb) mma_16816(acc[mb], e0x, e1x, e0y, e1y, xf[mb][i][0], xf[mb][i][1]);
-          } else {
-            uint32_t e0[4], e1[4];
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(e0[0]), "=r"(e0[1]), "=r"(e0[2]), "=r"(e0[3]) : "r"(a_lo));
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(e1[0]), "=r"(e1[1]), "=r"(e1[2]), "=r"(e1[3]) : "r"(a_hi));
+                for (int i = 0; i < 16; ++i) e[i] = lds64(img_s + (idx_at<IB>(w, i) << ENTRY_SHIFT), epoch);
 #pragma unroll
-            for (int mb = 0; mb < MB; ++mb) {
-              mma_16816(acc[mb], e0[0], e1[0], e0[1], e1[1], xf[mb][2 * i][0], xf[mb][2 * i][1]);
-              mma_16816(acc[mb], e0[2], e1[2], e0[3], e1[3], xf[mb][2 * i + 1][0], xf[mb][2 * i + 1][1]);
+                for (int q = 0; q < 8; ++q)
+                  mma_16816((q & 1) ? acc2 : acc, e[2 * q].x, e[2 * q].y, e[2 * q + 1].x, e[2 * q + 1].y, xf[2 * q], xf[2 * q + 1]);
+              } else {
+                uint4 e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) e[i] = lds128(img_s + (idx_at<IB>(w, i) << ENTRY_SHIFT), epoch);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) mma_16816((q & 1) ? acc2 : acc, e[q].x, e[q].y, e[q].z, e[q].w, xf[2 * q], xf[2 * q + 1]);
+              }
+            } else {
+              constexpr int XS = (FORM == 2) ? 2 : 4;
+              if constexpr (V == 4) {
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {   // two halves of 8 lookups keep the register count down
+                  uint2 e[8];
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) e[i] = lds64(img_s + (idx_at<IB>(w, 8 * hf + i) << ENTRY_SHIFT), epoch);
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    const int ii = 8 * hf + i;
+                    if constexpr (FORM == 2) mma_16816((i & 1) ? acc2 : acc, xf[XS * ii], 0u, xf[XS * ii + 1], 0u, e[i].x, e[i].y);
+                    else mma_16816((i & 1) ? acc2 : acc, xf[XS * ii], xf[XS * ii + 1], xf[XS * ii + 2], xf[XS * ii + 3], e[i].x, e[i].y);
+                  }
+                }
+              } else {
+                uint4 e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) e[i] = lds128(img_s + (idx_at<IB>(w, i) << ENTRY_SHIFT), epoch);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  if constexpr (FORM == 2) {
+                    mma_16816(acc, xf[XS * 2 * i], 0u, xf[XS * 2 * i + 1], 0u, e[i].x, e[i].y);
+                    mma_16816(acc2, xf[XS * (2 * i + 1)], 0u, xf[XS * (2 * i + 1) + 1], 0u, e[i].z, e[i].w);
+                  } else {
+                    mma_16816(acc, xf[XS * 2 * i], xf[XS * 2 * i + 1], xf[XS * 2 * i + 2], xf[XS * 2 * i + 3], e[i].x, e[i].y);
+                    mma_16816(acc2, xf[XS * (2 * i + 1)], xf[XS * (2 * i + 1) + 1], xf[XS * (2 * i + 1) + 2],
+                              xf[XS * (2 * i + 1) + 3], e[i].z, e[i].w);
+                  }
+                }
+              }
             }
           }
-        }
-      }
-
-      // cross-warp reduction, buffer alternates per item so one barrier per item suffices
-      float* rb = red + static_cast<size_t>(li & 1) * (kWarps * NB * kRedStride);
-      {
-        float* mine = rb + warp * (NB * kRedStride);
 #pragma unroll
-        for (int mb = 0; mb < MB; ++mb) {
-          const int b0 = mb * 8 + 2 * t4;
-          mine[b0 * kRedStride + g] = acc[mb][0];
-          mine[(b0 + 1) * kRedStride + g] = acc[mb][1];
-          mine[b0 * kRedStride + g + 8] = acc[mb][2];
-          mine[(b0 + 1) * kRedStride + g + 8] = acc[mb][3];
+          for (int c = 0; c < 4; ++c) acc[c] += acc2[c];
+          // this warp's partial tile of the unit: [m][8 rows]
+          float* dst = mine + (s * 2 + u) * unit_floats;
+          if constexpr (FORM == 1) {
+            if (t4 < p.M) dst[t4 * 8 + g] = acc[0] + acc[3];
+          } else {
+            // acc = D[batch g][rows 2t, 2t+1], D[batch g+8][rows 2t, 2t+1]
+            if (g < p.M) *reinterpret_cast<float2*>(dst + g * 8 + 2 * t4) = make_float2(acc[0], acc[1]);
+            if (FORM == 3 && g + 8 < p.M) *reinterpret_cast<float2*>(dst + (g + 8) * 8 + 2 * t4) = make_float2(acc[2], acc[3]);
+          }
         }
       }
-      __syncthreads();
+    }
+    __syncthreads();
 
-      const int nsl = min(kWarps, p.nslices - chunk * kWarps);  // slices present in this chunk
-      const int outs = p.rl * p.M * 16;
-      if (p.nchunks == 1) {
-        for (int o = tid; o < outs; o += kThreads) {
-          const int r = o & 15, m = (o >> 4) % p.M, lr = (o >> 4) / p.M;
-          float sum = 0.f;
-          for (int sl = 0; sl < nsl; ++sl) sum += rb[(lr * nsl_full + sl) * (NB * kRedStride) + m * kRedStride + r];
-          const int row = (rbg * p.rl + lr) * 16 + r;
+    // fixed-order reduction over the slices of the chunk: `lpo` lanes per output, then a butterfly.
+    // Output o = ((s*rl + lr)*M + m)*16 + r; divisions by M and rl use host-made reciprocals
+    // (exact for the small ranges involved).
+    const int nsl = min(kWarps, p.nslices - b.chunk * kWarps);
+    const int outs = b.cnt * p.rl * p.M * 16;
+    const int q = tid & (p.lpo - 1);
+    const int outs_per_pass = kThreads >> p.lpo_log2;
+    const bool split = p.nchunks > 1;
+    for (int o0 = 0; o0 < outs; o0 += outs_per_pass) {
+      const int o = o0 + (tid >> p.lpo_log2);
+      float sum = 0.f;
+      int m = 0, row = 0;
+      const bool valid = o < outs;
+      if (valid) {
+        const int r = o & 15;                 // row inside the 16-row item: unit r>>3, row r&7
+        const int t = o >> 4;
+        const int t1 = (t * p.inv_m) >> 16;   // t / M
+        m = t - t1 * p.M;
+        const int s = (t1 * p.inv_rl) >> 16;  // t1 / rl
+        const int lr = t1 - s * p.rl;
+        row = ((b.rbg + s) * p.rl + lr) * 16 + r;
+        const float* src = rb + (lr * nsl_full) * warp_stride + (s * 2 + (r >> 3)) * unit_floats + m * 8 + (r & 7);
+        for (int sl = q; sl < nsl; sl += p.lpo) sum += src[sl * warp_stride];
+      }
+      for (int d = p.lpo >> 1; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+      if (valid && q == 0) {
+        if (!split) {
           const __half h = __float2half_rn(sum);
           const size_t o_off = static_cast<size_t>(m) * p.ld_y + row;
           p.y[o_off] = h;
-          for (int q = 0; q < p.n_peers; ++q) p.peer_y[q][o_off] = h;
-        }
-      } else {
-        for (int o = tid; o < outs; o += kThreads) {
-          const int r = o & 15, m = (o >> 4) % p.M, lr = (o >> 4) / p.M;
-          float sum = 0.f;
-          for (int sl = 0; sl < nsl; ++sl) sum += rb[(lr * nsl_full + sl) * (NB * kRedStride) + m * kRedStride + r];
-          const int row = (rbg * p.rl + lr) * 16 + r;
-          __stcg(p.ws_partial + (static_cast<size_t>(chunk) * p.M + m) * p.N + row, sum);
-        }
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-          const int old = atomicAdd(p.ws_counter + rbg, 1);
-          const int last = (old == p.nchunks - 1);
-          if (last) p.ws_counter[rbg] = 0;  // leave the counter zero for the next call
-          s_last = last;
-        }
-        __syncthreads();
-        if (s_last) {
-          __threadfence();
-          for (int o = tid; o < outs; o += kThreads) {
-            const int r = o & 15, m = (o >> 4) % p.M, lr = (o >> 4) / p.M;
-            const int row = (rbg * p.rl + lr) * 16 + r;
-            float sum = 0.f;
-            for (int c = 0; c < p.nchunks; ++c)
-              sum += __ldcg(p.ws_partial + (static_cast<size_t>(c) * p.M + m) * p.N + row);
-            const __half h = __float2half_rn(sum);
-            const size_t o_off = static_cast<size_t>(m) * p.ld_y + row;
-            p.y[o_off] = h;
-            for (int q = 0; q < p.n_peers; ++q) p.peer_y[q][o_off] = h;
-          }
+          for (int pq = 0; pq < p.n_peers; ++pq) p.peer_y[pq][o_off] = h;
+        } else {
+          __stcg(p.ws_partial + (static_cast<size_t>(b.chunk) * p.M + m) * p.N + row, sum);
         }
       }
+    }
+    if (split) {
+      // split-K: the CTA that brings a row block's counter to nchunks sums the chunks in chunk order
+      __threadfence();
+      __syncthreads();
+      if (tid < b.cnt) {
+        const int old = atomicAdd(p.ws_counter + b.rbg + tid, 1);
+        const int last = (old == p.nchunks - 1);
+        if (last) p.ws_counter[b.rbg + tid] = 0;  // leave the counter zero for the next call
+        s_last[tid] = last;
+      }
+      __syncthreads();
+      __threadfence();
+      for (int o = tid; o < outs; o += kThreads) {
+        const int r = o & 15;
+        const int t = o >> 4;
+        const int t1 = (t * p.inv_m) >> 16;
+        const int m = t - t1 * p.M;
+        const int s = (t1 * p.inv_rl) >> 16;
+        const int lr = t1 - s * p.rl;
+        if (!s_last[s]) continue;
+        const int row = ((b.rbg + s) * p.rl + lr) * 16 + r;
+        float sum = 0.f;
+        for (int c = 0; c < p.nchunks; ++c)
+          sum += __ldcg(p.ws_partial + (static_cast<size_t>(c) * p.M + m) * p.N + row);
+        const __half h = __float2half_rn(sum);
+        const size_t o_off = static_cast<size_t>(m) * p.ld_y + row;
+        p.y[o_off] = h;
+        for (int pq = 0; pq < p.n_peers; ++pq) p.peer_y[pq][o_off] = h;
+      }
+      __syncthreads();  // s_last is rewritten by the next batch
     }
   }
 }
 
+// Full replication (16 or 8 copies fill a 128-byte line) when the image fits the budget, else none.
 int pick_rep_log2(int v, int C, size_t budget) {
-  int rep = (v == 4) ? 4 : 3;  // 16 or 8 replicas fill a 128-byte line
-  while (rep > 0 && (static_cast<size_t>(C) * 2 * v << rep) > budget) --rep;
-  return rep;
+  const int rep = (v == 4) ? 4 : 3;
+  return (static_cast<size_t>(C) * 2 * v << rep) <= budget ? rep : 0;
 }
 
 bool fill_params(const Problem& p, DecodeParams& d, size_t& smem_bytes) {
   if (p.M < 1 || p.M > 16) return false;
   if (!(p.v == 4 || p.v == 8)) return false;
-  if (!(p.idx_bytes == 1 || p.idx_bytes == 2)) return false;
+  if (!(p.idx_bytes == 1 || (p.idx_bytes == 2 && p.v == 8))) return false;
   if (p.K % kSliceK != 0 || p.N % 16 != 0 || p.K == 0 || p.N == 0) return false;
   const bool single = p.rows_per_cb >= p.N;
   if (!single && p.rows_per_cb % 16 != 0) return false;
@@ -329,11 +540,24 @@ bool fill_params(const Problem& p, DecodeParams& d, size_t& smem_bytes) {
   while (rl > 1 && ((p.N / 16) % rl != 0 || blocks_per_group % rl != 0)) --rl;
   d.rl = rl;
   d.nrbg = p.N / (16 * rl);
-  const int MB = p.M <= 8 ? 1 : 2;
-  const size_t red_bytes = static_cast<size_t>(2) * kWarps * (8 * MB) * kRedStride * sizeof(float);
-  d.rep_log2 = pick_rep_log2(p.v, p.C, 64 * 1024 > p.C * entry ? 64 * 1024 : p.C * entry);
-  smem_bytes = (static_cast<size_t>(p.C) * entry << d.rep_log2) + red_bytes;
-  if (smem_bytes > 200 * 1024) return false;
+  const int pfb = p.M <= 4 ? 6 : (p.M <= 8 ? 3 : 2);
+  d.ipg = blocks_per_group / rl;
+  // lanes per output in the reduction: as many as keep all outputs of a batch in one pass
+  const int outs_max = pfb * rl * p.M * 16;
+  d.lpo = 1; d.lpo_log2 = 0;
+  while (d.lpo * 2 <= nsl_full && d.lpo < 8 && outs_max * d.lpo * 2 <= kThreads) { d.lpo *= 2; ++d.lpo_log2; }
+  d.inv_m = (65536 + p.M - 1) / p.M;
+  d.inv_rl = (65536 + rl - 1) / rl;
+  const size_t red_bytes = static_cast<size_t>(2) * kWarps * (pfb * 2 * p.M * 8 + 2) * sizeof(float);
+  const int xr = p.M <= 4 ? 16 : (p.M <= 8 ? 32 : 64);
+  const size_t stage_bytes = static_cast<size_t>(kWarps) * 32 * (xr + 4) * sizeof(uint32_t);
+  const size_t work_bytes = red_bytes > stage_bytes ? red_bytes : stage_bytes;
+  d.rep_log2 = pick_rep_log2(p.v, p.C, 64 * 1024);
+  const size_t img_bytes = static_cast<size_t>(p.C) * entry << d.rep_log2;
+  // a second resident image lets batches straddle a group boundary without a rebuild in between
+  d.nslots = (!single && 2 * img_bytes + work_bytes <= 210 * 1024) ? 2 : 1;
+  smem_bytes = d.nslots * img_bytes + work_bytes;
+  if (smem_bytes > 220 * 1024) return false;
   d.x = p.x; d.idx = p.idx; d.cb = p.cb; d.y = p.y;
   d.M = p.M; d.N = p.N; d.K = p.K; d.C = p.C;
   d.rows_per_cb = single ? p.N : p.rows_per_cb;
@@ -376,14 +600,22 @@ int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s) {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long items = static_cast<long long>(d.nchunks) * d.nrbg;
   const int grid = static_cast<int>(items < sms ? items : sms);
+  d.items_q = static_cast<int>(items / grid);
+  d.items_r = static_cast<int>(items % grid);
 
-  const int MB = p.M <= 8 ? 1 : 2;
+  const int form = p.M <= 4 ? 1 : (p.M <= 8 ? 2 : 3);
   using KernelT = void (*)(const DecodeParams);
   KernelT k = nullptr;
-#define VQG_PICK(V_, IB_)                                                   \
-  if (p.v == V_ && p.idx_bytes == IB_)                                      \
-    k = (MB == 1) ? vq_decode_kernel<V_, IB_, 1> : vq_decode_kernel<V_, IB_, 2>;
-  VQG_PICK(4, 1) VQG_PICK(8, 1) VQG_PICK(4, 2) VQG_PICK(8, 2)
+#define VQG_PICK(V_, IB_)                                                                                \
+  if (p.v == V_ && p.idx_bytes == IB_) {                                                                 \
+    if (d.rep_log2 > 0)                                                                                  \
+      k = form == 1 ? vq_decode_kernel<V_, IB_, 1, true>                                                 \
+                    : (form == 2 ? vq_decode_kernel<V_, IB_, 2, true> : vq_decode_kernel<V_, IB_, 3, true>); \
+    else                                                                                                 \
+      k = form == 1 ? vq_decode_kernel<V_, IB_, 1, false>                                                \
+                    : (form == 2 ? vq_decode_kernel<V_, IB_, 2, false> : vq_decode_kernel<V_, IB_, 3, false>); \
+  }
+  VQG_PICK(4, 1) VQG_PICK(8, 1) VQG_PICK(8, 2)
 #undef VQG_PICK
   if (!k) return VQG_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -450,13 +682,21 @@ int launch_decode_static(const Problem& p, cudaStream_t s) {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long items = static_cast<long long>(d.nchunks) * d.nrbg;
   const int grid = static_cast<int>(items < sms ? items : sms);
-  const int MB = p.M <= 8 ? 1 : 2;
+  d.items_q = static_cast<int>(items / grid);
+  d.items_r = static_cast<int>(items % grid);
+  const int form = p.M <= 4 ? 1 : (p.M <= 8 ? 2 : 3);
   using KernelT = void (*)(const DecodeParams);
   KernelT k = nullptr;
-#define VQG_PICK(V_, IB_)                                                   \
-  if (p.v == V_ && p.idx_bytes == IB_)                                      \
-    k = (MB == 1) ? vq_decode_kernel<V_, IB_, 1> : vq_decode_kernel<V_, IB_, 2>;
-  VQG_PICK(4, 1) VQG_PICK(8, 1) VQG_PICK(4, 2) VQG_PICK(8, 2)
+#define VQG_PICK(V_, IB_)                                                                                \
+  if (p.v == V_ && p.idx_bytes == IB_) {                                                                 \
+    if (d.rep_log2 > 0)                                                                                  \
+      k = form == 1 ? vq_decode_kernel<V_, IB_, 1, true>                                                 \
+                    : (form == 2 ? vq_decode_kernel<V_, IB_, 2, true> : vq_decode_kernel<V_, IB_, 3, true>); \
+    else                                                                                                 \
+      k = form == 1 ? vq_decode_kernel<V_, IB_, 1, false>                                                \
+                    : (form == 2 ? vq_decode_kernel<V_, IB_, 2, false> : vq_decode_kernel<V_, IB_, 3, false>); \
+  }
+  VQG_PICK(4, 1) VQG_PICK(8, 1) VQG_PICK(8, 2)
 #undef VQG_PICK
   if (!k) return VQG_ERR_UNSUPPORTED;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)

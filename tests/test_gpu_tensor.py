@@ -31,9 +31,10 @@ def test_dense_gemm(M, K, N):
     (1024, 1024, 2048, 8, 256),   # 256 rows per codebook, many tiles per CTA? (64 tiles)
     (4096, 512, 4864, 4, 128),    # more tiles than SMs: persistent loop + accumulator ping-pong
 ])
-def test_fused_matches_oracle(M, K, N, v, rpc):
+@pytest.mark.parametrize("path", ["tensor", "tensor_pair"])
+def test_fused_matches_oracle(M, K, N, v, rpc, path):
     x, idx, cb = O.make_bl_inputs(M, K, N, v, 256, rpc, seed=M + K + N + v, cb_sigma=0.05)
-    y = run_bl(V, x, idx, cb, rpc, path="tensor")
+    y = run_bl(V, x, idx, cb, rpc, path=path)
     assert_within_tolerance(y, O.vq_gemm_bl(x, idx, cb, rpc))
 
 
@@ -74,6 +75,17 @@ def test_fused_deterministic():
     for o in outs[1:]:
         assert torch.equal(bits(outs[0]), bits(o))
     assert V.device_status() == 0
+
+
+def test_pair_kernel_equals_single_cta_kernel_bitwise():
+    # same operands, same K order inside every accumulator -> same bits
+    x, idx, cb = O.make_bl_inputs(700, 1024, 1280, 4, 256, 128, seed=12)
+    a = run_bl(V, x, idx, cb, 128, path="tensor")
+    b = run_bl(V, x, idx, cb, 128, path="tensor_pair")
+    assert torch.equal(bits(a), bits(b))
+    outs = [run_bl(V, x, idx, cb, 128, path="tensor_pair") for _ in range(3)]
+    for o in outs:
+        assert torch.equal(bits(o), bits(b))
 
 
 def test_fused_equals_two_phase_bitwise():

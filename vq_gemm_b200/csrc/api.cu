@@ -82,6 +82,7 @@ int auto_path(const Problem& p, int layout) {
   }
   if (p.K == 0) return VQG_PATH_GENERIC;
   if (p.M <= 16 && decode_supported(p)) return VQG_PATH_DECODE;
+  if (p.M > 128 && tensor_pair_supported(p)) return VQG_PATH_TENSOR_PAIR;
   if (p.M > 16 && tensor_supported(p)) return VQG_PATH_TENSOR;
   if (p.M > 16 && dense_supported(p.M, p.N, p.K) && (p.v == 2 || p.v == 4 || p.v == 8)) return VQG_PATH_TWO_PHASE;
   return VQG_PATH_GENERIC;
@@ -104,6 +105,9 @@ int run(const Problem& p, int layout, int path, void* ws, size_t ws_bytes, cudaS
     case VQG_PATH_TENSOR:
       if (layout != VQG_LAYOUT_BL) return VQG_ERR_UNSUPPORTED;
       return launch_tensor(p, s);
+    case VQG_PATH_TENSOR_PAIR:
+      if (layout != VQG_LAYOUT_BL) return VQG_ERR_UNSUPPORTED;
+      return launch_tensor_pair(p, s);
     case VQG_PATH_TWO_PHASE: {
       if (!dense_supported(p.M, p.N, p.K)) return VQG_ERR_UNSUPPORTED;
       const size_t need = two_phase_bytes(p.N, p.K);
@@ -115,6 +119,7 @@ int run(const Problem& p, int layout, int path, void* ws, size_t ws_bytes, cudaS
       else
         st = launch_dequant_ref(static_cast<const uint8_t*>(p.idx), p.cb, w, p.N / 2, p.K, /*transposed=*/true, s);
       if (st != VQG_OK) return st;
+      if (p.M > 128) return launch_dense_pair(p.x, w, p.y, p.M, p.N, p.K, p.ld_y, p.n_peers, p.peer_y, s);
       return launch_dense(p.x, w, p.y, p.M, p.N, p.K, p.ld_y, p.n_peers, p.peer_y, s);
     }
     default:
@@ -216,6 +221,7 @@ int vqg_dense_gemm(const void* x, const void* w, void* y, int M, int N, int K, i
     if (st != VQG_OK) return st;
     w_nk = wt;
   }
+  if (M > 128) return launch_dense_pair(static_cast<const __half*>(x), w_nk, static_cast<__half*>(y), M, N, K, N, 0, nullptr, s);
   return launch_dense(static_cast<const __half*>(x), w_nk, static_cast<__half*>(y), M, N, K, N, 0, nullptr, s);
 }
 

@@ -36,6 +36,7 @@ enum DeviceStatus : int {
   DS_ACC_EMPTY_TIMEOUT = 5,  // MMA warp waited for the epilogue to drain TMEM
   DS_SPLITK_TIMEOUT = 6,
   DS_DEQUANT_SYNC_TIMEOUT = 7,
+  DS_PEER_READY_TIMEOUT = 8, // pair leader waited for the second CTA's operands
 };
 int* device_status_ptr();          // device address of the status word of the current device
 cudaError_t ensure_status_word();  // allocates it on first use (per device)
@@ -60,6 +61,10 @@ bool dense_supported(int M, int N, int K);
 // Y[M,N] = X[M,K] * W[N,K]^T, all fp16, fp32 accumulate (tcgen05).
 int launch_dense(const __half* x, const __half* w_nk, __half* y, int M, int N, int K, long long ld_y,
                  int n_peers, __half* const* peer_y, cudaStream_t s);
+bool tensor_pair_supported(const Problem& p);
+int launch_tensor_pair(const Problem& p, cudaStream_t s);   // CTA-pair (cta_group::2) version
+int launch_dense_pair(const __half* x, const __half* w_nk, __half* y, int M, int N, int K, long long ld_y,
+                      int n_peers, __half* const* peer_y, cudaStream_t s);
 int launch_transpose(const __half* in, __half* out, int rows, int cols, cudaStream_t s);
 
 constexpr size_t kCounterBytes = 64 * 1024;  // arrival counters at the head of a workspace

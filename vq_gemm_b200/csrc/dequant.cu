@@ -43,6 +43,62 @@ __global__ void __launch_bounds__(256) dequant_bl_kernel(const IdxT* __restrict_
   }
 }
 
+// Fast path: every thread produces 16 output bytes (8/V indices) so that a warp's stores are one
+// contiguous 512-byte run; the codebook sits in shared memory replicated to fill 128-byte lines
+// (entry c, replica r at byte c*128 + r*2V, lane uses replica lane % (64/V)), so lookups are
+// bank-conflict free.  Needs C*128 bytes of shared memory (C <= 256 here) and K/V a multiple of 8/V.
+template <int V, typename IdxT>
+__global__ void __launch_bounds__(256) dequant_bl_fast_kernel(const IdxT* __restrict__ idx,
+                                                              const __half* __restrict__ cb,
+                                                              __half* __restrict__ w, int N, int K, int C,
+                                                              int rows_per_cb, int rows_per_block) {
+  using E = typename Entry<V>::T;
+  constexpr int IPT = 8 / V;                 // indices per thread (16 output bytes)
+  constexpr int REPS = 64 / V;               // replicas per 128-byte line
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int J = K / V;
+  const int row0 = blockIdx.x * rows_per_block;
+  const int group = row0 / rows_per_cb;
+  const E* cbg = reinterpret_cast<const E*>(cb) + static_cast<size_t>(group) * C;
+  E* img = reinterpret_cast<E*>(smem_raw);
+  for (int i = threadIdx.x; i < C * REPS; i += blockDim.x) img[i] = __ldg(cbg + i / REPS);
+  __syncthreads();
+  const E* mine = img + (threadIdx.x & (REPS - 1));
+  const int rows = min(rows_per_block, N - row0);
+  const long long total = static_cast<long long>(rows) * (J / IPT);   // 16-byte outputs
+  const IdxT* ip = idx + static_cast<size_t>(row0) * J;
+  uint4* op = reinterpret_cast<uint4*>(w + static_cast<size_t>(row0) * K);
+#pragma unroll 4
+  for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+    uint4 out;
+    if constexpr (V == 8) {
+      out = *reinterpret_cast<const uint4*>(mine + static_cast<uint32_t>(ip[i]) * REPS);
+    } else if constexpr (V == 4) {
+      uint32_t c0, c1;
+      if constexpr (sizeof(IdxT) == 1) {
+        const uint16_t two = __ldg(reinterpret_cast<const uint16_t*>(ip) + i);
+        c0 = two & 0xffu; c1 = two >> 8;
+      } else {
+        const uint32_t two = __ldg(reinterpret_cast<const uint32_t*>(ip) + i);
+        c0 = two & 0xffffu; c1 = two >> 16;
+      }
+      const uint2 e0 = mine[c0 * REPS], e1 = mine[c1 * REPS];
+      out = make_uint4(e0.x, e0.y, e1.x, e1.y);
+    } else {
+      uint32_t c[4];
+      if constexpr (sizeof(IdxT) == 1) {
+        const uint32_t four = __ldg(reinterpret_cast<const uint32_t*>(ip) + i);
+        c[0] = four & 0xffu; c[1] = (four >> 8) & 0xffu; c[2] = (four >> 16) & 0xffu; c[3] = four >> 24;
+      } else {
+        const uint2 four = __ldg(reinterpret_cast<const uint2*>(ip) + i);
+        c[0] = four.x & 0xffffu; c[1] = four.x >> 16; c[2] = four.y & 0xffffu; c[3] = four.y >> 16;
+      }
+      out = make_uint4(mine[c[0] * REPS], mine[c[1] * REPS], mine[c[2] * REPS], mine[c[3] * REPS]);
+    }
+    __stcs(op + i, out);
+  }
+}
+
 int launch_dequant_bl(const void* idx, const __half* cb, __half* w, int N, int K, int v, int C,
                       int idx_bytes, int rows_per_cb, cudaStream_t s) {
   if (N == 0 || K == 0) return VQG_OK;
@@ -52,6 +108,20 @@ int launch_dequant_bl(const void* idx, const __half* cb, __half* w, int N, int K
   while (rpb >= 16 && (single || rows_per_cb % (rpb * 2) == 0) && (N / (rpb * 2)) >= 148 * 16) rpb *= 2;
   const int blocks = (N + rpb - 1) / rpb;
   const size_t cb_bytes = static_cast<size_t>(C) * v * 2;
+  // fast path: replicated image (C * 128 bytes), 16 output bytes per thread
+  if ((v == 2 || v == 4 || v == 8) && C <= 256 && (K / v) % (8 / v) == 0 && (single || rows_per_cb % 16 == 0) &&
+      reinterpret_cast<uintptr_t>(idx) % 8 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
+    int rows = 16;
+    while ((single || rows_per_cb % (rows * 2) == 0) && (N / (rows * 2)) >= 148 * 8) rows *= 2;
+    const int nblocks = (N + rows - 1) / rows;
+    const size_t sm = static_cast<size_t>(C) * 128;
+#define VQG_DQF(V_, T_) dequant_bl_fast_kernel<V_, T_><<<nblocks, 256, sm, s>>>(static_cast<const T_*>(idx), cb, w, N, K, C, rows_per_cb, rows)
+    if (idx_bytes == 1) { if (v == 2) VQG_DQF(2, uint8_t); else if (v == 4) VQG_DQF(4, uint8_t); else VQG_DQF(8, uint8_t); }
+    else { if (v == 2) VQG_DQF(2, uint16_t); else if (v == 4) VQG_DQF(4, uint16_t); else VQG_DQF(8, uint16_t); }
+#undef VQG_DQF
+    count_launch();
+    return cuda_status(cudaGetLastError());
+  }
   const bool use_smem = cb_bytes <= 96 * 1024;
   const size_t smem = use_smem ? cb_bytes : 0;
 #define VQG_DQ(V_, T_)                                                                              \

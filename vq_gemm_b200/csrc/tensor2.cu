@@ -78,7 +78,6 @@ vq_tensor_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();         // 0 = pair leader
-  const uint32_t peer = rank ^ 1u;
   const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int ksteps = p.K / BK;
   const int total_tiles = p.m_tiles * p.n_tiles;
@@ -301,6 +300,11 @@ vq_tensor_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
           if (kt >= ksteps) break;
           if (!(ok = mbar_wait_cluster(bar_empty(stage), phase ^ 1, p.status, DS_STAGE_EMPTY_TIMEOUT))) break;
           const uint32_t dst_row = b_addr(stage) + row_off;
+          // all lookups of the row first, then the stores: the loads are independent of one another, so the
+          // warp is not held up chunk by chunk waiting for shared-memory latency
+          // all lookups of the row first, then the stores: the loads are independent of one another, so the
+          // warp is not held up chunk by chunk waiting for shared-memory latency
+          uint4 ch[8];
           if (V == 4) {
 #pragma unroll
             for (int w = 0; w < WPS; ++w) {
@@ -308,13 +312,8 @@ vq_tensor_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 #pragma unroll
               for (int hh = 0; hh < 2; ++hh) {
                 const uint32_t c0 = (word >> (16 * hh)) & 0xffu, c1 = (word >> (16 * hh + 8)) & 0xffu;
-                uint32_t e0x, e0y, e1x, e1y;
-                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(e0x), "=r"(e0y) : "r"(img + (c0 << 7)));
-                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(e1x), "=r"(e1y) : "r"(img + (c1 << 7)));
-                const uint32_t chunk = static_cast<uint32_t>(2 * w + hh);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst_row + ((chunk ^ rx) << 4)), "r"(e0x),
-                             "r"(e0y), "r"(e1x), "r"(e1y)
-                             : "memory");
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(ch[2 * w + hh].x), "=r"(ch[2 * w + hh].y) : "r"(img + (c0 << 7)));
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(ch[2 * w + hh].z), "=r"(ch[2 * w + hh].w) : "r"(img + (c1 << 7)));
               }
             }
           } else {
@@ -324,15 +323,17 @@ vq_tensor_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 #pragma unroll
               for (int b = 0; b < 4; ++b) {
                 const uint32_t c0 = (word >> (8 * b)) & 0xffu;
-                uint32_t e[4];
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(e[0]), "=r"(e[1]), "=r"(e[2]), "=r"(e[3]) : "r"(img + (c0 << 7)));
-                const uint32_t chunk = static_cast<uint32_t>(4 * w + b);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst_row + ((chunk ^ rx) << 4)), "r"(e[0]),
-                             "r"(e[1]), "r"(e[2]), "r"(e[3])
-                             : "memory");
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(ch[4 * w + b].x), "=r"(ch[4 * w + b].y), "=r"(ch[4 * w + b].z), "=r"(ch[4 * w + b].w)
+                             : "r"(img + (c0 << 7)));
               }
             }
           }
+#pragma unroll
+          for (uint32_t chunk = 0; chunk < 8; ++chunk)
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst_row + ((chunk ^ rx) << 4)), "r"(ch[chunk].x),
+                         "r"(ch[chunk].y), "r"(ch[chunk].z), "r"(ch[chunk].w)
+                         : "memory");
           fence_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_b_full(stage));

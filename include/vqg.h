@@ -55,7 +55,8 @@ enum {
   VQG_PATH_DECODE = 2,   /* M <= 16: index streaming + codebook lookups + mma.sync, split-K     */
   VQG_PATH_TENSOR = 3,   /* tcgen05 / TMEM / TMA warp-specialised kernel, fused dequant, 1 CTA  */
   VQG_PATH_TWO_PHASE = 4,/* dequantise to workspace, then the dense tcgen05 kernel              */
-  VQG_PATH_TENSOR_PAIR = 5 /* the fused kernel on CTA pairs (tcgen05 cta_group::2, 256x256 tiles) */
+  VQG_PATH_TENSOR_PAIR = 5, /* the fused kernel on CTA pairs (tcgen05 cta_group::2, 256x256 tiles) */
+  VQG_PATH_TENSOR_TS = 6   /* CTA pairs, dequantised weights as the MMA's tensor-memory operand    */
 };
 
 /* Library version (major*10000 + minor*100 + patch). */

@@ -31,7 +31,7 @@ def test_dense_gemm(M, K, N):
     (1024, 1024, 2048, 8, 256),   # 256 rows per codebook, many tiles per CTA? (64 tiles)
     (4096, 512, 4864, 4, 128),    # more tiles than SMs: persistent loop + accumulator ping-pong
 ])
-@pytest.mark.parametrize("path", ["tensor", "tensor_pair"])
+@pytest.mark.parametrize("path", ["tensor", "tensor_pair", "tensor_ts"])
 def test_fused_matches_oracle(M, K, N, v, rpc, path):
     x, idx, cb = O.make_bl_inputs(M, K, N, v, 256, rpc, seed=M + K + N + v, cb_sigma=0.05)
     y = run_bl(V, x, idx, cb, rpc, path=path)
@@ -86,6 +86,18 @@ def test_pair_kernel_equals_single_cta_kernel_bitwise():
     outs = [run_bl(V, x, idx, cb, 128, path="tensor_pair") for _ in range(3)]
     for o in outs:
         assert torch.equal(bits(o), bits(b))
+
+
+def test_tensor_memory_operand_kernel_is_deterministic_and_close_to_the_others():
+    # weights as the MMA's tensor-memory operand, problem transposed inside the kernel
+    x, idx, cb = O.make_bl_inputs(700, 1024, 1280, 4, 256, 128, seed=12)
+    ref = O.vq_gemm_bl(x, idx, cb, 128)
+    outs = [run_bl(V, x, idx, cb, 128, path="tensor_ts") for _ in range(3)]
+    assert_within_tolerance(outs[0], ref)
+    for o in outs[1:]:
+        assert torch.equal(bits(o), bits(outs[0]))
+    b = run_bl(V, x, idx, cb, 128, path="tensor_pair")
+    assert float((outs[0].float() - b.float()).abs().max()) <= 2e-3 * float(ref.float().abs().max())
 
 
 def test_fused_equals_two_phase_bitwise():

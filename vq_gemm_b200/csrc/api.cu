@@ -108,6 +108,9 @@ int run(const Problem& p, int layout, int path, void* ws, size_t ws_bytes, cudaS
     case VQG_PATH_TENSOR_PAIR:
       if (layout != VQG_LAYOUT_BL) return VQG_ERR_UNSUPPORTED;
       return launch_tensor_pair(p, s);
+    case VQG_PATH_TENSOR_TS:
+      if (layout != VQG_LAYOUT_BL) return VQG_ERR_UNSUPPORTED;
+      return launch_tensor_ts(p, s);
     case VQG_PATH_TWO_PHASE: {
       if (!dense_supported(p.M, p.N, p.K)) return VQG_ERR_UNSUPPORTED;
       const size_t need = two_phase_bytes(p.N, p.K);

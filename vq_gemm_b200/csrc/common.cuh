@@ -65,6 +65,8 @@ bool tensor_pair_supported(const Problem& p);
 int launch_tensor_pair(const Problem& p, cudaStream_t s);   // CTA-pair (cta_group::2) version
 int launch_dense_pair(const __half* x, const __half* w_nk, __half* y, int M, int N, int K, long long ld_y,
                       int n_peers, __half* const* peer_y, cudaStream_t s);
+bool tensor_ts_supported(const Problem& p);
+int launch_tensor_ts(const Problem& p, cudaStream_t s);     // weights through tensor memory (A operand)
 int launch_transpose(const __half* in, __half* out, int rows, int cols, cudaStream_t s);
 
 constexpr size_t kCounterBytes = 64 * 1024;  // arrival counters at the head of a workspace

@@ -1,0 +1,458 @@
+// Compute-bound VQ-GEMM for sm_100a with the dequantised weights fed to the tensor core THROUGH TENSOR
+// MEMORY (tcgen05.mma with the A operand in TMEM), on CTA pairs (cta_group::2).
+//
+// Why: with B dequantised into shared memory (tensor.cu, tensor2.cu) every weight byte crosses the
+// shared-memory pipe three times (codebook lookup, store into the operand tile, UMMA read) and the
+// kernel is bound by that pipe, not by the tensor core.  Here the problem is transposed: the MMA's M
+// dimension is the WEIGHT rows and its N dimension the batch rows,
+//
+//     D^T[n, m] = sum_k W[n, k] * X[m, k]        A = W (from tensor memory), B = X (from shared memory)
+//
+// A dequant thread owns weight row n = TMEM lane; the 32 registers it looks up per 64-wide K step are
+// exactly the 32 tensor-memory columns of its A row (two fp16 per column), written with one tcgen05.st.
+// Per K step a CTA's shared-memory pipe then carries only 16 KiB of lookups, 16 KiB of TMA writes (its
+// half of the X tile) and 16 KiB of UMMA reads: 48 KiB against 64 KiB of capacity in the 512 cycles the
+// MMA needs -- the kernel is tensor-bound.
+//
+// Pair tile: 256 weight rows x 256 batch rows.  CTA `rank` of the pair holds weight rows
+// [n0 + 128*rank, +128) (its 128 TMEM lanes: A stages and the 256-column fp32 accumulator) and loads
+// batch rows [m0 + 128*rank, +128) of X (its half of the B operand).
+//
+// Roles per CTA (320 threads):
+//   warp 0      TMA producer: this CTA's half of the X tile [128 x 64], SWIZZLE_128B
+//   warp 1      pair leader (rank 0): issues tcgen05.mma.cta_group::2 [d], [a_tmem], b_desc and commits
+//               stage-free / accumulator-ready mbarriers in both CTAs; in the other CTA the same warp
+//               forwards "my X half and my A stage are in place" with a remote mbarrier arrive
+//   warps 2..5  epilogue: tcgen05.ld of D^T (lane = weight row), fp16, transpose through a per-warp
+//               shared-memory tile, 16-byte row-major stores of Y (and peer copies).  Tensor memory is
+//               handed back to the MMA warp as soon as it has been read, before the write-out.
+//   warps 6..9  dequant: thread (quarter, lane) owns weight row 32*quarter + lane
+//
+// TMEM columns: [0, 256) accumulator, [256 + 32*s, +32) A stage s.  No TMA load uses cluster multicast.
+// Every mbarrier wait is bounded (see tensor2.cu).
+#include "tc_ptx.cuh"
+
+namespace vqg {
+
+using namespace tc;
+
+namespace {
+
+constexpr int BMH = 128;         // batch rows of X loaded per CTA (half of the pair's 256)
+constexpr int BM = 256;          // batch rows per pair tile (MMA N dimension)
+constexpr int BNH = 128;         // weight rows per CTA (its TMEM lanes)
+constexpr int BN = 256;          // weight rows per pair tile (MMA M dimension)
+constexpr int BK = 64;
+constexpr int kThreads = 320;
+constexpr int kDequantWarp0 = 6;
+constexpr int kDequantThreads = 128;
+constexpr uint32_t kXBytes = BMH * BK * 2;          // 16 KiB
+constexpr uint32_t kImageBytes = 32 * 1024;
+constexpr uint32_t kStagingPerWarp = 256 * 64;      // [256 batch rows][32 weight rows] fp16
+constexpr uint32_t kStagingBytes = 4 * kStagingPerWarp;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccCols = 256;                  // accumulator columns; A stages follow
+constexpr uint32_t kAColsPerStage = BK / 2;         // 32 columns: two fp16 per 32-bit column
+
+struct TsParams {
+  const unsigned char* idx;  // [N, K/v] uint8
+  const __half* cb;          // [G, C, v]
+  __half* y;
+  int* status;
+  int M, N, K, C;
+  int rows_per_cb;
+  long long ld_y;
+  int m_tiles, n_tiles;      // in 256 x 256 pair tiles
+  int n_peers;
+  __half* peer_y[8];
+};
+
+// kind::f16, A = B = fp16, D = fp32, both K-major, M = 256 weight rows (pair), N = 256 batch rows
+constexpr uint32_t kIdescTs = (1u << 4) | (static_cast<uint32_t>(BM >> 3) << 17) | (static_cast<uint32_t>(BN >> 4) << 24);
+
+template <int STAGES>
+struct TsSmem {
+  static constexpr uint32_t kImage = STAGES * kXBytes;
+  static constexpr uint32_t kStaging = kImage + kImageBytes;
+  static constexpr uint32_t kBars = kStaging + kStagingBytes;
+  // x_full[S], a_full[S], peer_full[S], empty[S], acc_full, acc_empty, dequant rendezvous
+  static constexpr uint32_t kTmemSlot = kBars + (4 * STAGES + 3) * 8;
+  static constexpr uint32_t kTotal = kTmemSlot + 16;
+};
+
+__device__ __forceinline__ void tc_mma_f16_pair_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                                   uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 32 registers -> 32 consecutive tensor-memory columns of this thread's lane
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+template <int V, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p) {
+  using L = TsSmem<STAGES>;
+  static_assert(kAccCols + STAGES * kAColsPerStage <= kTmemCols, "A stages do not fit tensor memory");
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;   // SWIZZLE_128B tiles need 1024-byte alignment
+  unsigned char* base_ptr = smem_dyn + (base - raw);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();         // 0 = pair leader
+  const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int ksteps = p.K / BK;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  auto x_addr = [&](int s) { return base + s * kXBytes; };
+  auto bar_x_full = [&](int s) { return base + L::kBars + 8 * s; };
+  auto bar_a_full = [&](int s) { return base + L::kBars + 8 * (STAGES + s); };
+  auto bar_peer_full = [&](int s) { return base + L::kBars + 8 * (2 * STAGES + s); };
+  auto bar_empty = [&](int s) { return base + L::kBars + 8 * (3 * STAGES + s); };
+  const uint32_t bar_acc_full = base + L::kBars + 8 * (4 * STAGES);
+  const uint32_t bar_acc_empty = base + L::kBars + 8 * (4 * STAGES + 1);
+  const uint32_t bar_dq = base + L::kBars + 8 * (4 * STAGES + 2);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kTmemSlot);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_x_full(s), 1);
+      mbar_init(bar_a_full(s), kDequantThreads / 32);
+      mbar_init(bar_peer_full(s), 1);
+      mbar_init(bar_empty(s), 1);
+    }
+    mbar_init(bar_acc_full, 1);
+    mbar_init(bar_acc_empty, 8);   // 4 epilogue warps in each CTA of the pair
+    mbar_init(bar_dq, kDequantThreads);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  if (warp == 1) {
+    // both CTAs of the pair allocate together (same warp index, same destination offset)
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(base + L::kTmemSlot),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the peer's mbarriers are initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
+        const int m0 = (tile % p.m_tiles) * BM + static_cast<int>(rank) * BMH;
+        for (int kt = 0; kt < ksteps; ++kt) {
+          if (!(ok = mbar_wait_cluster(bar_empty(stage), phase ^ 1, p.status, DS_STAGE_EMPTY_TIMEOUT))) break;
+          mbar_expect_tx(bar_x_full(stage), kXBytes);
+          tma_load_2d(x_addr(stage), &tmap_x, kt * BK, m0, bar_x_full(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      if (rank == 0) {
+        // ------------------------------- MMA issuer (pair leader) ---------------------------
+        uint32_t acc_phase = 0;
+        for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
+          if (!(ok = mbar_wait_cluster(bar_acc_empty, acc_phase ^ 1, p.status, DS_ACC_EMPTY_TIMEOUT))) break;
+          tc_fence_after();
+          for (int kt = 0; kt < ksteps; ++kt) {
+            if (!(ok = mbar_wait(bar_x_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
+            if (!(ok = mbar_wait(bar_a_full(stage), phase, p.status, DS_B_READY_TIMEOUT))) break;
+            if (!(ok = mbar_wait_cluster(bar_peer_full(stage), phase, p.status, DS_PEER_READY_TIMEOUT))) break;
+            tc_fence_after();
+            const uint64_t bd = make_desc(x_addr(stage));
+            const uint32_t a_t = tmem_base + kAccCols + static_cast<uint32_t>(stage) * kAColsPerStage;
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)   // 16 K values = 8 columns of A, 32 bytes of the X rows
+              tc_mma_f16_pair_ts(tmem_base, a_t + 8 * k, bd + 2 * k, kIdescTs, (kt | k) != 0 ? 1u : 0u);
+            // the stage (X tile and A columns) is free in both CTAs once these MMAs have read it
+            tc_commit_pair(bar_empty(stage));
+            tc_commit_pair(map_to_cta(bar_empty(stage), 1));
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (!ok) break;
+          tc_commit_pair(bar_acc_full);
+          tc_commit_pair(map_to_cta(bar_acc_full, 1));
+          acc_phase ^= 1;
+        }
+      } else {
+        // ------------------------------- forwarder (second CTA) -----------------------------
+        for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
+          for (int kt = 0; kt < ksteps; ++kt) {
+            if (!(ok = mbar_wait(bar_x_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
+            if (!(ok = mbar_wait(bar_a_full(stage), phase, p.status, DS_B_READY_TIMEOUT))) break;
+            mbar_arrive_remote(map_to_cta(bar_peer_full(stage), 0));
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+    }
+  } else if (warp < kDequantWarp0) {
+    // ------------------------------- epilogue -----------------------------------------------
+    // D^T: lane = weight row, column = batch row.  Each warp transposes its 32 weight rows through a
+    // private [256][32] fp16 tile and writes 64-byte row segments of Y.
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const uint32_t leader_acc_empty = map_to_cta(bar_acc_empty, 0);
+    unsigned char* stg = base_ptr + L::kStaging + quarter * kStagingPerWarp;
+    for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
+      const int m0 = (tile % p.m_tiles) * BM;
+      const int n0 = (tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH + quarter * 32;
+      if (!(ok = mbar_wait_cluster(bar_acc_full, acc_phase, p.status, DS_ACC_FULL_TIMEOUT))) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BM / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_row + c * 32, r);
+        __half* col = reinterpret_cast<__half*>(stg) + (c * 32) * 32 + lane;   // T[m][weight row], 32 halves per m
+#pragma unroll
+        for (int j = 0; j < 32; ++j) col[j * 32] = __float2half_rn(__uint_as_float(r[j]));
+      }
+      // tensor memory has been read: the next tile's MMAs may overwrite it while Y is written out
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(leader_acc_empty);
+      acc_phase ^= 1;
+      if (n0 < p.N) {
+        const int mrow = lane >> 2, chunk = lane & 3;
+#pragma unroll 4
+        for (int i = 0; i < BM / 8; ++i) {
+          const int m = 8 * i + mrow;
+          if (m0 + m < p.M) {
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + m * 64 + chunk * 16);
+            const size_t off = static_cast<size_t>(m0 + m) * p.ld_y + n0 + chunk * 8;
+            *reinterpret_cast<uint4*>(p.y + off) = v;
+            for (int q = 0; q < p.n_peers; ++q) *reinterpret_cast<uint4*>(p.peer_y[q] + off) = v;
+          }
+        }
+      }
+      __syncwarp();   // the tile is rewritten by the next tile's transposition
+    }
+  } else {
+    // ------------------------------- dequant warps ------------------------------------------
+    constexpr int ENTRY_LOG2 = (V == 4) ? 3 : 4;       // bytes per codebook entry
+    constexpr int REPS = 128 >> ENTRY_LOG2;             // replicas filling a 128-byte line
+    constexpr int WPS = (BK / V) / 4;                   // index words per K step (uint8 indices)
+    constexpr int GSTEPS = 16 / WPS;                    // K steps per 64-byte granule
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                  // weight row inside the CTA = TMEM lane
+    const int tix = threadIdx.x - kDequantWarp0 * 32;   // 0..127, for cooperative copies
+    const int J = p.K / V;                              // index bytes per weight row
+    unsigned char* image = base_ptr + L::kImage;
+    const uint32_t img = base + L::kImage + ((lane & (REPS - 1)) << ENTRY_LOG2);
+    const uint32_t a_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kAccCols;
+
+    int stage = 0;
+    uint32_t phase = 0;
+    int cur_group = -1;
+    bool ok = true;
+    uint32_t dq_phase = 0;
+    auto dq_sync = [&]() -> bool {   // bounded rendezvous of the dequant threads of this CTA
+      mbar_arrive(bar_dq);
+      const bool done = mbar_wait(bar_dq, dq_phase, p.status, DS_DEQUANT_SYNC_TIMEOUT);
+      dq_phase ^= 1;
+      return done;
+    };
+    for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
+      const int n_half0 = (tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH;
+      const int n = n_half0 + r;
+      const bool row_valid = n < p.N;
+      const int group = (n_half0 < p.N ? n_half0 : p.N - 1) / p.rows_per_cb;
+      if (group != cur_group) {
+        cur_group = group;
+        if (!(ok = dq_sync())) break;   // every thread has finished its lookups in the old image
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(p.cb) + (static_cast<size_t>(group) * p.C << ENTRY_LOG2);
+        if (V == 4) {
+          for (int u = tix; u < p.C * (REPS / 2); u += kDequantThreads) {
+            const uint2 e = __ldg(reinterpret_cast<const uint2*>(src) + u / (REPS / 2));
+            reinterpret_cast<uint4*>(image)[u] = make_uint4(e.x, e.y, e.x, e.y);
+          }
+        } else {
+          for (int u = tix; u < p.C * REPS; u += kDequantThreads)
+            reinterpret_cast<uint4*>(image)[u] = __ldg(reinterpret_cast<const uint4*>(src) + u / REPS);
+        }
+        if (!(ok = dq_sync())) break;
+      }
+
+      const unsigned char* row_ptr = p.idx + static_cast<size_t>(row_valid ? n : 0) * J;
+      uint32_t cur[16], nxt[16];
+      auto load_granule = [&](int gi, uint32_t (&dst)[16]) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 t = make_uint4(0, 0, 0, 0);
+          const int byte0 = gi * 64 + q * 16;
+          if (row_valid && byte0 + 16 <= J) t = __ldg(reinterpret_cast<const uint4*>(row_ptr + byte0));
+          dst[4 * q] = t.x; dst[4 * q + 1] = t.y; dst[4 * q + 2] = t.z; dst[4 * q + 3] = t.w;
+        }
+      };
+      const int ngran = (ksteps + GSTEPS - 1) / GSTEPS;
+      load_granule(0, nxt);
+      for (int gi = 0; ok && gi < ngran; ++gi) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) cur[i] = nxt[i];
+        if (gi + 1 < ngran) load_granule(gi + 1, nxt);
+#pragma unroll
+        for (int st = 0; st < GSTEPS; ++st) {
+          const int kt = gi * GSTEPS + st;
+          if (kt >= ksteps) break;
+          // 64 K values of this row: 32 registers, in K order = the 32 columns of the A stage
+          uint32_t a[32];
+          if (V == 4) {
+#pragma unroll
+            for (int w = 0; w < WPS; ++w) {
+              const uint32_t word = cur[st * WPS + w];
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                const uint32_t c0 = (word >> (8 * b)) & 0xffu;
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(a[8 * w + 2 * b]), "=r"(a[8 * w + 2 * b + 1]) : "r"(img + (c0 << 7)));
+              }
+            }
+          } else {
+#pragma unroll
+            for (int w = 0; w < WPS; ++w) {
+              const uint32_t word = cur[st * WPS + w];
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                const uint32_t c0 = (word >> (8 * b)) & 0xffu;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(a[16 * w + 4 * b]), "=r"(a[16 * w + 4 * b + 1]), "=r"(a[16 * w + 4 * b + 2]), "=r"(a[16 * w + 4 * b + 3])
+                             : "r"(img + (c0 << 7)));
+              }
+            }
+          }
+          // (lookups above overlap the wait for the stage)
+          if (!(ok = mbar_wait_cluster(bar_empty(stage), phase ^ 1, p.status, DS_STAGE_EMPTY_TIMEOUT))) break;
+          tc_fence_after();
+          tmem_st32(a_lane + static_cast<uint32_t>(stage) * kAColsPerStage, a);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_a_full(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  }
+
+  // ------------------------------- teardown --------------------------------------------------
+  // Nobody leaves before both CTAs are done: the leader's MMAs read the peer's shared and tensor memory
+  // and both CTAs signal each other's mbarriers.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeFn>(f);
+  }();
+  return fn;
+}
+
+// fp16 row-major [rows, cols] matrix, box [128 rows x 64 cols], 128-byte swizzle, zero fill.
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {BK, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool tensor_ts_supported(const Problem& p) {
+  if (p.M < 1 || p.N < 1 || p.K < BK || p.K % BK != 0) return false;
+  if (reinterpret_cast<uintptr_t>(p.x) % 16 || reinterpret_cast<uintptr_t>(p.y) % 16) return false;
+  if (p.N % 32 != 0 || p.ld_y % 8 != 0) return false;
+  if (!(p.v == 4 || p.v == 8) || p.idx_bytes != 1 || p.C < 1 || p.C > 256) return false;
+  if ((p.K / p.v) % 16 != 0) return false;  // 16-byte index loads per row
+  if (reinterpret_cast<uintptr_t>(p.idx) % 16 || reinterpret_cast<uintptr_t>(p.cb) % 16) return false;
+  const bool single = p.rows_per_cb >= p.N;
+  if (!single && p.rows_per_cb % 128 != 0) return false;
+  return true;
+}
+
+int launch_tensor_ts(const Problem& p, cudaStream_t s) {
+  if (!tensor_ts_supported(p)) return VQG_ERR_UNSUPPORTED;
+  CUtensorMap mx;
+  if (!make_map(&mx, p.x, p.M, p.K)) return VQG_ERR_LAUNCH;
+  TsParams tp{};
+  tp.idx = static_cast<const unsigned char*>(p.idx);
+  tp.cb = p.cb;
+  tp.y = p.y;
+  tp.status = device_status_ptr();
+  tp.M = p.M; tp.N = p.N; tp.K = p.K; tp.C = p.C;
+  tp.rows_per_cb = p.rows_per_cb >= p.N ? p.N : p.rows_per_cb;
+  tp.ld_y = p.ld_y;
+  tp.m_tiles = (p.M + BM - 1) / BM;
+  tp.n_tiles = (p.N + BN - 1) / BN;
+  tp.n_peers = p.n_peers;
+  for (int i = 0; i < 8; ++i) tp.peer_y[i] = p.peer_y[i];
+  constexpr int S = 7;
+  const size_t smem = TsSmem<S>::kTotal + 1024;
+  auto launch = [&](auto kernel) -> int {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+      return VQG_ERR_LAUNCH;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int tiles = tp.m_tiles * tp.n_tiles;
+    const int max_pairs = sms / 2;
+    const int pairs = tiles < max_pairs ? tiles : max_pairs;
+    kernel<<<2 * pairs, kThreads, smem, s>>>(mx, tp);
+    count_launch();
+    return cuda_status(cudaGetLastError());
+  };
+  if (p.v == 4) return launch(vq_tensor_ts_kernel<4, S>);
+  return launch(vq_tensor_ts_kernel<8, S>);
+}
+
+}  // namespace vqg

@@ -34,6 +34,10 @@ def test_dense_gemm(M, K, N):
 @pytest.mark.parametrize("path", ["tensor", "tensor_pair", "tensor_ts"])
 def test_fused_matches_oracle(M, K, N, v, rpc, path):
     x, idx, cb = O.make_bl_inputs(M, K, N, v, 256, rpc, seed=M + K + N + v, cb_sigma=0.05)
+    if path == "tensor_ts" and K % 128:   # that kernel's pipeline stage is 128 K values
+        with pytest.raises(RuntimeError, match="unsupported"):
+            run_bl(V, x, idx, cb, rpc, path=path)
+        return
     y = run_bl(V, x, idx, cb, rpc, path=path)
     assert_within_tolerance(y, O.vq_gemm_bl(x, idx, cb, rpc))
 

@@ -82,6 +82,7 @@ int auto_path(const Problem& p, int layout) {
   }
   if (p.K == 0) return VQG_PATH_GENERIC;
   if (p.M <= 16 && decode_supported(p)) return VQG_PATH_DECODE;
+  if (p.M > 128 && tensor_ts_supported(p)) return VQG_PATH_TENSOR_TS;
   if (p.M > 128 && tensor_pair_supported(p)) return VQG_PATH_TENSOR_PAIR;
   if (p.M > 16 && tensor_supported(p)) return VQG_PATH_TENSOR;
   if (p.M > 16 && dense_supported(p.M, p.N, p.K) && (p.v == 2 || p.v == 4 || p.v == 8)) return VQG_PATH_TWO_PHASE;

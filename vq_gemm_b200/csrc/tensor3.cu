@@ -70,13 +70,13 @@ struct TsParams {
 // kind::f16, A = B = fp16, D = fp32, both K-major, M = 256 weight rows (pair), N = 256 batch rows
 constexpr uint32_t kIdescTs = (1u << 4) | (static_cast<uint32_t>(BM >> 3) << 17) | (static_cast<uint32_t>(BN >> 4) << 24);
 
-template <int STAGES>
+template <int STAGES, int KS>
 struct TsSmem {
-  static constexpr uint32_t kImage = STAGES * kXBytes;
+  static constexpr uint32_t kImage = STAGES * KS * kXBytes;
   static constexpr uint32_t kStaging = kImage + kImageBytes;
   static constexpr uint32_t kBars = kStaging + kStagingBytes;
-  // x_full[S], a_full[S], peer_full[S], empty[S], acc_full, acc_empty, dequant rendezvous
-  static constexpr uint32_t kTmemSlot = kBars + (4 * STAGES + 3) * 8;
+  // full[S], empty[S], acc_full, acc_empty, dequant rendezvous
+  static constexpr uint32_t kTmemSlot = kBars + (2 * STAGES + 3) * 8;
   static constexpr uint32_t kTotal = kTmemSlot + 16;
 };
 
@@ -104,11 +104,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-template <int V, int STAGES>
+// KS: 64-wide K sub-tiles per pipeline stage (a stage is KS*64 K values: fewer barrier round trips and
+// commits per MMA for the single issuing thread).
+template <int V, int STAGES, int KS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p) {
-  using L = TsSmem<STAGES>;
-  static_assert(kAccCols + STAGES * kAColsPerStage <= kTmemCols, "A stages do not fit tensor memory");
+  using L = TsSmem<STAGES, KS>;
+  constexpr uint32_t kStageCols = KS * kAColsPerStage;
+  constexpr uint32_t kStageXBytes = KS * kXBytes;
+  static_assert(kAccCols + STAGES * kStageCols <= kTmemCols, "A stages do not fit tensor memory");
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;   // SWIZZLE_128B tiles need 1024-byte alignment
@@ -117,24 +121,25 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();         // 0 = pair leader
   const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int ksteps = p.K / BK;
+  const int ksubs = p.K / BK;        // 64-wide K sub-steps
+  const int ksteps = ksubs / KS;     // pipeline stages per tile
   const int total_tiles = p.m_tiles * p.n_tiles;
 
-  auto x_addr = [&](int s) { return base + s * kXBytes; };
-  auto bar_x_full = [&](int s) { return base + L::kBars + 8 * s; };
-  auto bar_a_full = [&](int s) { return base + L::kBars + 8 * (STAGES + s); };
-  auto bar_peer_full = [&](int s) { return base + L::kBars + 8 * (2 * STAGES + s); };
-  auto bar_empty = [&](int s) { return base + L::kBars + 8 * (3 * STAGES + s); };
-  const uint32_t bar_acc_full = base + L::kBars + 8 * (4 * STAGES);
-  const uint32_t bar_acc_empty = base + L::kBars + 8 * (4 * STAGES + 1);
-  const uint32_t bar_dq = base + L::kBars + 8 * (4 * STAGES + 2);
+  auto x_addr = [&](int s) { return base + s * kStageXBytes; };
+  // full[s]: this CTA's X half has landed (TMA, 1 arrival + bytes) and its 4 dequant warps have written
+  // their A columns; in the leader one more arrival says the same of the second CTA.  One wait per stage.
+  auto bar_full = [&](int s) { return base + L::kBars + 8 * s; };
+  auto bar_empty = [&](int s) { return base + L::kBars + 8 * (STAGES + s); };
+  const uint32_t bar_acc_full = base + L::kBars + 8 * (2 * STAGES);
+  const uint32_t bar_acc_empty = base + L::kBars + 8 * (2 * STAGES + 1);
+  const uint32_t bar_dq = base + L::kBars + 8 * (2 * STAGES + 2);
+  // shared::cluster address of the same offset in the other CTA = local address + a constant
+  const uint32_t to_peer = map_to_cta(base, rank ^ 1u) - base;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kTmemSlot);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_x_full(s), 1);
-      mbar_init(bar_a_full(s), kDequantThreads / 32);
-      mbar_init(bar_peer_full(s), 1);
+      mbar_init(bar_full(s), 1 + kDequantThreads / 32 + (rank == 0 ? 1 : 0));
       mbar_init(bar_empty(s), 1);
     }
     mbar_init(bar_acc_full, 1);
@@ -166,8 +171,10 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
         const int m0 = (tile % p.m_tiles) * BM + static_cast<int>(rank) * BMH;
         for (int kt = 0; kt < ksteps; ++kt) {
           if (!(ok = mbar_wait_cluster(bar_empty(stage), phase ^ 1, p.status, DS_STAGE_EMPTY_TIMEOUT))) break;
-          mbar_expect_tx(bar_x_full(stage), kXBytes);
-          tma_load_2d(x_addr(stage), &tmap_x, kt * BK, m0, bar_x_full(stage));
+          mbar_expect_tx(bar_full(stage), kStageXBytes);
+#pragma unroll
+          for (int u = 0; u < KS; ++u)
+            tma_load_2d(x_addr(stage) + u * kXBytes, &tmap_x, (kt * KS + u) * BK, m0, bar_full(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -184,32 +191,33 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
           if (!(ok = mbar_wait_cluster(bar_acc_empty, acc_phase ^ 1, p.status, DS_ACC_EMPTY_TIMEOUT))) break;
           tc_fence_after();
           for (int kt = 0; kt < ksteps; ++kt) {
-            if (!(ok = mbar_wait(bar_x_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
-            if (!(ok = mbar_wait(bar_a_full(stage), phase, p.status, DS_B_READY_TIMEOUT))) break;
-            if (!(ok = mbar_wait_cluster(bar_peer_full(stage), phase, p.status, DS_PEER_READY_TIMEOUT))) break;
+            if (!(ok = mbar_wait_cluster(bar_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
             tc_fence_after();
-            const uint64_t bd = make_desc(x_addr(stage));
-            const uint32_t a_t = tmem_base + kAccCols + static_cast<uint32_t>(stage) * kAColsPerStage;
+            const uint32_t a_t = tmem_base + kAccCols + static_cast<uint32_t>(stage) * kStageCols;
 #pragma unroll
-            for (int k = 0; k < BK / 16; ++k)   // 16 K values = 8 columns of A, 32 bytes of the X rows
-              tc_mma_f16_pair_ts(tmem_base, a_t + 8 * k, bd + 2 * k, kIdescTs, (kt | k) != 0 ? 1u : 0u);
+            for (int u = 0; u < KS; ++u) {
+              const uint64_t bd = make_desc(x_addr(stage) + u * kXBytes);
+#pragma unroll
+              for (int k = 0; k < BK / 16; ++k)   // 16 K values = 8 columns of A, 32 bytes of the X rows
+                tc_mma_f16_pair_ts(tmem_base, a_t + u * kAColsPerStage + 8 * k, bd + 2 * k, kIdescTs,
+                                   (kt | u | k) != 0 ? 1u : 0u);
+            }
             // the stage (X tile and A columns) is free in both CTAs once these MMAs have read it
             tc_commit_pair(bar_empty(stage));
-            tc_commit_pair(map_to_cta(bar_empty(stage), 1));
+            tc_commit_pair(bar_empty(stage) + to_peer);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
           if (!ok) break;
           tc_commit_pair(bar_acc_full);
-          tc_commit_pair(map_to_cta(bar_acc_full, 1));
+          tc_commit_pair(bar_acc_full + to_peer);
           acc_phase ^= 1;
         }
       } else {
         // ------------------------------- forwarder (second CTA) -----------------------------
         for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
           for (int kt = 0; kt < ksteps; ++kt) {
-            if (!(ok = mbar_wait(bar_x_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
-            if (!(ok = mbar_wait(bar_a_full(stage), phase, p.status, DS_B_READY_TIMEOUT))) break;
-            mbar_arrive_remote(map_to_cta(bar_peer_full(stage), 0));
+            if (!(ok = mbar_wait(bar_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
+            mbar_arrive_remote(bar_full(stage) + to_peer);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         }
@@ -315,7 +323,7 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
           dst[4 * q] = t.x; dst[4 * q + 1] = t.y; dst[4 * q + 2] = t.z; dst[4 * q + 3] = t.w;
         }
       };
-      const int ngran = (ksteps + GSTEPS - 1) / GSTEPS;
+      const int ngran = (ksubs + GSTEPS - 1) / GSTEPS;
       load_granule(0, nxt);
       for (int gi = 0; ok && gi < ngran; ++gi) {
 #pragma unroll
@@ -323,9 +331,9 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
         if (gi + 1 < ngran) load_granule(gi + 1, nxt);
 #pragma unroll
         for (int st = 0; st < GSTEPS; ++st) {
-          const int kt = gi * GSTEPS + st;
-          if (kt >= ksteps) break;
-          // 64 K values of this row: 32 registers, in K order = the 32 columns of the A stage
+          const int ks = gi * GSTEPS + st;                 // 64-wide sub-step; KS of them make a stage
+          if (ks >= ksubs) break;
+          // 64 K values of this row: 32 registers, in K order = 32 columns of the A stage
           uint32_t a[32];
           if (V == 4) {
 #pragma unroll
@@ -350,14 +358,19 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
               }
             }
           }
-          // (lookups above overlap the wait for the stage)
-          if (!(ok = mbar_wait_cluster(bar_empty(stage), phase ^ 1, p.status, DS_STAGE_EMPTY_TIMEOUT))) break;
-          tc_fence_after();
-          tmem_st32(a_lane + static_cast<uint32_t>(stage) * kAColsPerStage, a);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_a_full(stage));
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          // (the lookups above overlap the wait for the stage)
+          const int sub = st % KS;                          // GSTEPS is a multiple of KS
+          if (sub == 0) {
+            if (!(ok = mbar_wait_cluster(bar_empty(stage), phase ^ 1, p.status, DS_STAGE_EMPTY_TIMEOUT))) break;
+            tc_fence_after();
+          }
+          tmem_st32(a_lane + static_cast<uint32_t>(stage) * kStageCols + sub * kAColsPerStage, a);
+          if (sub == KS - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_full(stage));
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
         }
       }
     }
@@ -409,7 +422,7 @@ bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols) {
 }  // namespace
 
 bool tensor_ts_supported(const Problem& p) {
-  if (p.M < 1 || p.N < 1 || p.K < BK || p.K % BK != 0) return false;
+  if (p.M < 1 || p.N < 1 || p.K < 2 * BK || p.K % (2 * BK) != 0) return false;   // stages of 128 K values
   if (reinterpret_cast<uintptr_t>(p.x) % 16 || reinterpret_cast<uintptr_t>(p.y) % 16) return false;
   if (p.N % 32 != 0 || p.ld_y % 8 != 0) return false;
   if (!(p.v == 4 || p.v == 8) || p.idx_bytes != 1 || p.C < 1 || p.C > 256) return false;
@@ -436,8 +449,8 @@ int launch_tensor_ts(const Problem& p, cudaStream_t s) {
   tp.n_tiles = (p.N + BN - 1) / BN;
   tp.n_peers = p.n_peers;
   for (int i = 0; i < 8; ++i) tp.peer_y[i] = p.peer_y[i];
-  constexpr int S = 7;
-  const size_t smem = TsSmem<S>::kTotal + 1024;
+  constexpr int S = 4, KS = 2;   // 4 stages of 128 K values: 128 KiB of X tiles, 4 x 64 TMEM columns of A
+  const size_t smem = TsSmem<S, KS>::kTotal + 1024;
   auto launch = [&](auto kernel) -> int {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return VQG_ERR_LAUNCH;
@@ -451,8 +464,8 @@ int launch_tensor_ts(const Problem& p, cudaStream_t s) {
     count_launch();
     return cuda_status(cudaGetLastError());
   };
-  if (p.v == 4) return launch(vq_tensor_ts_kernel<4, S>);
-  return launch(vq_tensor_ts_kernel<8, S>);
+  if (p.v == 4) return launch(vq_tensor_ts_kernel<4, S, KS>);
+  return launch(vq_tensor_ts_kernel<8, S, KS>);
 }
 
 }  // namespace vqg

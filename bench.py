@@ -318,7 +318,9 @@ def main():
         def kernel_only():
             V.vq_gemm(x, idx, cb, rows_per_codebook=rpc, layout="bl", out=kout)
         kout = torch.empty((shape.M, n_local), dtype=torch.float16, device=dev)
-        kms = _time_loop(kernel_only, max(10, args.steps // 2), 3, None)
+        # with one rank a step IS the kernel (no barriers, no peer copies): reuse its time rather than a
+        # second loop that would run at a different point of the power/clock curve
+        kms = ms if world == 1 else _time_loop(kernel_only, max(10, args.steps // 2), 3, None)
 
         # end to end: host inputs in, host output out, every step
         y_h = torch.empty((shape.M, n_local), dtype=torch.float16).pin_memory()
@@ -349,7 +351,10 @@ def main():
     if shape.bound == "tensor":
         ach = kflops / kms / 1e9
         roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"],
-                "traffic": None, "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                # ncu dram__bytes_read+write per launch of this kernel on this workload (profiles/), N=1 only
+                "traffic": 157.6e6 if (world == 1 and shape.name == "c5_mlp70b") else None,
+                "traffic_algorithmic": shape.bytes_algorithmic if world == 1 else None,
+                "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
                 "frac_of_sustained": ach / peaks["tflops_sustained"] if peaks["tflops_sustained"] else None,
                 "frac_of_nominal_2250": ach / 2250.0, "kernel": "vq_tensor_ts_kernel", "kernel_us": kms * 1e3}
     else:

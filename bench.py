@@ -385,7 +385,7 @@ def main():
 
     ms, kms, ems = reduce_max(ms), reduce_max(kms), reduce_max(ems)
     h2d = x_h.numel() * 2 + idx_h.numel() * idx_h.element_size() + cb_h.numel() * 2
-    d2h = y_h.numel() * 2
+    d2h = y_h[0].numel() * 2
     flops = shape.flops
     kflops = 2.0 * shape.M * n_local * shape.K
     if shape.bound == "tensor":

@@ -37,6 +37,7 @@ enum DeviceStatus : int {
   DS_SPLITK_TIMEOUT = 6,
   DS_DEQUANT_SYNC_TIMEOUT = 7,
   DS_PEER_READY_TIMEOUT = 8, // pair leader waited for the second CTA's operands
+  DS_EPILOGUE_SYNC_TIMEOUT = 9,
 };
 int* device_status_ptr();          // device address of the status word of the current device
 cudaError_t ensure_status_word();  // allocates it on first use (per device)

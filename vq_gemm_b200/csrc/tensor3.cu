@@ -48,8 +48,7 @@ constexpr int kDequantWarp0 = 6;
 constexpr int kDequantThreads = 128;
 constexpr uint32_t kXBytes = BMH * BK * 2;          // 16 KiB
 constexpr uint32_t kImageBytes = 32 * 1024;
-constexpr uint32_t kStagingPerWarp = 256 * 64;      // [256 batch rows][32 weight rows] fp16
-constexpr uint32_t kStagingBytes = 4 * kStagingPerWarp;
+constexpr uint32_t kStagingBytes = 256 * 256;       // [256 batch rows][128 weight rows] fp16, shared by the 4 epilogue warps
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccCols = 256;                  // accumulator columns; A stages follow
 constexpr uint32_t kAColsPerStage = BK / 2;         // 32 columns: two fp16 per 32-bit column
@@ -75,8 +74,8 @@ struct TsSmem {
   static constexpr uint32_t kImage = STAGES * KS * kXBytes;
   static constexpr uint32_t kStaging = kImage + kImageBytes;
   static constexpr uint32_t kBars = kStaging + kStagingBytes;
-  // full[S], empty[S], acc_full, acc_empty, dequant rendezvous
-  static constexpr uint32_t kTmemSlot = kBars + (2 * STAGES + 3) * 8;
+  // full[S], empty[S], acc_full, acc_empty, dequant rendezvous, epilogue rendezvous
+  static constexpr uint32_t kTmemSlot = kBars + (2 * STAGES + 4) * 8;
   static constexpr uint32_t kTotal = kTmemSlot + 16;
 };
 
@@ -133,6 +132,7 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
   const uint32_t bar_acc_full = base + L::kBars + 8 * (2 * STAGES);
   const uint32_t bar_acc_empty = base + L::kBars + 8 * (2 * STAGES + 1);
   const uint32_t bar_dq = base + L::kBars + 8 * (2 * STAGES + 2);
+  const uint32_t bar_epi = base + L::kBars + 8 * (2 * STAGES + 3);
   // shared::cluster address of the same offset in the other CTA = local address + a constant
   const uint32_t to_peer = map_to_cta(base, rank ^ 1u) - base;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kTmemSlot);
@@ -145,6 +145,7 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
     mbar_init(bar_acc_full, 1);
     mbar_init(bar_acc_empty, 8);   // 4 epilogue warps in each CTA of the pair
     mbar_init(bar_dq, kDequantThreads);
+    mbar_init(bar_epi, 4);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
   }
@@ -225,16 +226,23 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
     }
   } else if (warp < kDequantWarp0) {
     // ------------------------------- epilogue -----------------------------------------------
-    // D^T: lane = weight row, column = batch row.  Each warp transposes its 32 weight rows through a
-    // private [256][32] fp16 tile and writes 64-byte row segments of Y.
+    // D^T: lane = weight row, column = batch row.  The four warps transpose the CTA's 128 weight rows
+    // through one [256][128] fp16 tile and write Y in 256-byte row segments (whole lines, also on NVLink).
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
-    uint32_t acc_phase = 0;
+    uint32_t acc_phase = 0, epi_phase = 0;
     bool ok = true;
-    const uint32_t leader_acc_empty = map_to_cta(bar_acc_empty, 0);
-    unsigned char* stg = base_ptr + L::kStaging + quarter * kStagingPerWarp;
+    const uint32_t leader_acc_empty = bar_acc_empty + (rank == 0 ? 0u : to_peer);
+    unsigned char* stg = base_ptr + L::kStaging;
+    auto epi_sync = [&]() -> bool {   // bounded rendezvous of the four epilogue warps
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_epi);
+      const bool done = mbar_wait(bar_epi, epi_phase, p.status, DS_EPILOGUE_SYNC_TIMEOUT);
+      epi_phase ^= 1;
+      return done;
+    };
     for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
       const int m0 = (tile % p.m_tiles) * BM;
-      const int n0 = (tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH + quarter * 32;
+      const int n0 = (tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH;
       if (!(ok = mbar_wait_cluster(bar_acc_full, acc_phase, p.status, DS_ACC_FULL_TIMEOUT))) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -242,29 +250,31 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
       for (int c = 0; c < BM / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(t_row + c * 32, r);
-        __half* col = reinterpret_cast<__half*>(stg) + (c * 32) * 32 + lane;   // T[m][weight row], 32 halves per m
+        __half* col = reinterpret_cast<__half*>(stg) + (c * 32) * 128 + quarter * 32 + lane;   // T[m][weight row]
 #pragma unroll
-        for (int j = 0; j < 32; ++j) col[j * 32] = __float2half_rn(__uint_as_float(r[j]));
+        for (int j = 0; j < 32; ++j) col[j * 128] = __float2half_rn(__uint_as_float(r[j]));
       }
       // tensor memory has been read: the next tile's MMAs may overwrite it while Y is written out
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(leader_acc_empty);
       acc_phase ^= 1;
-      if (n0 < p.N) {
-        const int mrow = lane >> 2, chunk = lane & 3;
+      if (!(ok = epi_sync())) break;   // the whole tile is in shared memory
+      {
+        const int half_row = lane >> 4, chunk = lane & 15;   // a warp instruction covers two 256-byte rows
+        const int ncol = n0 + chunk * 8;
 #pragma unroll 4
         for (int i = 0; i < BM / 8; ++i) {
-          const int m = 8 * i + mrow;
-          if (m0 + m < p.M) {
-            const uint4 v = *reinterpret_cast<const uint4*>(stg + m * 64 + chunk * 16);
-            const size_t off = static_cast<size_t>(m0 + m) * p.ld_y + n0 + chunk * 8;
+          const int m = 8 * i + 2 * quarter + half_row;
+          if (m0 + m < p.M && ncol < p.N) {
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + m * 256 + chunk * 16);
+            const size_t off = static_cast<size_t>(m0 + m) * p.ld_y + ncol;
             *reinterpret_cast<uint4*>(p.y + off) = v;
             for (int q = 0; q < p.n_peers; ++q) *reinterpret_cast<uint4*>(p.peer_y[q] + off) = v;
           }
         }
       }
-      __syncwarp();   // the tile is rewritten by the next tile's transposition
+      if (!(ok = epi_sync())) break;   // the tile is rewritten by the next tile's transposition
     }
   } else {
     // ------------------------------- dequant warps ------------------------------------------

@@ -205,6 +205,65 @@ def _single_shape(V, shape, peaks, steps, warmup):
     return res
 
 
+def _reference_cuda_kernels(V):
+    """Optional baseline leg (--baselines): the reference's own CUDA kernels, rebuilt unmodified for
+    sm_100a by oracle/build_ref.py, on data in the reference's format; and this library on the same data.
+    The reference launchers print to stdout and (PROFILING 1) run 50 + 100 launches per call, so stdout is
+    parked on /dev/null around them and the event time of one call is divided by 150."""
+    import importlib.util
+    from oracle import vq_oracle as O
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    launches = {"s1": 150, "s2_128": 150, "s2_512": 150, "s3_naive": 1, "s3_wasp": 150}
+    out = []
+    for tag, (M, K, Nq) in {"reference_default": (2048, 4096, 640), "c4_sized": (4096, 4096, 7168)}.items():
+        x, w, cb = O.make_ref_inputs(M, K, Nq, seed=42)
+        cb = (cb.float() * 0.02).half()
+        xd, wd, cbd = x.cuda(), w.cuda(), cb.cuda()
+        flops = 2.0 * M * K * Nq * 2
+        e0, e1 = _events()
+        for _ in range(3):
+            ours = V.e2e_gemm(xd, wd, cbd)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(20):
+            ours = V.e2e_gemm(xd, wd, cbd)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 20
+        row = {"shape": tag, "M": M, "K": K, "Nq": Nq, "ours": {"us": ms * 1e3, "tflops": flops / ms / 1e9}}
+        for variant, per_call in launches.items():
+            path = os.path.join(ref_dir, f"vq_gemm_cuda_{variant}.so")
+            if not os.path.exists(path):
+                row[variant] = {"unavailable": "not built (python oracle/build_ref.py)"}
+                continue
+            spec = importlib.util.spec_from_file_location(f"vq_gemm_cuda_{variant}", path)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            sys.stdout.flush()
+            saved = os.dup(1)
+            devnull = os.open(os.devnull, os.O_WRONLY)
+            os.dup2(devnull, 1)
+            try:
+                calls = 1 if per_call > 1 else 20
+                theirs = mod.e2e_gemm(xd, wd, cbd)          # warm-up call
+                torch.cuda.synchronize()
+                e0.record()
+                for _ in range(calls):
+                    theirs = mod.e2e_gemm(xd, wd, cbd)
+                e1.record()
+                torch.cuda.synchronize()
+            finally:
+                os.dup2(saved, 1)
+                os.close(saved)
+                os.close(devnull)
+            rms = e0.elapsed_time(e1) / (calls * per_call)
+            diff = float((theirs.float() - ours.float()).abs().max() / ours.float().abs().max())
+            row[variant] = {"us": rms * 1e3, "tflops": flops / rms / 1e9, "speedup_ours": rms / ms,
+                            "max_rel_diff_vs_ours": diff, "launches_per_call": per_call}
+        out.append(row)
+    return out
+
+
 def _cpu_sample(shape, seconds_budget=20.0):
     """Torch CPU oracle on a column block of the workload (full M and K)."""
     from oracle import vq_oracle as O
@@ -269,6 +328,8 @@ def main():
     ap.add_argument("--workload", default="c5_mlp70b")
     ap.add_argument("--mode", default="peer", choices=["peer", "nccl"], help="how the N-sharded output is assembled")
     ap.add_argument("--no-shapes", action="store_true", help="skip the per-configuration table")
+    ap.add_argument("--baselines", action="store_true",
+                    help="also time the reference's own CUDA kernels from oracle/_ref (N=1 only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -427,6 +488,11 @@ def main():
             except Exception as e:  # keep the headline line even if a side measurement fails
                 shapes.append({"workload": name, "error": repr(e)})
         line["shapes"] = shapes
+    if world == 1 and rank == 0 and args.baselines:
+        try:
+            line["reference_cuda_kernels"] = _reference_cuda_kernels(V)
+        except Exception as e:
+            line["reference_cuda_kernels"] = {"error": repr(e)}
     if rank == 0:
         if world == 1:
             try:

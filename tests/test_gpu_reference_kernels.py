@@ -29,7 +29,7 @@ def _load(variant):
     return mod
 
 
-@pytest.mark.parametrize("variant", ["s1", "s2_128", "s2_512"])
+@pytest.mark.parametrize("variant", ["s1", "s2_128", "s2_512", "s3_naive", "s3_wasp"])
 def test_reference_kernel_agrees(variant, capfd):
     mod = _load(variant)
     M, K, Nq = 256, 1024, 128

@@ -61,8 +61,8 @@ struct PairSmem {
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kImage = STAGES * kStageBytes;
   static constexpr uint32_t kBars = kImage + (DENSE ? 0 : kImageBytes);
-  // a_full[S], b_full[S], peer_full[S], empty[S], acc_full[2], acc_empty[2], dequant rendezvous
-  static constexpr uint32_t kTmemSlot = kBars + (4 * STAGES + 5) * 8;
+  // full[S], empty[S], acc_full[2], acc_empty[2], dequant rendezvous
+  static constexpr uint32_t kTmemSlot = kBars + (2 * STAGES + 5) * 8;
   static constexpr uint32_t kTotal = kTmemSlot + 16;
 };
 
@@ -84,20 +84,20 @@ vq_tensor_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 
   auto a_addr = [&](int s) { return base + s * L::kStageBytes; };
   auto b_addr = [&](int s) { return base + s * L::kStageBytes + kABytes; };
-  auto bar_a_full = [&](int s) { return base + L::kBars + 8 * s; };
-  auto bar_b_full = [&](int s) { return base + L::kBars + 8 * (STAGES + s); };
-  auto bar_peer_full = [&](int s) { return base + L::kBars + 8 * (2 * STAGES + s); };
-  auto bar_empty = [&](int s) { return base + L::kBars + 8 * (3 * STAGES + s); };
-  auto bar_acc_full = [&](int a) { return base + L::kBars + 8 * (4 * STAGES + a); };
-  auto bar_acc_empty = [&](int a) { return base + L::kBars + 8 * (4 * STAGES + 2 + a); };
-  const uint32_t bar_dq = base + L::kBars + 8 * (4 * STAGES + 4);
+  // full[s]: this CTA's TMA bytes have landed (1 arrival + bytes) and, in the fused variant, its 4 dequant
+  // warps have written B; in the leader one more arrival says the same of the second CTA.
+  auto bar_full = [&](int s) { return base + L::kBars + 8 * s; };
+  auto bar_empty = [&](int s) { return base + L::kBars + 8 * (STAGES + s); };
+  auto bar_acc_full = [&](int a) { return base + L::kBars + 8 * (2 * STAGES + a); };
+  auto bar_acc_empty = [&](int a) { return base + L::kBars + 8 * (2 * STAGES + 2 + a); };
+  const uint32_t bar_dq = base + L::kBars + 8 * (2 * STAGES + 4);
+  // shared::cluster address of the same offset in the other CTA = local address + a constant
+  const uint32_t to_peer = map_to_cta(base, rank ^ 1u) - base;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kTmemSlot);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_a_full(s), 1);
-      mbar_init(bar_b_full(s), kDequantThreads / 32);
-      mbar_init(bar_peer_full(s), 1);
+      mbar_init(bar_full(s), 1 + (DENSE ? 0 : kDequantThreads / 32) + (rank == 0 ? 1 : 0));
       mbar_init(bar_empty(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -132,9 +132,9 @@ vq_tensor_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         const int n0 = (tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH;
         for (int kt = 0; kt < ksteps; ++kt) {
           if (!(ok = mbar_wait_cluster(bar_empty(stage), phase ^ 1, p.status, DS_STAGE_EMPTY_TIMEOUT))) break;
-          mbar_expect_tx(bar_a_full(stage), DENSE ? (kABytes + kBBytes) : kABytes);
-          tma_load_2d(a_addr(stage), &tmap_x, kt * BK, m0, bar_a_full(stage));
-          if (DENSE) tma_load_2d(b_addr(stage), &tmap_w, kt * BK, n0, bar_a_full(stage));
+          mbar_expect_tx(bar_full(stage), DENSE ? (kABytes + kBBytes) : kABytes);
+          tma_load_2d(a_addr(stage), &tmap_x, kt * BK, m0, bar_full(stage));
+          if (DENSE) tma_load_2d(b_addr(stage), &tmap_w, kt * BK, n0, bar_full(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -153,11 +153,7 @@ vq_tensor_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
           for (int kt = 0; kt < ksteps; ++kt) {
-            if (!(ok = mbar_wait(bar_a_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
-            if (!DENSE) {
-              if (!(ok = mbar_wait(bar_b_full(stage), phase, p.status, DS_B_READY_TIMEOUT))) break;
-            }
-            if (!(ok = mbar_wait_cluster(bar_peer_full(stage), phase, p.status, DS_PEER_READY_TIMEOUT))) break;
+            if (!(ok = mbar_wait_cluster(bar_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
             tc_fence_after();
             const uint64_t ad = make_desc(a_addr(stage));
             const uint64_t bd = make_desc(b_addr(stage));
@@ -166,23 +162,20 @@ vq_tensor_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
               tc_mma_f16_pair(d_tmem, ad + 2 * k, bd + 2 * k, kIdescPair, (kt | k) != 0 ? 1u : 0u);
             // the stage is free in both CTAs once these MMAs have read it
             tc_commit_pair(bar_empty(stage));
-            tc_commit_pair(map_to_cta(bar_empty(stage), 1));
+            tc_commit_pair(bar_empty(stage) + to_peer);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
           if (!ok) break;
           tc_commit_pair(bar_acc_full(acc));
-          tc_commit_pair(map_to_cta(bar_acc_full(acc), 1));
+          tc_commit_pair(bar_acc_full(acc) + to_peer);
           if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
       } else {
         // ------------------------------- forwarder (second CTA) -----------------------------
         for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
           for (int kt = 0; kt < ksteps; ++kt) {
-            if (!(ok = mbar_wait(bar_a_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
-            if (!DENSE) {
-              if (!(ok = mbar_wait(bar_b_full(stage), phase, p.status, DS_B_READY_TIMEOUT))) break;
-            }
-            mbar_arrive_remote(map_to_cta(bar_peer_full(stage), 0));
+            if (!(ok = mbar_wait(bar_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
+            mbar_arrive_remote(bar_full(stage) + to_peer);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         }
@@ -194,8 +187,8 @@ vq_tensor_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    const uint32_t leader_acc_empty0 = map_to_cta(bar_acc_empty(0), 0);
-    const uint32_t leader_acc_empty1 = map_to_cta(bar_acc_empty(1), 0);
+    const uint32_t leader_acc_empty0 = bar_acc_empty(0) + (rank == 0 ? 0u : to_peer);
+    const uint32_t leader_acc_empty1 = bar_acc_empty(1) + (rank == 0 ? 0u : to_peer);
     for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
       const int m0 = (tile % p.m_tiles) * 256 + static_cast<int>(rank) * BM;
       const int n0 = (tile / p.m_tiles) * BN;
@@ -336,7 +329,7 @@ vq_tensor_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
                          : "memory");
           fence_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_b_full(stage));
+          if (lane == 0) mbar_arrive(bar_full(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }

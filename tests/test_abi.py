@@ -52,7 +52,10 @@ def test_workspace_sizes(lib):
     cb = lib.vqg_workspace_counter_bytes()
     # K <= 4096 decode needs no scratch; K = 8192 splits K in two chunks of fp32 partials
     assert lib.vqg_workspace_bytes(1, 11008, 4096, 4, 256, 1, 128, 0, 0) == 0
-    assert lib.vqg_workspace_bytes(16, 8192, 8192, 8, 4096, 2, 0, 0, 0) == cb + 2 * 16 * 8192 * 4
+    assert lib.vqg_workspace_bytes(16, 8192, 8192, 8, 4096, 2, 0, 0, _lib.PATH_DECODE) == cb + 2 * 16 * 8192 * 4
+    # the small-batch tensor-memory kernel (what AUTO picks for 4 < M <= 128) keeps per-tile partial sums
+    assert lib.vqg_workspace_bytes(16, 8192, 8192, 8, 4096, 2, 0, 0, _lib.PATH_SMALL_TS) > cb
+    assert lib.vqg_workspace_bytes(16, 8192, 8192 + 64, 8, 4096, 2, 0, 0, _lib.PATH_SMALL_TS) == 0   # K % 128
     # two-phase: one fp16 copy of the dequantised weights
     assert lib.vqg_workspace_bytes(256, 512, 256, 4, 256, 1, 128, 0, _lib.PATH_TWO_PHASE) == cb + 512 * 256 * 2
     assert lib.vqg_workspace_bytes(0, 0, 0, 4, 256, 1, 0, 0, 0) == 0

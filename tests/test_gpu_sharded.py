@@ -38,13 +38,17 @@ def test_column_block_with_leading_dimension():
     full = O.vq_gemm_bl(x, idx, cb, 128)
     y = torch.zeros(64, 512, dtype=torch.float16, device="cuda")
     other = torch.zeros_like(y)
+    # the workspace a rank's block needs, as the header tells callers to size it (zeroed once)
+    nbytes = _lib.load().vqg_workspace_bytes(64, 256, 512, 8, 256, 1, 128, 0, 0)
+    ws = torch.zeros(max(nbytes, 1), dtype=torch.uint8, device="cuda")
     for rank in range(2):
         idx_l, cb_l = idx[rank * 256:(rank + 1) * 256].contiguous().cuda(), cb[rank * 2:(rank + 1) * 2].contiguous().cuda()
         ptrs = [other.data_ptr(), other.data_ptr()]
         ptrs[rank] = y.data_ptr()
         arr = (ctypes.c_void_p * 2)(*ptrs)
         st = _lib.load().vqg_gemm_sharded(x.cuda().data_ptr(), idx_l.data_ptr(), cb_l.data_ptr(), arr, rank, 2, 64, 256, 512,
-                                          8, 256, 1, 128, None, 0, torch.cuda.current_stream().cuda_stream)
+                                          8, 256, 1, 128, ws.data_ptr() if nbytes else None, nbytes,
+                                          torch.cuda.current_stream().cuda_stream)
         assert st == 0
         torch.cuda.synchronize()
     # y holds both blocks (each call wrote its own block locally); `other` received both as the "peer"

@@ -81,7 +81,11 @@ int auto_path(const Problem& p, int layout) {
     return dense_supported(p.M, p.N, p.K) && p.M >= 32 ? VQG_PATH_TWO_PHASE : VQG_PATH_GENERIC;
   }
   if (p.K == 0) return VQG_PATH_GENERIC;
-  if (p.M <= 16 && decode_supported(p)) return VQG_PATH_DECODE;
+  // Up to 16 batch rows the register-level kernel wins while the codebook is small enough for its
+  // replicated shared-memory image (measured 10-12 us against 17-20 us); with large codebooks, and from
+  // 17 to 128 batch rows, the tensor-memory kernel with the even split of K is faster (29 us against 47 us).
+  if (p.M <= 16 && decode_supported(p) && (p.C <= 256 || !small_ts_supported(p))) return VQG_PATH_DECODE;
+  if (p.M <= 128 && small_ts_supported(p)) return VQG_PATH_SMALL_TS;
   if (p.M > 128 && tensor_ts_supported(p)) return VQG_PATH_TENSOR_TS;
   if (p.M > 128 && tensor_pair_supported(p)) return VQG_PATH_TENSOR_PAIR;
   if (p.M > 16 && tensor_supported(p)) return VQG_PATH_TENSOR;
@@ -112,6 +116,9 @@ int run(const Problem& p, int layout, int path, void* ws, size_t ws_bytes, cudaS
     case VQG_PATH_TENSOR_TS:
       if (layout != VQG_LAYOUT_BL) return VQG_ERR_UNSUPPORTED;
       return launch_tensor_ts(p, s);
+    case VQG_PATH_SMALL_TS:
+      if (layout != VQG_LAYOUT_BL) return VQG_ERR_UNSUPPORTED;
+      return launch_small_ts(p, ws, ws_bytes, s);
     case VQG_PATH_TWO_PHASE: {
       if (!dense_supported(p.M, p.N, p.K)) return VQG_ERR_UNSUPPORTED;
       const size_t need = two_phase_bytes(p.N, p.K);
@@ -164,6 +171,7 @@ size_t vqg_workspace_bytes(int M, int N, int K, int v, int C, int idx_bytes, int
   Problem p = make_problem(dummy, dummy, dummy, dummy, M, N, K, v, C, idx_bytes, rows_per_codebook, N);
   if (path == VQG_PATH_AUTO) path = auto_path(p, layout);
   if (path == VQG_PATH_DECODE) return decode_workspace_bytes(p);
+  if (path == VQG_PATH_SMALL_TS) return small_ts_workspace_bytes(p);
   if (path == VQG_PATH_TWO_PHASE) return two_phase_bytes(N, K);
   return 0;
 }

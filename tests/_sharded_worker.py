@@ -21,7 +21,14 @@ def main():
     ok = True
     for (M, K, N, v, C, rpc) in [(256, 512, 1024, 4, 256, 128), (4, 1024, 512, 8, 256, 128), (512, 1024, 2048, 8, 256, 128)]:
         x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=5)
-        single = V.vq_gemm(x.to(dev), idx.to(dev), cb.to(dev), rows_per_codebook=rpc, layout="bl")
+        # the single-GPU result, block by block: a block computed alone has the same shape, hence the same
+        # schedule and summation order, as the one a rank computes (the whole-N product may cut its K loops
+        # elsewhere and differ in the last bits)
+        blocks = []
+        for r in range(world):
+            idx_r, cb_r = shard_weights(idx, cb, world, r, rpc)
+            blocks.append(V.vq_gemm(x.to(dev), idx_r.to(dev), cb_r.to(dev), rows_per_codebook=rpc, layout="bl"))
+        single = torch.cat(blocks, dim=1)
         idx_l, cb_l = shard_weights(idx, cb, world, rank, rpc)
         for mode in ("peer", "nccl"):
             op = ShardedVQGemm(M, N, mode=mode, device=dev)

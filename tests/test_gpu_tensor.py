@@ -110,3 +110,33 @@ def test_fused_equals_two_phase_bitwise():
     a = run_bl(V, x, idx, cb, 128, path="tensor")
     b = run_bl(V, x, idx, cb, 128, path="two_phase")
     assert torch.equal(bits(a), bits(b))
+
+
+@pytest.mark.parametrize("M,K,N,v", [
+    (700, 2048, 1024, 4),     # 12 tiles x 8 units over 74 CTA pairs: tiles shared by up to 8 pairs
+    (520, 4096, 768, 8),      # 9 tiles x 8 units: one unit per pair
+    (1024, 4096, 2304, 8),    # 288 units: every pair ends in the middle of a tile
+])
+def test_even_split_of_k_loops_matches_whole_tiles(M, K, N, v):
+    # with a workspace the K loops are dealt out evenly over the CTA pairs and shared tiles are summed
+    # from fp32 partials in pair order; without one every tile is computed by a single pair
+    import ctypes
+    from vq_gemm_b200 import _lib
+    x, idx, cb = O.make_bl_inputs(M, K, N, v, 256, 128, seed=M + N, cb_sigma=0.05)
+    ref = O.vq_gemm_bl(x, idx, cb, 128)
+    outs = [run_bl(V, x, idx, cb, 128, path="tensor_ts") for _ in range(3)]
+    assert_within_tolerance(outs[0], ref)
+    for o in outs[1:]:
+        assert torch.equal(bits(o), bits(outs[0]))      # the counters are back at zero; order is fixed
+    lib = _lib.load()
+    assert lib.vqg_workspace_bytes(M, N, K, v, 256, 1, 128, 0, _lib.PATHS["tensor_ts"]) > lib.vqg_workspace_counter_bytes()
+    xd, idd, cbd = x.cuda(), idx.cuda(), cb.cuda()
+    y = torch.empty(M, N, dtype=torch.float16, device="cuda")
+    st = lib.vqg_gemm_path(xd.data_ptr(), idd.data_ptr(), cbd.data_ptr(), y.data_ptr(), M, N, K, v, 256, 1, 128, 0,
+                           _lib.PATHS["tensor_ts"], None, 0, torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    torch.cuda.synchronize()
+    assert V.device_status() == 0
+    assert_within_tolerance(y.cpu(), ref)
+    # the two schedules round differently only in the last fp32 bits of the partial sums
+    assert float((y.cpu().float() - outs[0].float()).abs().max()) <= 2e-3 * float(ref.float().abs().max())

@@ -115,7 +115,7 @@ int run(const Problem& p, int layout, int path, void* ws, size_t ws_bytes, cudaS
       return launch_tensor_pair(p, s);
     case VQG_PATH_TENSOR_TS:
       if (layout != VQG_LAYOUT_BL) return VQG_ERR_UNSUPPORTED;
-      return launch_tensor_ts(p, s);
+      return launch_tensor_ts(p, ws, ws_bytes, s);
     case VQG_PATH_SMALL_TS:
       if (layout != VQG_LAYOUT_BL) return VQG_ERR_UNSUPPORTED;
       return launch_small_ts(p, ws, ws_bytes, s);
@@ -172,6 +172,7 @@ size_t vqg_workspace_bytes(int M, int N, int K, int v, int C, int idx_bytes, int
   if (path == VQG_PATH_AUTO) path = auto_path(p, layout);
   if (path == VQG_PATH_DECODE) return decode_workspace_bytes(p);
   if (path == VQG_PATH_SMALL_TS) return small_ts_workspace_bytes(p);
+  if (path == VQG_PATH_TENSOR_TS) return tensor_ts_workspace_bytes(p);
   if (path == VQG_PATH_TWO_PHASE) return two_phase_bytes(N, K);
   return 0;
 }

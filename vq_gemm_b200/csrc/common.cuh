@@ -67,7 +67,8 @@ int launch_tensor_pair(const Problem& p, cudaStream_t s);   // CTA-pair (cta_gro
 int launch_dense_pair(const __half* x, const __half* w_nk, __half* y, int M, int N, int K, long long ld_y,
                       int n_peers, __half* const* peer_y, cudaStream_t s);
 bool tensor_ts_supported(const Problem& p);
-int launch_tensor_ts(const Problem& p, cudaStream_t s);     // weights through tensor memory (A operand)
+size_t tensor_ts_workspace_bytes(const Problem& p);
+int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s);     // weights through tensor memory (A operand)
 bool small_ts_supported(const Problem& p);
 size_t small_ts_workspace_bytes(const Problem& p);
 int launch_small_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s);   // M <= 128, stream-K

@@ -62,9 +62,39 @@ struct TsParams {
   int rows_per_cb;
   long long ld_y;
   int m_tiles, n_tiles;      // in 256 x 256 pair tiles
+  // Schedule: the K loop of every tile is cut into `units_per_tile` units of `unit_stages` pipeline stages;
+  // the tiles*units_per_tile units are dealt out evenly and contiguously, pair b taking
+  // [b*q + min(b, r), +q + (b < r)).  units_per_tile == 1 keeps whole tiles per pair (no workspace needed).
+  int unit_stages, units_per_tile, q, r;
+  float* ws_partial;         // [pair][first/last segment][rank][256 batch rows][128 weight rows] fp32
+  int* ws_counter;           // [tile][rank] arrivals of contributors; zero between calls
   int n_peers;
   __half* peer_y[8];
 };
+
+__device__ __forceinline__ int pair_begin(int b, int q, int r) { return b * q + (b < r ? b : r); }
+// pair that owns unit u
+__device__ __forceinline__ int pair_of_unit(int u, int q, int r) {
+  const int big = r * (q + 1);
+  return u < big ? u / (q + 1) : r + (u - big) / q;
+}
+
+// One contiguous piece of a pair's range inside one tile.
+struct Segment {
+  int tile, kt_begin, kt_end;   // pipeline stages [kt_begin, kt_end) of the tile's K loop
+  bool whole;                   // the piece is the whole tile
+  int next;                     // first unit after the piece
+};
+__device__ __forceinline__ Segment segment_at(int u, int u_end, const TsParams& p) {
+  Segment g;
+  g.tile = u / p.units_per_tile;
+  const int t0 = g.tile * p.units_per_tile;
+  g.next = min(u_end, t0 + p.units_per_tile);
+  g.kt_begin = (u - t0) * p.unit_stages;
+  g.kt_end = (g.next - t0) * p.unit_stages;
+  g.whole = (u == t0) && (g.next == t0 + p.units_per_tile);
+  return g;
+}
 
 // kind::f16, A = B = fp16, D = fp32, both K-major, M = 256 weight rows (pair), N = 256 batch rows
 constexpr uint32_t kIdescTs = (1u << 4) | (static_cast<uint32_t>(BM >> 3) << 17) | (static_cast<uint32_t>(BN >> 4) << 24);
@@ -120,9 +150,7 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();         // 0 = pair leader
   const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int ksubs = p.K / BK;        // 64-wide K sub-steps
-  const int ksteps = ksubs / KS;     // pipeline stages per tile
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int u_begin = pair_begin(pair_id, p.q, p.r), u_end = pair_begin(pair_id + 1, p.q, p.r);
 
   auto x_addr = [&](int s) { return base + s * kStageXBytes; };
   // full[s]: this CTA's X half has landed (TMA, 1 arrival + bytes) and its 4 dequant warps have written
@@ -168,9 +196,11 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
-        const int m0 = (tile % p.m_tiles) * BM + static_cast<int>(rank) * BMH;
-        for (int kt = 0; kt < ksteps; ++kt) {
+      for (int unit = u_begin; ok && unit < u_end;) {
+        const Segment g = segment_at(unit, u_end, p);
+        unit = g.next;
+        const int m0 = (g.tile % p.m_tiles) * BM + static_cast<int>(rank) * BMH;
+        for (int kt = g.kt_begin; kt < g.kt_end; ++kt) {
           if (!(ok = mbar_wait_cluster(bar_empty(stage), phase ^ 1, p.status, DS_STAGE_EMPTY_TIMEOUT))) break;
           mbar_expect_tx(bar_full(stage), kStageXBytes);
 #pragma unroll
@@ -188,10 +218,12 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
       if (rank == 0) {
         // ------------------------------- MMA issuer (pair leader) ---------------------------
         uint32_t acc_phase = 0;
-        for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
+        for (int unit = u_begin; ok && unit < u_end;) {
+          const Segment g = segment_at(unit, u_end, p);
+          unit = g.next;
           if (!(ok = mbar_wait_cluster(bar_acc_empty, acc_phase ^ 1, p.status, DS_ACC_EMPTY_TIMEOUT))) break;
           tc_fence_after();
-          for (int kt = 0; kt < ksteps; ++kt) {
+          for (int kt = g.kt_begin; kt < g.kt_end; ++kt) {
             if (!(ok = mbar_wait_cluster(bar_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
             tc_fence_after();
             const uint32_t a_t = tmem_base + kAccCols + static_cast<uint32_t>(stage) * kStageCols;
@@ -201,7 +233,7 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
 #pragma unroll
               for (int k = 0; k < BK / 16; ++k)   // 16 K values = 8 columns of A, 32 bytes of the X rows
                 tc_mma_f16_pair_ts(tmem_base, a_t + u * kAColsPerStage + 8 * k, bd + 2 * k, kIdescTs,
-                                   (kt | u | k) != 0 ? 1u : 0u);
+                                   ((kt - g.kt_begin) | u | k) != 0 ? 1u : 0u);
             }
             // the stage (X tile and A columns) is free in both CTAs once these MMAs have read it
             tc_commit_pair(bar_empty(stage));
@@ -215,8 +247,10 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
         }
       } else {
         // ------------------------------- forwarder (second CTA) -----------------------------
-        for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
-          for (int kt = 0; kt < ksteps; ++kt) {
+        for (int unit = u_begin; ok && unit < u_end;) {
+          const Segment g = segment_at(unit, u_end, p);
+          unit = g.next;
+          for (int kt = g.kt_begin; kt < g.kt_end; ++kt) {
             if (!(ok = mbar_wait(bar_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
             mbar_arrive_remote(bar_full(stage) + to_peer);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -240,25 +274,85 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
       epi_phase ^= 1;
       return done;
     };
-    for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
+    volatile int* last_flag = reinterpret_cast<volatile int*>(base_ptr + L::kTmemSlot + 8);
+    constexpr size_t kPartialFloats = static_cast<size_t>(BM) * BNH;   // one CTA's share of a pair tile
+    for (int unit = u_begin; ok && unit < u_end;) {
+      const Segment g = segment_at(unit, u_end, p);
+      const int tile = g.tile;
       const int m0 = (tile % p.m_tiles) * BM;
       const int n0 = (tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH;
       if (!(ok = mbar_wait_cluster(bar_acc_full, acc_phase, p.status, DS_ACC_FULL_TIMEOUT))) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      if (g.whole) {
 #pragma unroll 1
-      for (int c = 0; c < BM / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_row + c * 32, r);
-        __half* col = reinterpret_cast<__half*>(stg) + (c * 32) * 128 + quarter * 32 + lane;   // T[m][weight row]
+        for (int c = 0; c < BM / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+          __half* col = reinterpret_cast<__half*>(stg) + (c * 32) * 128 + quarter * 32 + lane;   // T[m][weight row]
 #pragma unroll
-        for (int j = 0; j < 32; ++j) col[j * 128] = __float2half_rn(__uint_as_float(r[j]));
+          for (int j = 0; j < 32; ++j) col[j * 128] = __float2half_rn(__uint_as_float(r[j]));
+        }
+      } else {
+        // a piece of a tile: the fp32 partial goes to this pair's slot (0 when the pair's range begins
+        // inside the tile, 1 when it begins at or before the tile's first unit)
+        const int slot = (unit > tile * p.units_per_tile) ? 0 : 1;
+        float* part = p.ws_partial + ((static_cast<size_t>(pair_id) * 2 + slot) * 2 + rank) * kPartialFloats + quarter * 32 + lane;
+#pragma unroll 1
+        for (int c = 0; c < BM / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) __stcg(part + static_cast<size_t>(c * 32 + j) * BNH, __uint_as_float(r[j]));
+        }
       }
       // tensor memory has been read: the next tile's MMAs may overwrite it while Y is written out
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(leader_acc_empty);
       acc_phase ^= 1;
+      unit = g.next;
+      if (!g.whole) {
+        // The contributor that arrives last sums the partials of all contributors (consecutive pairs) in
+        // pair order, so the result does not depend on who that is.
+        const int t0u = tile * p.units_per_tile;
+        const int b_first = pair_of_unit(t0u, p.q, p.r);
+        const int b_last = pair_of_unit(t0u + p.units_per_tile - 1, p.q, p.r);
+        __threadfence();
+        if (!(ok = epi_sync())) break;   // all four warps' partials are written and fenced
+        if (warp == 2 && lane == 0) {
+          int* ctr = p.ws_counter + tile * 2 + static_cast<int>(rank);
+          const int old = atomicAdd(ctr, 1);
+          const int last = (old == b_last - b_first);
+          if (last) *ctr = 0;            // leave the counter zero for the next call
+          *last_flag = last;
+        }
+        if (!(ok = epi_sync())) break;
+        const int last = *last_flag;
+        if (!last) {
+          if (!(ok = epi_sync())) break; // the flag is rewritten only after everyone has read it
+          continue;
+        }
+        __threadfence();
+#pragma unroll 1
+        for (int c = 0; c < BM / 32; ++c) {
+          float sum[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum[j] = 0.f;
+          for (int b = b_first; b <= b_last; ++b) {
+            const int slot = (pair_begin(b, p.q, p.r) > t0u) ? 0 : 1;
+            const float* src = p.ws_partial + ((static_cast<size_t>(b) * 2 + slot) * 2 + rank) * kPartialFloats + quarter * 32 + lane;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __ldcg(src + static_cast<size_t>(c * 32 + j) * BNH);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sum[j] += v[j];
+          }
+          __half* col = reinterpret_cast<__half*>(stg) + (c * 32) * 128 + quarter * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) col[j * 128] = __float2half_rn(sum[j]);
+        }
+      }
       if (!(ok = epi_sync())) break;   // the whole tile is in shared memory
       {
         const int half_row = lane >> 4, chunk = lane & 15;   // a warp instruction covers two 256-byte rows
@@ -301,8 +395,10 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
       dq_phase ^= 1;
       return done;
     };
-    for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
-      const int n_half0 = (tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH;
+    for (int unit = u_begin; ok && unit < u_end;) {
+      const Segment g = segment_at(unit, u_end, p);
+      unit = g.next;
+      const int n_half0 = (g.tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH;
       const int n = n_half0 + r;
       const bool row_valid = n < p.N;
       const int group = (n_half0 < p.N ? n_half0 : p.N - 1) / p.rows_per_cb;
@@ -333,16 +429,18 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
           dst[4 * q] = t.x; dst[4 * q + 1] = t.y; dst[4 * q + 2] = t.z; dst[4 * q + 3] = t.w;
         }
       };
-      const int ngran = (ksubs + GSTEPS - 1) / GSTEPS;
-      load_granule(0, nxt);
-      for (int gi = 0; ok && gi < ngran; ++gi) {
+      // a unit is a whole number of 64-byte index granules unless it is the whole tile
+      const int ks_begin = g.kt_begin * KS, ks_end = g.kt_end * KS;    // 64-wide sub-steps of the piece
+      const int gi_begin = ks_begin / GSTEPS, ngran = (ks_end + GSTEPS - 1) / GSTEPS;
+      load_granule(gi_begin, nxt);
+      for (int gi = gi_begin; ok && gi < ngran; ++gi) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) cur[i] = nxt[i];
         if (gi + 1 < ngran) load_granule(gi + 1, nxt);
 #pragma unroll
         for (int st = 0; st < GSTEPS; ++st) {
           const int ks = gi * GSTEPS + st;                 // 64-wide sub-step; KS of them make a stage
-          if (ks >= ksubs) break;
+          if (ks >= ks_end) break;
           // 64 K values of this row: 32 registers, in K order = 32 columns of the A stage
           uint32_t a[32];
           if (V == 4) {
@@ -443,7 +541,25 @@ bool tensor_ts_supported(const Problem& p) {
   return true;
 }
 
-int launch_tensor_ts(const Problem& p, cudaStream_t s) {
+namespace {
+int sm_count() {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms > 1 ? sms : 148;
+}
+constexpr size_t kPairPartialBytes = 2 /*slots*/ * 2 /*ranks*/ * static_cast<size_t>(BM) * BNH * sizeof(float);
+// pipeline stages per schedule unit: a whole number of the dequant threads' 64-byte index granules
+int unit_stages_for(int v) { return v == 4 ? 2 : 4; }
+}  // namespace
+
+// Counters plus two fp32 partial tiles per CTA pair: with it the K loops are dealt out evenly over the
+// pairs (no partly filled last wave); without it every tile is computed by one pair.
+size_t tensor_ts_workspace_bytes(const Problem& p) {
+  if (!tensor_ts_supported(p)) return 0;
+  return kCounterBytes + static_cast<size_t>(sm_count() / 2) * kPairPartialBytes;
+}
+
+int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s) {
   if (!tensor_ts_supported(p)) return VQG_ERR_UNSUPPORTED;
   CUtensorMap mx;
   if (!make_map(&mx, p.x, p.M, p.K)) return VQG_ERR_LAUNCH;
@@ -459,17 +575,28 @@ int launch_tensor_ts(const Problem& p, cudaStream_t s) {
   tp.n_tiles = (p.N + BN - 1) / BN;
   tp.n_peers = p.n_peers;
   for (int i = 0; i < 8; ++i) tp.peer_y[i] = p.peer_y[i];
+  const int max_pairs = sm_count() / 2;
+  const int tiles = tp.m_tiles * tp.n_tiles;
+  const int ksteps = p.K / (2 * BK);
+  const int us = unit_stages_for(p.v);
+  const bool split = ws && reinterpret_cast<uintptr_t>(ws) % 256 == 0 &&
+                     ws_bytes >= kCounterBytes + static_cast<size_t>(max_pairs) * kPairPartialBytes &&
+                     ksteps % us == 0 && ksteps / us > 1 && tiles % max_pairs != 0 &&
+                     static_cast<size_t>(tiles) * 2 * sizeof(int) <= kCounterBytes;
+  tp.unit_stages = split ? us : ksteps;
+  tp.units_per_tile = split ? ksteps / us : 1;
+  const long long units = static_cast<long long>(tiles) * tp.units_per_tile;
+  if (units > 0x7fffffffLL) return VQG_ERR_UNSUPPORTED;
+  const int pairs = units < max_pairs ? static_cast<int>(units) : max_pairs;
+  tp.q = static_cast<int>(units / pairs);
+  tp.r = static_cast<int>(units % pairs);
+  tp.ws_counter = split ? static_cast<int*>(ws) : nullptr;
+  tp.ws_partial = split ? reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + kCounterBytes) : nullptr;
   constexpr int S = 4, KS = 2;   // 4 stages of 128 K values: 128 KiB of X tiles, 4 x 64 TMEM columns of A
   const size_t smem = TsSmem<S, KS>::kTotal + 1024;
   auto launch = [&](auto kernel) -> int {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return VQG_ERR_LAUNCH;
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int tiles = tp.m_tiles * tp.n_tiles;
-    const int max_pairs = sms / 2;
-    const int pairs = tiles < max_pairs ? tiles : max_pairs;
     kernel<<<2 * pairs, kThreads, smem, s>>>(mx, tp);
     count_launch();
     return cuda_status(cudaGetLastError());

@@ -83,16 +83,34 @@ __device__ __forceinline__ int pair_of_unit(int u, int q, int r) {
 struct Segment {
   int tile, kt_begin, kt_end;   // pipeline stages [kt_begin, kt_end) of the tile's K loop
   bool whole;                   // the piece is the whole tile
-  int next;                     // first unit after the piece
+  int start;                    // first unit of the piece
 };
-__device__ __forceinline__ Segment segment_at(int u, int u_end, const TsParams& p) {
+// Takes the next piece off the remaining range [lo, hi).  A range that ends inside a tile gives up that
+// last piece first (`from_back`, once), then is walked from the front: both pieces of a tile shared by
+// pairs b and b+1 are then computed at the start of the kernel, the sum of their partials overlaps the
+// main loop of whoever arrives second, and every pair ends on a whole tile at the same time.
+__device__ __forceinline__ Segment take_segment(int& lo, int& hi, bool& from_back, const TsParams& p) {
   Segment g;
-  g.tile = u / p.units_per_tile;
+  int end;
+  const bool rev = from_back;
+  from_back = false;
+  if (!rev) {
+    g.tile = lo / p.units_per_tile;
+    const int t0 = g.tile * p.units_per_tile;
+    g.start = lo;
+    end = min(hi, t0 + p.units_per_tile);
+    lo = end;
+  } else {
+    g.tile = (hi - 1) / p.units_per_tile;
+    const int t0 = g.tile * p.units_per_tile;
+    g.start = max(lo, t0);
+    end = hi;
+    hi = g.start;
+  }
   const int t0 = g.tile * p.units_per_tile;
-  g.next = min(u_end, t0 + p.units_per_tile);
-  g.kt_begin = (u - t0) * p.unit_stages;
-  g.kt_end = (g.next - t0) * p.unit_stages;
-  g.whole = (u == t0) && (g.next == t0 + p.units_per_tile);
+  g.kt_begin = (g.start - t0) * p.unit_stages;
+  g.kt_end = (end - t0) * p.unit_stages;
+  g.whole = (g.start == t0) && (end == t0 + p.units_per_tile);
   return g;
 }
 
@@ -151,6 +169,7 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
   const uint32_t rank = cluster_ctarank();         // 0 = pair leader
   const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int u_begin = pair_begin(pair_id, p.q, p.r), u_end = pair_begin(pair_id + 1, p.q, p.r);
+  const bool ends_inside_tile = (u_end % p.units_per_tile) != 0;
 
   auto x_addr = [&](int s) { return base + s * kStageXBytes; };
   // full[s]: this CTA's X half has landed (TMA, 1 arrival + bytes) and its 4 dequant warps have written
@@ -196,9 +215,9 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int unit = u_begin; ok && unit < u_end;) {
-        const Segment g = segment_at(unit, u_end, p);
-        unit = g.next;
+      bool from_back = ends_inside_tile;
+      for (int lo = u_begin, hi = u_end; ok && lo < hi;) {
+        const Segment g = take_segment(lo, hi, from_back, p);
         const int m0 = (g.tile % p.m_tiles) * BM + static_cast<int>(rank) * BMH;
         for (int kt = g.kt_begin; kt < g.kt_end; ++kt) {
           if (!(ok = mbar_wait_cluster(bar_empty(stage), phase ^ 1, p.status, DS_STAGE_EMPTY_TIMEOUT))) break;
@@ -218,9 +237,9 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
       if (rank == 0) {
         // ------------------------------- MMA issuer (pair leader) ---------------------------
         uint32_t acc_phase = 0;
-        for (int unit = u_begin; ok && unit < u_end;) {
-          const Segment g = segment_at(unit, u_end, p);
-          unit = g.next;
+        bool from_back = ends_inside_tile;
+        for (int lo = u_begin, hi = u_end; ok && lo < hi;) {
+          const Segment g = take_segment(lo, hi, from_back, p);
           if (!(ok = mbar_wait_cluster(bar_acc_empty, acc_phase ^ 1, p.status, DS_ACC_EMPTY_TIMEOUT))) break;
           tc_fence_after();
           for (int kt = g.kt_begin; kt < g.kt_end; ++kt) {
@@ -247,9 +266,9 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
         }
       } else {
         // ------------------------------- forwarder (second CTA) -----------------------------
-        for (int unit = u_begin; ok && unit < u_end;) {
-          const Segment g = segment_at(unit, u_end, p);
-          unit = g.next;
+        bool from_back = ends_inside_tile;
+        for (int lo = u_begin, hi = u_end; ok && lo < hi;) {
+          const Segment g = take_segment(lo, hi, from_back, p);
           for (int kt = g.kt_begin; kt < g.kt_end; ++kt) {
             if (!(ok = mbar_wait(bar_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
             mbar_arrive_remote(bar_full(stage) + to_peer);
@@ -276,8 +295,9 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
     };
     volatile int* last_flag = reinterpret_cast<volatile int*>(base_ptr + L::kTmemSlot + 8);
     constexpr size_t kPartialFloats = static_cast<size_t>(BM) * BNH;   // one CTA's share of a pair tile
-    for (int unit = u_begin; ok && unit < u_end;) {
-      const Segment g = segment_at(unit, u_end, p);
+    bool from_back = ends_inside_tile;
+    for (int lo = u_begin, hi = u_end; ok && lo < hi;) {
+      const Segment g = take_segment(lo, hi, from_back, p);
       const int tile = g.tile;
       const int m0 = (tile % p.m_tiles) * BM;
       const int n0 = (tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH;
@@ -296,7 +316,7 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
       } else {
         // a piece of a tile: the fp32 partial goes to this pair's slot (0 when the pair's range begins
         // inside the tile, 1 when it begins at or before the tile's first unit)
-        const int slot = (unit > tile * p.units_per_tile) ? 0 : 1;
+        const int slot = (g.start > tile * p.units_per_tile) ? 0 : 1;
         float* part = p.ws_partial + ((static_cast<size_t>(pair_id) * 2 + slot) * 2 + rank) * kPartialFloats + quarter * 32 + lane;
 #pragma unroll 1
         for (int c = 0; c < BM / 32; ++c) {
@@ -311,7 +331,6 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(leader_acc_empty);
       acc_phase ^= 1;
-      unit = g.next;
       if (!g.whole) {
         // The contributor that arrives last sums the partials of all contributors (consecutive pairs) in
         // pair order, so the result does not depend on who that is.
@@ -334,23 +353,38 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
           continue;
         }
         __threadfence();
+        {
+          // thread -> four consecutive weight rows of one batch row; 16 independent 16-byte loads in flight
+          // per thread and contributor (a dependent chain of L2 round trips would dominate otherwise)
+          const int et = quarter * 32 + lane;          // 0..127
+          const int row4 = (et & 31) * 4, msub = et >> 5;
+          constexpr int INFL = 16;
 #pragma unroll 1
-        for (int c = 0; c < BM / 32; ++c) {
-          float sum[32];
+          for (int i0 = 0; i0 < BM / 4; i0 += INFL) {
+            float4 sum[INFL];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) sum[j] = 0.f;
-          for (int b = b_first; b <= b_last; ++b) {
-            const int slot = (pair_begin(b, p.q, p.r) > t0u) ? 0 : 1;
-            const float* src = p.ws_partial + ((static_cast<size_t>(b) * 2 + slot) * 2 + rank) * kPartialFloats + quarter * 32 + lane;
-            float v[32];
+            for (int j = 0; j < INFL; ++j) sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int b = b_first; b <= b_last; ++b) {
+              const int slot = (pair_begin(b, p.q, p.r) > t0u) ? 0 : 1;
+              const float* src = p.ws_partial + ((static_cast<size_t>(b) * 2 + slot) * 2 + rank) * kPartialFloats + row4;
+              float4 v[INFL];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __ldcg(src + static_cast<size_t>(c * 32 + j) * BNH);
+              for (int j = 0; j < INFL; ++j)
+                v[j] = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(4 * (i0 + j) + msub) * BNH));
 #pragma unroll
-            for (int j = 0; j < 32; ++j) sum[j] += v[j];
+              for (int j = 0; j < INFL; ++j) {
+                sum[j].x += v[j].x; sum[j].y += v[j].y; sum[j].z += v[j].z; sum[j].w += v[j].w;
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < INFL; ++j) {
+              const __half2 lo2 = __floats2half2_rn(sum[j].x, sum[j].y), hi2 = __floats2half2_rn(sum[j].z, sum[j].w);
+              uint2 o;
+              o.x = *reinterpret_cast<const uint32_t*>(&lo2);
+              o.y = *reinterpret_cast<const uint32_t*>(&hi2);
+              *reinterpret_cast<uint2*>(stg + (4 * (i0 + j) + msub) * 256 + row4 * 2) = o;
+            }
           }
-          __half* col = reinterpret_cast<__half*>(stg) + (c * 32) * 128 + quarter * 32 + lane;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) col[j * 128] = __float2half_rn(sum[j]);
         }
       }
       if (!(ok = epi_sync())) break;   // the whole tile is in shared memory
@@ -395,9 +429,9 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
       dq_phase ^= 1;
       return done;
     };
-    for (int unit = u_begin; ok && unit < u_end;) {
-      const Segment g = segment_at(unit, u_end, p);
-      unit = g.next;
+    bool from_back = ends_inside_tile;
+    for (int lo = u_begin, hi = u_end; ok && lo < hi;) {
+      const Segment g = take_segment(lo, hi, from_back, p);
       const int n_half0 = (g.tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH;
       const int n = n_half0 + r;
       const bool row_valid = n < p.N;

@@ -4,11 +4,14 @@ Y[M, N].  One process per GPU, ``torch.distributed`` for the plumbing.
 
 Two ways of assembling Y:
 
-``mode="peer"``   Y lives in symmetric memory (one [M, N] buffer per rank, peer-mapped over
-                  NVLink).  The GEMM epilogue stores each finished tile into every rank's buffer
+``mode="peer"``   Y lives in symmetric memory (two [M, N] buffers per rank, used in turn, peer-mapped
+                  over NVLink).  The GEMM epilogue stores each finished tile into every rank's buffer
                   with ordinary global stores (``vqg_gemm_sharded``), so the exchange overlaps the
-                  main loop; a device-side barrier across ranks ends the step.  No TMA and no
-                  multicast touch peer memory.
+                  main loop; one device-side barrier across ranks ends the step.  A step writes the
+                  buffer that was last written two steps ago: every rank passed the previous step's
+                  barrier after reading it, so no barrier is needed before the stores.  The returned
+                  tensor is therefore valid until the second call after it.  No TMA and no multicast
+                  touch peer memory.
 ``mode="nccl"``   each rank computes its [M, N/G] block, NCCL all-gathers the blocks into
                   [G, M, N/G] and a re-layout copy interleaves them into [M, N].
 
@@ -81,11 +84,13 @@ class ShardedVQGemm:
             self._ptrs = [self.y.data_ptr()]
         elif mode == "peer":
             import torch.distributed._symmetric_memory as symm_mem
-            self.y = symm_mem.empty((M, N), dtype=torch.float16, device=self.device)
-            self._hdl = symm_mem.rendezvous(self.y, self.group)
+            self._ybuf = symm_mem.empty((2, M, N), dtype=torch.float16, device=self.device)
+            self._hdl = symm_mem.rendezvous(self._ybuf, self.group)
             self._ptrs = [int(p) for p in self._hdl.buffer_ptrs]
-            if self._ptrs[self.rank] != self.y.data_ptr():
+            if self._ptrs[self.rank] != self._ybuf.data_ptr():
                 raise RuntimeError("symmetric memory: local buffer pointer mismatch")
+            self._step = 0
+            self.y = self._ybuf[0]
         else:
             self.y = torch.empty((M, N), dtype=torch.float16, device=self.device)
             self._block = torch.empty((M, self.n_local), dtype=torch.float16, device=self.device)
@@ -113,9 +118,12 @@ class ShardedVQGemm:
         if self.mode == "peer" or self.world == 1:
             ws_ptr, ws_n = self._workspace(
                 lib.vqg_workspace_bytes(M, self.n_local, K, v, C, ib, rows_per_codebook, _lib.LAYOUT_BL, _lib.PATH_AUTO))
-            arr = (ctypes.c_void_p * self.world)(*self._ptrs)
+            off = 0
             if self._hdl is not None:
-                self._hdl.barrier()  # every rank has finished reading the previous step's Y
+                self.y = self._ybuf[self._step & 1]
+                off = (self._step & 1) * self.M * self.N * 2
+                self._step += 1
+            arr = (ctypes.c_void_p * self.world)(*[p + off for p in self._ptrs])
             st = lib.vqg_gemm_sharded(x.data_ptr(), idx_local.data_ptr(), cb_local.data_ptr(), arr, self.rank,
                                       self.world, M, self.n_local, K, v, C, ib, rows_per_codebook, ws_ptr, ws_n, stream)
             _lib.check(st, "vqg_gemm_sharded")

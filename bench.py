@@ -143,25 +143,29 @@ def _single_shape(V, shape, peaks, steps, warmup):
         step()
     torch.cuda.synchronize()
     # CUDA-graph replay of `ring` launches removes host launch gaps for the microsecond kernels
-    g = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(g):
-            for i in range(ring):
-                V.vq_gemm(x, idxs[i], cb, rows_per_codebook=shape.rows_per_codebook, layout="bl", out=out)
-    torch.cuda.current_stream().wait_stream(side)
-    reps = max(3, steps // ring)
-    for _ in range(3):
-        g.replay()
-    torch.cuda.synchronize()
+    def graph_ms(path):
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g):
+                for i in range(ring):
+                    V.vq_gemm(x, idxs[i], cb, rows_per_codebook=shape.rows_per_codebook, layout="bl", path=path, out=out)
+        torch.cuda.current_stream().wait_stream(side)
+        reps = max(3, steps // ring)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = _events()
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (reps * ring)
+
+    ms = graph_ms("auto")
     e0, e1 = _events()
-    e0.record()
-    for _ in range(reps):
-        g.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / (reps * ring)
     res = {"workload": shape.name, "M": shape.M, "K": shape.K, "N": shape.N, "v": shape.v, "C": shape.C,
            "us_per_launch": ms * 1e3, "tflops": shape.flops / ms / 1e9, "gbs_compressed": shape.bytes_algorithmic / ms / 1e6,
            "ring_buffers": ring, "timing": "cuda-graph replay, CUDA events"}
@@ -169,6 +173,14 @@ def _single_shape(V, shape, peaks, steps, warmup):
         a = shape.bytes_algorithmic / ms / 1e6
         res["roofline"] = {"bound": "hbm", "achieved": a, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                            "frac": a / peaks["hbm_gbs"], "frac_of_nominal_8000": a / 8000.0}
+        # both small-batch kernels, whichever the library picks by itself for this shape
+        for alt in ("decode", "small_ts"):
+            try:
+                V.vq_gemm(x, idx, cb, rows_per_codebook=shape.rows_per_codebook, layout="bl", path=alt, out=out)
+            except RuntimeError:
+                continue
+            ams = graph_ms(alt)
+            res["path_" + alt] = {"us": ams * 1e3, "gbs_compressed": shape.bytes_algorithmic / ams / 1e6}
     else:
         a = shape.flops / ms / 1e9
         res["roofline"] = {"bound": "tensor", "achieved": a, "peak": peaks["tflops"], "unit": "TFLOP/s",
@@ -453,7 +465,7 @@ def main():
         ach = kflops / kms / 1e9
         roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"],
                 # ncu dram__bytes_read+write per launch of this kernel on this workload (profiles/), N=1 only
-                "traffic": 157.6e6 if (world == 1 and shape.name == "c5_mlp70b") else None,
+                "traffic": 295.6e6 if (world == 1 and shape.name == "c5_mlp70b") else None,
                 "traffic_algorithmic": shape.bytes_algorithmic if world == 1 else None,
                 "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
                 "frac_of_sustained": ach / peaks["tflops_sustained"] if peaks["tflops_sustained"] else None,

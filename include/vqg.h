@@ -147,6 +147,32 @@ VQG_API int vqg_gemm_small_batch_noalloc(const void* x, const void* idx, const v
                                  int M, int N, int K, int v, int C, int idx_bytes,
                                  int rows_per_codebook, void* stream);
 
+/* ---- Quantiser: the step before the product ------------------------------------------------
+ * The reference has no quantiser (bench.py:83-85 fills `w` with random bytes); these entry points
+ * turn a dense fp16 weight W[N, K] into the BL format on the GPU.  All pointers are device
+ * pointers; W must be 16-byte aligned; v in {2, 4, 8}; C <= 256 with 1-byte indices, any C whose
+ * fp32 copy (C*v*4 bytes) fits 200 KiB of shared memory with 2-byte indices.
+ *
+ * vqg_quantize_assign: idx[n, j] = the entry of codebook g(n) nearest to W[n, jv : jv+v], where
+ *   distance = sum over i ascending of (float(w_i) - float(c_i))^2 with every subtraction,
+ *   multiplication and addition rounded to fp32 separately (no fused multiply-add), and the
+ *   lowest index wins among equal distances -- a rule a CPU restates bit for bit.
+ * vqg_quantize_update: one k-means (Lloyd) update -- every codebook entry becomes the mean of
+ *   the sub-vectors whose index names it (entries nobody chose keep their value).  Sums are exact
+ *   64-bit fixed-point (fp16 values are multiples of 2^-24), hence independent of the order of
+ *   accumulation; mean = (float)((double)sum * 2^-24 / count), rounded to fp16.  `workspace` of
+ *   vqg_quantize_workspace_bytes() bytes, 16-byte aligned; the call zeroes it itself.
+ * vqg_pack12 / vqg_unpack12: `values` (even) 12-bit indices held in uint16 <-> 3 bytes per pair:
+ *   bytes [a & 255, (a >> 8) | ((b & 15) << 4), b >> 4]; the uint16 side must be 4-byte aligned. */
+VQG_API int vqg_quantize_assign(const void* w, const void* codebook, void* idx_out, int N, int K, int v, int C,
+                                int idx_bytes, int rows_per_codebook, void* stream);
+VQG_API size_t vqg_quantize_workspace_bytes(int N, int v, int C, int rows_per_codebook);
+VQG_API int vqg_quantize_update(const void* w, const void* idx, void* codebook_inout, void* workspace,
+                                size_t workspace_bytes, int N, int K, int v, int C, int idx_bytes,
+                                int rows_per_codebook, void* stream);
+VQG_API int vqg_pack12(const void* idx_u16, void* packed_out, long long values, void* stream);
+VQG_API int vqg_unpack12(const void* packed, void* idx_u16_out, long long values, void* stream);
+
 /* Reads and clears the device-side status word of the current device: 0 if no bounded wait has
  * run out since the last call, else a code naming the wait.  Synchronises the device. */
 VQG_API int vqg_device_status(int* code_out);

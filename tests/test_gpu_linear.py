@@ -1,0 +1,81 @@
+"""The registered operator and the nn.Module on top of it."""
+import pytest
+import torch
+
+import vq_gemm_b200 as V
+from oracle import vq_oracle as O
+from tests._util import assert_within_tolerance, bits
+from vq_gemm_b200.linear import VQLinear
+
+pytestmark = pytest.mark.gpu
+
+
+def _layer(M=8, K=512, N=256, v=8, rpc=128, bias=False, seed=1):
+    x, idx, cb = O.make_bl_inputs(M, K, N, v, 256, rpc, seed=seed)
+    b = (torch.randn(N, generator=torch.Generator().manual_seed(seed)) * 0.1).half() if bias else None
+    return x, idx, cb, b, VQLinear(idx, cb, rpc, b).cuda()
+
+
+def test_module_equals_the_functional_call_and_the_oracle():
+    x, idx, cb, _, layer = _layer()
+    y = layer(x.cuda())
+    assert torch.equal(bits(y), bits(V.vq_gemm(x.cuda(), idx.cuda(), cb.cuda(), rows_per_codebook=128, layout="bl")))
+    assert_within_tolerance(y.cpu(), O.vq_gemm_bl(x, idx, cb, 128))
+    assert "in_features=512" in repr(layer)
+
+
+def test_leading_dimensions_bias_and_state_dict():
+    x, idx, cb, b, layer = _layer(M=12, bias=True)
+    x3 = x.reshape(3, 4, -1).cuda()
+    y = layer(x3)
+    assert y.shape == (3, 4, 256)
+    ref = O.vq_gemm_bl(x, idx, cb, 128).float() + b.float()
+    assert_within_tolerance(y.reshape(12, 256).cpu(), ref.half())
+    clone = VQLinear(torch.zeros_like(idx), torch.zeros_like(cb), 128, torch.zeros_like(b)).cuda()
+    clone.load_state_dict(layer.state_dict())
+    assert torch.equal(bits(clone(x3)), bits(y))
+    assert torch.equal(layer.dequantized_weight().cpu(), O.dequant_bl_layout(idx, cb, 128))
+
+
+def test_cuda_graph_capture_and_replay():
+    x, idx, cb, _, layer = _layer(M=4, K=8192, N=512)      # K > 4096: the split-K counters are in play
+    xs = x.cuda()
+    eager = layer(xs).clone()
+    static_x = xs.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        layer(static_x)                                     # warm-up on the capture stream
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = layer(static_x)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(bits(out), bits(eager))
+    static_x.copy_(xs * 2)
+    g.replay()
+    torch.cuda.synchronize()
+    assert_within_tolerance(out.cpu(), O.vq_gemm_bl((x.float() * 2).half(), idx, cb, 128))
+    assert V.device_status() == 0
+
+
+def test_traceable_operator():
+    x, idx, cb, _, layer = _layer()
+    torch.library.opcheck(torch.ops.vq_gemm_b200.vq_linear.default, (x.cuda(), idx.cuda(), cb.cuda(), 128),
+                          test_utils=("test_schema", "test_faketensor"))
+    compiled = torch.compile(layer, backend="eager", fullgraph=True)
+    assert torch.equal(bits(compiled(x.cuda())), bits(layer(x.cuda())))
+
+
+def test_from_weight_quantises_and_runs():
+    w = (torch.randn(256, 512, generator=torch.Generator().manual_seed(2)) * 0.05).half().cuda()
+    layer = VQLinear.from_weight(w, v=8, entries=256, rows_per_codebook=128, iters=3)
+    x = torch.randn(16, 512, generator=torch.Generator().manual_seed(3)).half().cuda()
+    y = layer(x)
+    dense = x.float() @ w.float().t()
+    rel = float((y.float() - dense).norm() / dense.norm())
+    assert rel < 0.7          # 1 bit per weight on Gaussian noise: coarse, but far from random indices (~1.4)
+    rel_q = float((y.float() - x.float() @ layer.dequantized_weight().float().t()).abs().max())
+    assert rel_q <= 2e-2 * (float(dense.abs().max()) + 1)

@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_int, c_size_t, c_ulonglong, c_void_p, POINTER
+from ctypes import c_char_p, c_int, c_longlong, c_size_t, c_ulonglong, c_void_p, POINTER
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libvqg_b200.so")
@@ -30,6 +30,11 @@ SIGNATURES = {
     "vqg_dense_workspace_bytes": (c_size_t, [c_int] * 4),
     "vqg_gemm_sharded": (c_int, [c_void_p] * 3 + [POINTER(c_void_p), c_int, c_int] + [c_int] * 7
                          + [c_void_p, c_size_t, c_void_p]),
+    "vqg_quantize_assign": (c_int, [c_void_p] * 3 + [c_int] * 6 + [c_void_p]),
+    "vqg_quantize_workspace_bytes": (c_size_t, [c_int] * 4),
+    "vqg_quantize_update": (c_int, [c_void_p] * 4 + [c_size_t] + [c_int] * 6 + [c_void_p]),
+    "vqg_pack12": (c_int, [c_void_p, c_void_p, c_longlong, c_void_p]),
+    "vqg_unpack12": (c_int, [c_void_p, c_void_p, c_longlong, c_void_p]),
     "vqg_gemm_small_batch_noalloc": (c_int, [c_void_p] * 4 + [c_int] * 7 + [c_void_p]),
     "vqg_device_status": (c_int, [POINTER(c_int)]),
     "vqg_launch_count": (c_ulonglong, []),

@@ -265,6 +265,38 @@ int vqg_gemm_small_batch_noalloc(const void* x, const void* idx, const void* cod
   return launch_decode_static(p, static_cast<cudaStream_t>(stream));
 }
 
+int vqg_quantize_assign(const void* w, const void* codebook, void* idx_out, int N, int K, int v, int C, int idx_bytes,
+                        int rows_per_codebook, void* stream) {
+  if (!w || !codebook || !idx_out || N < 0 || K < 0) return VQG_ERR_BAD_ARG;
+  if (N == 0 || K == 0) return VQG_OK;
+  return launch_quantize_assign(static_cast<const __half*>(w), static_cast<const __half*>(codebook), idx_out, N, K, v, C,
+                                idx_bytes, rows_per_codebook, static_cast<cudaStream_t>(stream));
+}
+
+size_t vqg_quantize_workspace_bytes(int N, int v, int C, int rows_per_codebook) {
+  if (N <= 0 || v <= 0 || C <= 0) return 0;
+  return quantize_workspace_bytes(N, v, C, rows_per_codebook);
+}
+
+int vqg_quantize_update(const void* w, const void* idx, void* codebook_inout, void* workspace, size_t workspace_bytes,
+                        int N, int K, int v, int C, int idx_bytes, int rows_per_codebook, void* stream) {
+  if (!w || !idx || !codebook_inout || N < 0 || K < 0) return VQG_ERR_BAD_ARG;
+  if (N == 0 || K == 0) return VQG_OK;
+  return launch_quantize_update(static_cast<const __half*>(w), idx, static_cast<__half*>(codebook_inout), workspace,
+                                workspace_bytes, N, K, v, C, idx_bytes, rows_per_codebook,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int vqg_pack12(const void* idx_u16, void* packed_out, long long values, void* stream) {
+  if (values < 0 || (values > 0 && (!idx_u16 || !packed_out))) return VQG_ERR_BAD_ARG;
+  return launch_pack12(idx_u16, packed_out, values, true, static_cast<cudaStream_t>(stream));
+}
+
+int vqg_unpack12(const void* packed, void* idx_u16_out, long long values, void* stream) {
+  if (values < 0 || (values > 0 && (!packed || !idx_u16_out))) return VQG_ERR_BAD_ARG;
+  return launch_pack12(packed, idx_u16_out, values, false, static_cast<cudaStream_t>(stream));
+}
+
 int vqg_device_status(int* code_out) {
   if (!code_out) return VQG_ERR_BAD_ARG;
   *code_out = 0;

@@ -72,6 +72,13 @@ int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s
 bool small_ts_supported(const Problem& p);
 size_t small_ts_workspace_bytes(const Problem& p);
 int launch_small_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s);   // M <= 128, stream-K
+// quantiser (the step before the product): nearest-entry search, exact k-means update, 12-bit packing
+size_t quantize_workspace_bytes(int N, int v, int C, int rows_per_cb);
+int launch_quantize_assign(const __half* w, const __half* cb, void* idx, int N, int K, int v, int C, int idx_bytes,
+                           int rows_per_cb, cudaStream_t s);
+int launch_quantize_update(const __half* w, const void* idx, __half* cb, void* ws, size_t ws_bytes, int N, int K, int v,
+                           int C, int idx_bytes, int rows_per_cb, cudaStream_t s);
+int launch_pack12(const void* in, void* out, long long values, bool pack, cudaStream_t s);
 int launch_transpose(const __half* in, __half* out, int rows, int cols, cudaStream_t s);
 
 constexpr size_t kCounterBytes = 64 * 1024;  // arrival counters at the head of a workspace

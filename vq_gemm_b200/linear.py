@@ -1,0 +1,96 @@
+"""Caller side of the boundary: the VQ-GEMM as a registered torch operator and an ``nn.Module``.
+
+The reference stops at ``bench.py`` calling ``e2e_gemm`` on raw tensors (bench.py:66-80); a model
+needs the product as a layer.  ``vq_gemm_b200::vq_linear`` is registered with ``torch.library`` so
+that it can be traced (a fake-tensor rule gives shapes and dtypes without running anything), used
+under ``torch.compile`` as an opaque call, and captured in CUDA graphs: the launch allocates nothing
+but its output, and the scratch it uses is cached per (device, stream) and left as it found it.
+
+Inference only: no autograd formula is registered.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+from . import ops
+
+
+@torch.library.custom_op("vq_gemm_b200::vq_linear", mutates_args=(), device_types="cuda")
+def vq_linear(x: torch.Tensor, indices: torch.Tensor, codebook: torch.Tensor, rows_per_codebook: int) -> torch.Tensor:
+    """x [M, K] fp16, indices [N, K/v] uint8/int16, codebook [G, C, v] fp16 -> [M, N] fp16."""
+    return ops.vq_gemm(x, indices, codebook, rows_per_codebook=rows_per_codebook, layout="bl")
+
+
+@vq_linear.register_fake
+def _(x, indices, codebook, rows_per_codebook):
+    if x.dim() != 2 or indices.dim() != 2 or codebook.dim() != 3:
+        raise RuntimeError("vq_linear expects x [M, K], indices [N, K/v], codebook [G, C, v]")
+    if indices.shape[1] * codebook.shape[2] != x.shape[1]:
+        raise RuntimeError("indices [N, K/v] and codebook [G, C, v] do not match x [M, K]")
+    return x.new_empty((x.shape[0], indices.shape[0]))
+
+
+class VQLinear(nn.Module):
+    """``y = x @ dequant(indices, codebook)^T (+ bias)`` with the weight kept in compressed form.
+
+    ``indices`` [out_features, in_features / v] (uint8, or int16 for codebooks of more than 256
+    entries), ``codebook`` [groups, C, v] fp16 with one codebook per ``rows_per_codebook``
+    consecutive output features (0: a single codebook).  Both are buffers, so ``state_dict`` /
+    ``load_state_dict`` / ``.to(device)`` carry them.  Accepts inputs of any leading shape.
+    """
+
+    def __init__(self, indices: torch.Tensor, codebook: torch.Tensor, rows_per_codebook: int = 0,
+                 bias: Optional[torch.Tensor] = None):
+        super().__init__()
+        if indices.dim() != 2 or codebook.dim() not in (2, 3):
+            raise ValueError("indices must be [N, K/v] and codebook [G, C, v] (or [C, v])")
+        if indices.dtype not in (torch.uint8, torch.int16, torch.uint16):
+            raise ValueError("indices must be uint8 or (u)int16")
+        cb = codebook if codebook.dim() == 3 else codebook.unsqueeze(0)
+        N = indices.shape[0]
+        groups = 1 if rows_per_codebook <= 0 else -(-N // rows_per_codebook)
+        if cb.shape[0] < groups:
+            raise ValueError(f"{cb.shape[0]} codebooks given, {groups} needed")
+        self.out_features = N
+        self.v = cb.shape[2]
+        self.in_features = indices.shape[1] * self.v
+        self.rows_per_codebook = int(rows_per_codebook)
+        self.register_buffer("indices", indices.contiguous())
+        self.register_buffer("codebook", cb.to(torch.float16).contiguous())
+        if bias is not None:
+            if bias.shape != (N,):
+                raise ValueError("bias must be [out_features]")
+            self.register_buffer("bias", bias.to(torch.float16).contiguous())
+        else:
+            self.bias = None
+
+    @classmethod
+    def from_weight(cls, weight: torch.Tensor, *, v: int = 8, entries: int = 256, rows_per_codebook: int = 128,
+                    iters: int = 10, seed: int = 0, bias: Optional[torch.Tensor] = None) -> "VQLinear":
+        """Quantises a dense [out_features, in_features] weight (on its CUDA device) with k-means."""
+        from .quantize import kmeans_quantize
+        idx, cb = kmeans_quantize(weight, v=v, entries=entries, rows_per_codebook=rows_per_codebook, iters=iters, seed=seed)
+        return cls(idx, cb, rows_per_codebook, bias)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.shape[-1] != self.in_features:
+            raise RuntimeError(f"last dimension {x.shape[-1]} != in_features {self.in_features}")
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.in_features)
+        if x2.dtype != torch.float16:
+            x2 = x2.to(torch.float16)
+        y = torch.ops.vq_gemm_b200.vq_linear(x2.contiguous(), self.indices, self.codebook, self.rows_per_codebook)
+        if self.bias is not None:
+            y = y + self.bias
+        return y.reshape(*lead, self.out_features)
+
+    def dequantized_weight(self) -> torch.Tensor:
+        """The dense fp16 [out_features, in_features] weight this layer stands for (bit-exact gather)."""
+        return ops.dequant(self.indices, self.codebook, rows_per_codebook=self.rows_per_codebook)
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, v={self.v}, "
+                f"entries={self.codebook.shape[1]}, rows_per_codebook={self.rows_per_codebook}, bias={self.bias is not None}")

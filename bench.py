@@ -18,6 +18,8 @@ each rank owns N/G output columns and the fp16 output is assembled on every rank
                the M <= 16 workloads), from CUDA-event time of the kernel alone.
 ``shapes``     (N=1 only) the other single-GPU configurations, each with its own roofline, and
                cuBLAS fp16 (torch.matmul) on pre-dequantised weights for the prefill shapes.
+``quantizer``  (N=1 only) the step before the product on a C4-sized layer: nearest-entry search
+               against the fp32 pipe, one exact k-means update, 12-bit pack/unpack against HBM.
 ``cpu_baseline`` the torch CPU oracle (gather + fp32-accumulated matmul) on a bounded sample.
 
 ``--impl reference`` times the reference's torch path restated for CPU (oracle/vq_oracle.py) on
@@ -198,23 +200,78 @@ def _single_shape(V, shape, peaks, steps, warmup):
             torch.cuda.synchronize()
             ams = e0.elapsed_time(e1) / n
             res["path_" + alt] = {"tflops": shape.flops / ams / 1e9, "us": ams * 1e3}
-        # cuBLAS fp16 on pre-dequantised weights (the reference's ref_gemm comparator)
+        # cuBLAS fp16 on pre-dequantised weights (the reference's ref_gemm comparator).  The two are timed in
+        # alternating blocks of equal length so that both see the same clocks under the power cap.
         w = V.dequant(idx, cb, rows_per_codebook=shape.rows_per_codebook)
         wt = w.t()
-        for _ in range(3):
+
+        def ours():
+            V.vq_gemm(x, idx, cb, rows_per_codebook=shape.rows_per_codebook, layout="bl", out=out)
+
+        def cublas():
             torch.matmul(x, wt)
-        torch.cuda.synchronize()
-        n = max(5, min(steps, 30))
-        e0.record()
-        for _ in range(n):
-            torch.matmul(x, wt)
-        e1.record()
-        torch.cuda.synchronize()
-        cms = e0.elapsed_time(e1) / n
+
+        def block(fn, n=20):
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n
+
+        for fn in (ours, cublas):
+            block(fn, 5)
+        t_ours, t_cublas = [], []
+        for _ in range(5):
+            t_ours.append(block(ours))
+            t_cublas.append(block(cublas))
+        oms, cms = statistics.median(t_ours), statistics.median(t_cublas)
+        res["alternating_blocks"] = {"blocks": 5, "launches_per_block": 20, "us": oms * 1e3, "tflops": shape.flops / oms / 1e9}
         res["cublas_fp16_dequantised"] = {"tflops": shape.flops / cms / 1e9, "us": cms * 1e3,
-                                          "speedup_vs_cublas": cms / ms}
+                                          "speedup_vs_cublas": cms / oms, "timing": "alternating blocks with ours"}
         del w, wt
     return res
+
+
+def _quantizer(peaks, clocks_mhz):
+    """Quantiser kernels on a layer of C4's size (N=14336, K=4096, v=4, 256 entries per 128 rows)."""
+    from vq_gemm_b200 import quantize as VQ
+    N, K, v, C, rpc = 14336, 4096, 4, 256, 128
+    w = (torch.randn(N, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(0)) * 0.02).half()
+    cb = VQ.initial_codebook(w, v, C, rpc, seed=0)
+    idx = VQ.assign(w, cb, rpc)
+    e0, e1 = _events()
+
+    def timed(fn, n=5):
+        fn()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    t_assign = timed(lambda: VQ.assign(w, cb, rpc, out=idx))
+    t_update = timed(lambda: VQ.kmeans_update(w, idx, cb.clone(), rpc))
+    # search: per (sub-vector, entry) pair v subtractions, v multiplications, v additions, none fused
+    lane_ops = 3.0 * v * C * (N * K / v)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    fp32_peak = sms * 128 * clocks_mhz * 1e6          # one fp32 operation per lane and cycle (no FMA by rule)
+    idx12 = torch.randint(0, 4096, (8192, 8192), device="cuda").to(torch.int16)
+    packed = VQ.pack12(idx12)
+    t_pack = timed(lambda: VQ.pack12(idx12))
+    t_unpack = timed(lambda: VQ.unpack12(packed))
+    pack_bytes = idx12.numel() * 2 + packed.numel()
+    return {"layer": {"N": N, "K": K, "v": v, "C": C, "rows_per_codebook": rpc},
+            "assign": {"ms": t_assign, "subvectors_per_s": (N * K / v) / t_assign * 1e3,
+                       "roofline": {"bound": "fp32", "achieved": lane_ops / t_assign / 1e6, "peak": fp32_peak / 1e9,
+                                    "unit": "Gop/s", "frac": lane_ops / (t_assign * 1e-3) / fp32_peak,
+                                    "peak_source": "SMs x 128 lanes x max SM clock; unfused sub/mul/add by the parity rule"}},
+            "kmeans_update": {"ms": t_update, "gbs": (N * K * 2 + N * K / v) / t_update / 1e6},
+            "pack12": {"ms": t_pack, "gbs": pack_bytes / t_pack / 1e6, "frac_of_hbm": pack_bytes / t_pack / 1e6 / peaks["hbm_gbs"]},
+            "unpack12": {"ms": t_unpack, "gbs": pack_bytes / t_unpack / 1e6,
+                         "frac_of_hbm": pack_bytes / t_unpack / 1e6 / peaks["hbm_gbs"]}}
 
 
 def _reference_cuda_kernels(V):
@@ -500,6 +557,10 @@ def main():
             except Exception as e:  # keep the headline line even if a side measurement fails
                 shapes.append({"workload": name, "error": repr(e)})
         line["shapes"] = shapes
+        try:
+            line["quantizer"] = _quantizer(peaks, line["clocks"].get("sm_max_mhz") or 1965.0)
+        except Exception as e:
+            line["quantizer"] = {"error": repr(e)}
     if world == 1 and rank == 0 and args.baselines:
         try:
             line["reference_cuda_kernels"] = _reference_cuda_kernels(V)

@@ -304,14 +304,32 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
       if (!(ok = mbar_wait_cluster(bar_acc_full, acc_phase, p.status, DS_ACC_FULL_TIMEOUT))) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      bool released = false;
       if (g.whole) {
-#pragma unroll 1
-        for (int c = 0; c < BM / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(t_row + c * 32, r);
+        // two register buffers: the tensor-memory load of the next 32 columns runs while these are converted
+        // and stored, and tensor memory is handed back as soon as the last load has landed
+        uint32_t ra[32], rb[32];
+        auto put = [&](int c, const uint32_t (&r)[32]) {
           __half* col = reinterpret_cast<__half*>(stg) + (c * 32) * 128 + quarter * 32 + lane;   // T[m][weight row]
 #pragma unroll
           for (int j = 0; j < 32; ++j) col[j * 128] = __float2half_rn(__uint_as_float(r[j]));
+        };
+        tmem_ld32_async(t_row, ra);
+#pragma unroll 1
+        for (int c = 0; c < BM / 32; c += 2) {
+          tmem_ld_wait(ra);
+          tmem_ld32_async(t_row + (c + 1) * 32, rb);
+          put(c, ra);
+          tmem_ld_wait(rb);
+          if (c + 2 < BM / 32) {
+            tmem_ld32_async(t_row + (c + 2) * 32, ra);
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(leader_acc_empty);
+            released = true;
+          }
+          put(c + 1, rb);
         }
       } else {
         // a piece of a tile: the fp32 partial goes to this pair's slot (0 when the pair's range begins
@@ -327,9 +345,11 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
         }
       }
       // tensor memory has been read: the next tile's MMAs may overwrite it while Y is written out
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_remote(leader_acc_empty);
+      if (!released) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(leader_acc_empty);
+      }
       acc_phase ^= 1;
       if (!g.whole) {
         // The contributor that arrives last sums the partials of all contributors (consecutive pairs) in

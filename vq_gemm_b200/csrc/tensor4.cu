@@ -37,7 +37,6 @@ namespace {
 constexpr int BNROWS = 128;      // weight rows per tile (TMEM lanes)
 constexpr int BK = 64;           // K values per sub-step
 constexpr int KS = 2;            // sub-steps per pipeline stage
-constexpr int STAGES = 4;
 constexpr int kThreads = 800;    // 25 warps
 constexpr int kMmaWarps = 4;     // MMA-issuing warps (one lane each), each with its own accumulator
 constexpr int kEpiWarp0 = 1 + kMmaWarps;
@@ -46,7 +45,6 @@ constexpr int kDequantWarps = 16;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAColsPerSub = BK / 2;             // 32 columns: two fp16 per 32-bit column
 constexpr uint32_t kAColsPerStage = KS * kAColsPerSub;
-constexpr uint32_t kACols = STAGES * kAColsPerStage;   // 256; the accumulator follows
 
 struct SmallParams {
   const unsigned char* idx;
@@ -76,7 +74,11 @@ struct SmallSmem {
   static constexpr uint32_t kXStageAligned = KS * kXSubAligned;
   static constexpr int kXStages = NB <= 16 ? 16 : (NB <= 32 ? 12 : (NB <= 64 ? 6 : 4));
   static constexpr uint32_t kImage = kXStages * kXStageAligned;
-  static constexpr int kBarriers = 2 * kXStages + 2 * STAGES + 3;
+  // A stages in tensor memory: what the 512 columns leave after the accumulators (4 x NB columns up to 64
+  // batch columns, 2 x 128 above).  Measured: 7 stages are no faster than 4, and 2 issuing warps no slower
+  // than 4 -- neither the ring depth nor the issue rate of one thread bounds this kernel
+  static constexpr int kStages = NB <= 16 ? 7 : (NB <= 32 ? 6 : 4);
+  static constexpr int kBarriers = 2 * kXStages + 2 * kStages + 3;
 };
 
 __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
@@ -146,6 +148,8 @@ vq_small_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallParams
 
   auto x_addr = [&](int s, int u) { return base + s * L::kXStageAligned + u * L::kXSubAligned; };
   constexpr int XS = L::kXStages;
+  constexpr int STAGES = L::kStages;
+  constexpr uint32_t kACols = STAGES * kAColsPerStage;   // the accumulators follow
   constexpr int NW = (NB <= 64) ? kMmaWarps : 2;          // MMA-issuing warps in use, one accumulator each
   constexpr int MPW = (KS * BK / 16) / NW;                 // MMAs per warp and stage
   static_assert(kACols + NW * NB <= kTmemCols, "accumulators do not fit tensor memory");

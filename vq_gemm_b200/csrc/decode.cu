@@ -153,6 +153,9 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
   const int bid = blockIdx.x;
   const int it_begin = bid * p.items_q + min(bid, p.items_r);
   const int it_end = it_begin + p.items_q + (bid < p.items_r ? 1 : 0);
+  // the next kernel in the stream may be scheduled as soon as SMs free up (it waits as below before it
+  // touches anything this kernel reads or writes)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (it_end <= it_begin) return;
 
   // warp role inside a chunk: (slice, row lane)
@@ -325,6 +328,27 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
       nb = make_batch(it, chunk, rbg, gpos, group);
     }
 
+    const int g_first = b.group;
+    const int g_last = b.group + ((b.gpos + b.cnt - 1 >= p.ipg) ? 1 : 0);   // a batch touches at most two groups
+    {
+      const bool need0 = (p.nslots == 1) ? (slot_group0 != g_first)
+                                         : ((((g_first & 1) == 0) && slot_group0 != g_first) ||
+                                            (((g_last & 1) == 0) && slot_group0 != g_last));
+      const bool need1 = (p.nslots == 2) && ((((g_first & 1) == 1) && slot_group1 != g_first) ||
+                                             (((g_last & 1) == 1) && slot_group1 != g_last));
+      if (need0 || need1) {
+        if (!first_batch) __syncthreads();   // everyone is done looking up in the old images
+        if (need0) { slot_group0 = (p.nslots == 1 || (g_first & 1) == 0) ? g_first : g_last; build_image(slot_group0, 0); }
+        if (need1) { slot_group1 = ((g_first & 1) == 1) ? g_first : g_last; build_image(slot_group1, 1); }
+        __syncthreads();
+        asm volatile("add.u32 %0, %0, 1;" : "+r"(epoch));
+      }
+    }
+
+    // Everything above reads only the weights (indices, codebooks).  X, Y and the workspace belong to the
+    // stream's order: when the launch was made with programmatic stream serialisation this kernel may have
+    // started while its predecessor was still running, and waits here for it to complete.
+    if (first_batch) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (b.chunk != loaded_chunk) {
       loaded_chunk = b.chunk;
       active = role_ok && (b.chunk * kWarps + wsl) < p.nslices;
@@ -345,23 +369,6 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
         load_x_fragments(b.chunk);
       }
     }
-    const int g_first = b.group;
-    const int g_last = b.group + ((b.gpos + b.cnt - 1 >= p.ipg) ? 1 : 0);   // a batch touches at most two groups
-    {
-      const bool need0 = (p.nslots == 1) ? (slot_group0 != g_first)
-                                         : ((((g_first & 1) == 0) && slot_group0 != g_first) ||
-                                            (((g_last & 1) == 0) && slot_group0 != g_last));
-      const bool need1 = (p.nslots == 2) && ((((g_first & 1) == 1) && slot_group1 != g_first) ||
-                                             (((g_last & 1) == 1) && slot_group1 != g_last));
-      if (need0 || need1) {
-        if (!first_batch) __syncthreads();   // everyone is done looking up in the old images
-        if (need0) { slot_group0 = (p.nslots == 1 || (g_first & 1) == 0) ? g_first : g_last; build_image(slot_group0, 0); }
-        if (need1) { slot_group1 = ((g_first & 1) == 1) ? g_first : g_last; build_image(slot_group1, 1); }
-        __syncthreads();
-        asm volatile("add.u32 %0, %0, 1;" : "+r"(epoch));
-      }
-    }
-
     first_batch = false;
     float* rb = red + static_cast<size_t>(parity) * (kWarps * warp_stride);
     parity ^= 1;
@@ -620,9 +627,21 @@ int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s) {
   if (!k) return VQG_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return VQG_ERR_LAUNCH;
-  k<<<grid, kThreads, smem, s>>>(d);
+  // Programmatic dependent launch: set-up, the codebook image and the first batch of index loads of this
+  // launch overlap the tail of the kernel before it in the stream (see the wait inside the kernel).
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, k, d);
   count_launch();
-  return cuda_status(cudaGetLastError());
+  return cuda_status(e == cudaSuccess ? cudaGetLastError() : e);
 }
 
 

@@ -141,6 +141,9 @@ vq_small_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallParams
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bid = blockIdx.x;
+  // the next kernel in the stream may be scheduled as soon as SMs free up; like this one it waits
+  // (griddepcontrol.wait in the TMA and epilogue roles) before it touches X, Y or the workspace
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int s_begin = cta_begin(bid, p.q, p.r);
   const int s_end = cta_begin(bid + 1, p.q, p.r);
   const uint32_t img_bytes = static_cast<uint32_t>(p.C) << ENTRY_SHIFT;
@@ -195,6 +198,7 @@ vq_small_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallParams
     if (lane == 0) {
       bool ok = true;
       int seq = 0;
+      asm volatile("griddepcontrol.wait;" ::: "memory");   // X is the predecessor's to write
       for (int s = s_begin; ok && s < s_end; ++s, ++seq) {
         const int stage = seq % XS;
         const uint32_t phase = (seq / XS) & 1;
@@ -246,6 +250,7 @@ vq_small_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallParams
     uint32_t acc_phase = 0;
     bool ok = true;
     int s = s_begin;
+    asm volatile("griddepcontrol.wait;" ::: "memory");     // Y and the workspace follow the stream's order
     while (ok && s < s_end) {
       const int tile = s / p.ksteps;
       const int t0 = tile * p.ksteps;
@@ -559,9 +564,21 @@ int launch_small_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s)
     if (smem > 227 * 1024) return VQG_ERR_UNSUPPORTED;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return VQG_ERR_LAUNCH;
-    kernel<<<pl.grid, kThreads, smem, s>>>(mx, sp);
+    // programmatic dependent launch: set-up, codebook image and index prefetch overlap the tail of the
+    // kernel before this one in the stream; the roles that touch X, Y or the workspace wait inside
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(pl.grid));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mx, sp);
     count_launch();
-    return cuda_status(cudaGetLastError());
+    return cuda_status(e == cudaSuccess ? cudaGetLastError() : e);
   };
 #define VQG_SMALL(V_, IB_, NB_, R_) launch(vq_small_ts_kernel<V_, IB_, NB_, R_>, SmallSmem<NB_>::kImage, SmallSmem<NB_>::kBarriers)
 #define VQG_SMALL_NB(V_, IB_, R_)                                        \

@@ -57,13 +57,15 @@ class ClockSampler:
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index: int, enabled: bool = True):
+        self.index, self.rows, self.proc, self.enabled = index, [], None, enabled
 
     def __enter__(self):
+        if not self.enabled:   # one sampler per job: the driver queries of eight pollers delay kernel launches
+            return self
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -116,8 +118,10 @@ def _time_loop(fn, steps, warmup, barrier=None, counter=None):
     c0 = counter() if counter else 0
     e0, e1 = _events()
     e0.record()
+    t0 = time.perf_counter()
     for i in range(steps):
         fn()
+    _time_loop.host_issue_ms = (time.perf_counter() - t0) * 1e3 / steps   # host time to enqueue one step
     e1.record()
     torch.cuda.synchronize()
     if barrier:
@@ -441,8 +445,9 @@ def main():
     def step():
         op(x, idx, cb, rpc)
 
-    with ClockSampler(local) as clocks:
+    with ClockSampler(local, enabled=(rank == 0)) as clocks:
         ms, launches = _time_loop(step, args.steps, args.warmup, barrier, counter=V.launch_count)
+        host_issue_ms = _time_loop.host_issue_ms
 
         # kernel alone (no barriers, local columns only) for the roofline
         def kernel_only():
@@ -545,6 +550,7 @@ def main():
                 "ms_per_step": ems, "steps": e2e_steps,
                 "pipeline": "3 streams, double-buffered; every step copies X + indices + codebooks in and its Y block out"},
         "gpu_launches": int(launches),
+        "host_issue_ms_per_step": host_issue_ms,
         "roofline": roof,
         "clocks": clocks.summary(),
         "device_status": status,

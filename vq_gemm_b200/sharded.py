@@ -96,6 +96,7 @@ class ShardedVQGemm:
             self._block = torch.empty((M, self.n_local), dtype=torch.float16, device=self.device)
             self._gathered = torch.empty((self.world, M, self.n_local), dtype=torch.float16, device=self.device)
         self._ws = None
+        self._plans = {}
 
     def _workspace(self, nbytes: int):
         if nbytes == 0:
@@ -116,14 +117,22 @@ class ShardedVQGemm:
         ib = 1 if idx_local.dtype == torch.uint8 else 2
         stream = torch.cuda.current_stream(self.device).cuda_stream
         if self.mode == "peer" or self.world == 1:
-            ws_ptr, ws_n = self._workspace(
-                lib.vqg_workspace_bytes(M, self.n_local, K, v, C, ib, rows_per_codebook, _lib.LAYOUT_BL, _lib.PATH_AUTO))
-            off = 0
+            # per-shape constants are looked up once: at 8 ranks a step is ~0.2 ms and host time counts
+            key = (K, v, C, ib, rows_per_codebook)
+            plan = self._plans.get(key)
+            if plan is None:
+                ws_ptr, ws_n = self._workspace(
+                    lib.vqg_workspace_bytes(M, self.n_local, K, v, C, ib, rows_per_codebook, _lib.LAYOUT_BL, _lib.PATH_AUTO))
+                arrs = [(ctypes.c_void_p * self.world)(*[p + par * self.M * self.N * 2 for p in self._ptrs])
+                        for par in range(2 if self._hdl is not None else 1)]
+                plan = self._plans[key] = (ws_ptr, ws_n, arrs)
+            ws_ptr, ws_n, arrs = plan
+            arr = arrs[0]
             if self._hdl is not None:
-                self.y = self._ybuf[self._step & 1]
-                off = (self._step & 1) * self.M * self.N * 2
+                par = self._step & 1
+                self.y = self._ybuf[par]
+                arr = arrs[par]
                 self._step += 1
-            arr = (ctypes.c_void_p * self.world)(*[p + off for p in self._ptrs])
             st = lib.vqg_gemm_sharded(x.data_ptr(), idx_local.data_ptr(), cb_local.data_ptr(), arr, self.rank,
                                       self.world, M, self.n_local, K, v, C, ib, rows_per_codebook, ws_ptr, ws_n, stream)
             _lib.check(st, "vqg_gemm_sharded")

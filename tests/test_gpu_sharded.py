@@ -63,3 +63,33 @@ def test_two_ranks_equal_single_gpu():
            "--master-port", "29511", os.path.join(ROOT, "tests", "_sharded_worker.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert p.returncode == 0 and "SHARDED_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def test_prefill_kernel_writes_every_rank_buffer():
+    # three ranks emulated on one GPU: the prefill kernel stores its block into its own buffer with plain
+    # stores and into the two others with TMA tensor stores (clipped at M = 300 and at the block's edge)
+    import ctypes
+    from vq_gemm_b200 import _lib
+    M, K, N, G = 300, 1024, 1536, 3
+    x, idx, cb = O.make_bl_inputs(M, K, N, 8, 256, 128, seed=8)
+    full = O.vq_gemm_bl(x, idx, cb, 128)
+    bufs = [torch.full((M + 4, N), 7.0, dtype=torch.float16, device="cuda") for _ in range(G)]   # 4 guard rows
+    lib = _lib.load()
+    n_local = N // G
+    nbytes = lib.vqg_workspace_bytes(M, n_local, K, 8, 256, 1, 128, 0, 0)
+    ws = torch.zeros(max(nbytes, 1), dtype=torch.uint8, device="cuda")
+    xd = x.cuda()
+    for rank in range(G):
+        idx_l = idx[rank * n_local:(rank + 1) * n_local].contiguous().cuda()
+        cb_l = cb[rank * n_local // 128:(rank + 1) * n_local // 128].contiguous().cuda()
+        arr = (ctypes.c_void_p * G)(*[b.data_ptr() for b in bufs])
+        st = lib.vqg_gemm_sharded(xd.data_ptr(), idx_l.data_ptr(), cb_l.data_ptr(), arr, rank, G, M, n_local, K, 8, 256, 1, 128,
+                                  ws.data_ptr(), nbytes, torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+        torch.cuda.synchronize()
+    assert V.device_status() == 0
+    assert_within_tolerance(bufs[0][:M].cpu(), full)
+    for b in bufs[1:]:
+        assert torch.equal(bits(b[:M]), bits(bufs[0][:M]))
+    for b in bufs:
+        assert bool((b[M:] == 7.0).all())        # nothing written past row M

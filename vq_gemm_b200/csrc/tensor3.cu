@@ -79,6 +79,23 @@ __device__ __forceinline__ int pair_of_unit(int u, int q, int r) {
   return u < big ? u / (q + 1) : r + (u - big) / q;
 }
 
+// Tensor maps of the other ranks' Y blocks (sharded mode): the staging tile goes to each of them with one
+// TMA tensor store (no multicast; an ordinary asynchronous bulk store whose destination is peer memory).
+struct alignas(64) PeerMaps {
+  CUtensorMap m[7];
+};
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// shared memory of all committed stores has been read (it may be rewritten)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all committed stores are complete
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // One contiguous piece of a pair's range inside one tile.
 struct Segment {
   int tile, kt_begin, kt_end;   // pipeline stages [kt_begin, kt_end) of the tile's K loop
@@ -155,7 +172,8 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 // commits per MMA for the single issuing thread).
 template <int V, int STAGES, int KS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p) {
+vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ PeerMaps peer_maps,
+                    const TsParams p) {
   using L = TsSmem<STAGES, KS>;
   constexpr uint32_t kStageCols = KS * kAColsPerStage;
   constexpr uint32_t kStageXBytes = KS * kXBytes;
@@ -407,7 +425,14 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
           }
         }
       }
+      if (p.n_peers > 0) fence_async_smem();   // this thread's staging writes become visible to the TMA unit
       if (!(ok = epi_sync())) break;   // the whole tile is in shared memory
+      if (p.n_peers > 0 && warp == 2 && lane == 0) {
+        // peers: one tensor store of the [256 x 128] tile per rank; rows beyond M and columns beyond the
+        // block are clipped by the tensor map.  The SM's load/store pipe stays free for the index loads.
+        for (int q = 0; q < p.n_peers; ++q) tma_store_2d(&peer_maps.m[q], n0, m0, smem_u32(stg));
+        tma_store_commit();
+      }
       {
         const int half_row = lane >> 4, chunk = lane & 15;   // a warp instruction covers two 256-byte rows
         const int ncol = n0 + chunk * 8;
@@ -416,14 +441,14 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const TsParams p
           const int m = 8 * i + 2 * quarter + half_row;
           if (m0 + m < p.M && ncol < p.N) {
             const uint4 v = *reinterpret_cast<const uint4*>(stg + m * 256 + chunk * 16);
-            const size_t off = static_cast<size_t>(m0 + m) * p.ld_y + ncol;
-            *reinterpret_cast<uint4*>(p.y + off) = v;
-            for (int q = 0; q < p.n_peers; ++q) *reinterpret_cast<uint4*>(p.peer_y[q] + off) = v;
+            *reinterpret_cast<uint4*>(p.y + static_cast<size_t>(m0 + m) * p.ld_y + ncol) = v;
           }
         }
       }
+      if (p.n_peers > 0 && warp == 2 && lane == 0) tma_store_wait_read();   // the TMA unit has read the tile
       if (!(ok = epi_sync())) break;   // the tile is rewritten by the next tile's transposition
     }
+    if (p.n_peers > 0 && warp == 2 && lane == 0) tma_store_wait_all();   // peer stores done before the kernel ends
   } else {
     // ------------------------------- dequant warps ------------------------------------------
     constexpr int ENTRY_LOG2 = (V == 4) ? 3 : 4;       // bytes per codebook entry
@@ -581,6 +606,20 @@ bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols) {
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// fp16 row-major Y block [rows, cols] with leading dimension ld, box = the epilogue's staging tile
+// [256 rows x 128 cols], no swizzle (the tile is dense in shared memory).
+bool make_y_map(CUtensorMap* map, const void* ptr, int rows, int cols, long long ld) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {128, 256};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 bool tensor_ts_supported(const Problem& p) {
@@ -617,6 +656,12 @@ int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s
   if (!tensor_ts_supported(p)) return VQG_ERR_UNSUPPORTED;
   CUtensorMap mx;
   if (!make_map(&mx, p.x, p.M, p.K)) return VQG_ERR_LAUNCH;
+  PeerMaps pm{};
+  if (p.n_peers < 0 || p.n_peers > 7) return VQG_ERR_BAD_ARG;
+  for (int q = 0; q < p.n_peers; ++q) {
+    if (reinterpret_cast<uintptr_t>(p.peer_y[q]) % 16) return VQG_ERR_BAD_ARG;
+    if (!make_y_map(&pm.m[q], p.peer_y[q], p.M, p.N, p.ld_y)) return VQG_ERR_LAUNCH;
+  }
   TsParams tp{};
   tp.idx = static_cast<const unsigned char*>(p.idx);
   tp.cb = p.cb;
@@ -651,7 +696,7 @@ int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s
   auto launch = [&](auto kernel) -> int {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return VQG_ERR_LAUNCH;
-    kernel<<<2 * pairs, kThreads, smem, s>>>(mx, tp);
+    kernel<<<2 * pairs, kThreads, smem, s>>>(mx, pm, tp);
     count_launch();
     return cuda_status(cudaGetLastError());
   };

@@ -11,6 +11,9 @@ namespace {
 std::atomic<unsigned long long> g_launches{0};
 std::mutex g_mu;
 int* g_status[64] = {};
+// The status word kernels report a run-out wait in: a zero-initialised device variable of the library image
+// (every device that loads the library has its own copy), so that no call ever allocates device memory.
+__device__ int g_status_word[64];
 }  // namespace
 
 void count_launch(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
@@ -22,12 +25,10 @@ cudaError_t ensure_status_word() {
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   std::lock_guard<std::mutex> lk(g_mu);
   if (g_status[dev]) return cudaSuccess;
-  int* p = nullptr;
-  e = cudaMalloc(&p, 256);
+  void* p = nullptr;
+  e = cudaGetSymbolAddress(&p, g_status_word);
   if (e != cudaSuccess) return e;
-  e = cudaMemset(p, 0, 256);
-  if (e != cudaSuccess) return e;
-  g_status[dev] = p;
+  g_status[dev] = static_cast<int*>(p);
   return cudaSuccess;
 }
 

@@ -40,7 +40,7 @@ enum DeviceStatus : int {
   DS_EPILOGUE_SYNC_TIMEOUT = 9,
 };
 int* device_status_ptr();          // device address of the status word of the current device
-cudaError_t ensure_status_word();  // allocates it on first use (per device)
+cudaError_t ensure_status_word();  // looks its address up on first use (per device); allocates nothing
 
 void count_launch(int n = 1);
 

@@ -147,6 +147,20 @@ VQG_API int vqg_gemm_small_batch_noalloc(const void* x, const void* idx, const v
                                  int M, int N, int K, int v, int C, int idx_bytes,
                                  int rows_per_codebook, void* stream);
 
+/* ---- Gated product: the step after the path in a gated MLP (no counterpart in the reference) ----
+ * The weight matrix holds (gate, up) row pairs: row 2i is gate row i and row 2i+1 is up row i
+ * (BL layout, idx [2*N_out, K/v], one codebook per `rows_per_codebook` of those interleaved rows).
+ *     Y[m, i] = SiLU(X[m,:] . g_i) * (X[m,:] . u_i),   SiLU(t) = t / (1 + exp(-t)),
+ * both dot products accumulated in fp32 and combined in fp32 before the single rounding to fp16.
+ * Y is [M, N_out] row-major.  For M > 128 and shapes the prefill kernel takes, the combination
+ * happens in that kernel's epilogue and the two products never reach memory; otherwise the product
+ * is written to scratch inside the workspace and combined by a second kernel.  Workspace of
+ * vqg_swiglu_workspace_bytes() bytes, 1024-byte aligned, zeroed once, one per stream. */
+VQG_API size_t vqg_swiglu_workspace_bytes(int M, int N_out, int K, int v, int C, int idx_bytes, int rows_per_codebook);
+VQG_API int vqg_gemm_swiglu(const void* x, const void* idx, const void* codebook, void* y, int M, int N_out, int K,
+                            int v, int C, int idx_bytes, int rows_per_codebook, void* workspace,
+                            size_t workspace_bytes, void* stream);
+
 /* ---- Quantiser: the step before the product ------------------------------------------------
  * The reference has no quantiser (bench.py:83-85 fills `w` with random bytes); these entry points
  * turn a dense fp16 weight W[N, K] into the BL format on the GPU.  All pointers are device

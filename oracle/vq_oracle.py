@@ -126,6 +126,16 @@ def vq_gemm_bl(x, idx, codebook, rows_per_codebook: int = 0) -> torch.Tensor:
     return matmul_fp32acc(x, dequant_bl_layout(idx, codebook, rows_per_codebook))
 
 
+def vq_gemm_swiglu_bl(x, idx, codebook, rows_per_codebook: int = 0) -> torch.Tensor:
+    """Gated product over (gate, up) row pairs (row 2i gate, row 2i+1 up): fp32 products, SiLU(g) * u in
+    fp32, one rounding to fp16.  The reference has no such step; the rule is the one stated in
+    include/vqg.h (the gather half is the pinned BL gather, the rest is torch fp32 arithmetic)."""
+    w = dequant_bl_layout(idx, codebook, rows_per_codebook)
+    p = x.float() @ w.float().t()
+    g, u = p[:, 0::2], p[:, 1::2]
+    return (g / (1.0 + torch.exp(-g)) * u).half()
+
+
 def vq_gemm_ref_layout(x, w, codebook) -> torch.Tensor:
     wdec = dequant_ref_layout(w, codebook)              # [K, Nout]
     return (x.float() @ wdec.float()).half()

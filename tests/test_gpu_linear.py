@@ -79,3 +79,21 @@ def test_from_weight_quantises_and_runs():
     assert rel < 0.7          # 1 bit per weight on Gaussian noise: coarse, but far from random indices (~1.4)
     rel_q = float((y.float() - x.float() @ layer.dequantized_weight().float().t()).abs().max())
     assert rel_q <= 2e-2 * (float(dense.abs().max()) + 1)
+
+
+def test_gated_module_and_operator():
+    from vq_gemm_b200.linear import VQGatedUp
+    x, idx, cb = O.make_bl_inputs(160, 512, 512, 8, 256, 128, seed=7, cb_sigma=0.05)
+    layer = VQGatedUp(idx, cb, 128).cuda()
+    y = layer(x.reshape(4, 40, 512).cuda())
+    assert y.shape == (4, 40, 256)
+    assert_within_tolerance(y.reshape(160, 256).cpu(), O.vq_gemm_swiglu_bl(x, idx, cb, 128))
+    torch.library.opcheck(torch.ops.vq_gemm_b200.vq_swiglu.default, (x.cuda(), idx.cuda(), cb.cuda(), 128),
+                          test_utils=("test_schema", "test_faketensor"))
+    gate = (torch.randn(128, 256, generator=torch.Generator().manual_seed(1)) * 0.05).half().cuda()
+    up = (torch.randn(128, 256, generator=torch.Generator().manual_seed(2)) * 0.05).half().cuda()
+    q = VQGatedUp.from_weights(gate, up, v=8, entries=256, rows_per_codebook=128, iters=2)
+    xs = torch.randn(8, 256, generator=torch.Generator().manual_seed(3)).half().cuda()
+    w = V.dequant(q.indices, q.codebook, rows_per_codebook=128).float()
+    ref = torch.nn.functional.silu(xs.float() @ w[0::2].t()) * (xs.float() @ w[1::2].t())
+    assert float((q(xs).float() - ref).abs().max()) <= 2e-2 * (float(ref.abs().max()) + 1)

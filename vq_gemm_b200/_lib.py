@@ -30,6 +30,8 @@ SIGNATURES = {
     "vqg_dense_workspace_bytes": (c_size_t, [c_int] * 4),
     "vqg_gemm_sharded": (c_int, [c_void_p] * 3 + [POINTER(c_void_p), c_int, c_int] + [c_int] * 7
                          + [c_void_p, c_size_t, c_void_p]),
+    "vqg_swiglu_workspace_bytes": (c_size_t, [c_int] * 7),
+    "vqg_gemm_swiglu": (c_int, [c_void_p] * 4 + [c_int] * 7 + [c_void_p, c_size_t, c_void_p]),
     "vqg_quantize_assign": (c_int, [c_void_p] * 3 + [c_int] * 6 + [c_void_p]),
     "vqg_quantize_workspace_bytes": (c_size_t, [c_int] * 4),
     "vqg_quantize_update": (c_int, [c_void_p] * 4 + [c_size_t] + [c_int] * 6 + [c_void_p]),

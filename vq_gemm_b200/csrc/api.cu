@@ -256,6 +256,48 @@ int vqg_gemm_sharded(const void* x, const void* idx, const void* codebook, void*
   return run(p, VQG_LAYOUT_BL, VQG_PATH_AUTO, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
+namespace {
+size_t align_up(size_t n, size_t a) { return (n + a - 1) / a * a; }
+// Scratch for the two products sits behind whatever the product itself needs, and never inside the counter
+// region at the head of a workspace (a cached workspace serves other calls that expect those counters zero).
+size_t swiglu_scratch_offset(size_t inner) { return align_up(inner < vqg::kCounterBytes ? vqg::kCounterBytes : inner, 1024); }
+// fused epilogue when the prefill kernel takes the shape, otherwise product into scratch + elementwise kernel
+bool swiglu_fused(const vqg::Problem& p) { return p.M > 128 && vqg::tensor_ts_supported(p); }
+}  // namespace
+
+size_t vqg_swiglu_workspace_bytes(int M, int N_out, int K, int v, int C, int idx_bytes, int rows_per_codebook) {
+  if (M <= 0 || N_out <= 0 || K <= 0 || N_out > 0x3fffffff) return 0;
+  void* dummy = reinterpret_cast<void*>(static_cast<uintptr_t>(1024));
+  const int N = 2 * N_out;
+  Problem p = make_problem(dummy, dummy, dummy, dummy, M, N, K, v, C, idx_bytes, rows_per_codebook, N_out);
+  if (swiglu_fused(p)) return tensor_ts_workspace_bytes(p);
+  const size_t inner = vqg_workspace_bytes(M, N, K, v, C, idx_bytes, rows_per_codebook, VQG_LAYOUT_BL, VQG_PATH_AUTO);
+  return swiglu_scratch_offset(inner) + static_cast<size_t>(M) * N * 2;
+}
+
+int vqg_gemm_swiglu(const void* x, const void* idx, const void* codebook, void* y, int M, int N_out, int K, int v, int C,
+                    int idx_bytes, int rows_per_codebook, void* workspace, size_t workspace_bytes, void* stream) {
+  if (N_out < 0 || N_out > 0x3fffffff) return VQG_ERR_BAD_ARG;
+  const int N = 2 * N_out;
+  const int st = check_common(x, idx, codebook, y, M, N, K, v, C, idx_bytes, VQG_LAYOUT_BL);
+  if (st != VQG_OK) return st;
+  if (M == 0 || N == 0) return VQG_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Problem p = make_problem(x, idx, codebook, y, M, N, K, v, C, idx_bytes, rows_per_codebook, N_out);
+  if (swiglu_fused(p)) {
+    if (ensure_status_word() != cudaSuccess) return VQG_ERR_NO_DEVICE;
+    return launch_tensor_ts(p, workspace, workspace_bytes, s, /*gated=*/true);
+  }
+  const size_t need = vqg_workspace_bytes(M, N, K, v, C, idx_bytes, rows_per_codebook, VQG_LAYOUT_BL, VQG_PATH_AUTO);
+  const size_t inner = swiglu_scratch_offset(need);
+  if (!workspace || workspace_bytes < inner + static_cast<size_t>(M) * N * 2 || !aligned(workspace, 1024)) return VQG_ERR_WORKSPACE;
+  __half* tmp = reinterpret_cast<__half*>(static_cast<unsigned char*>(workspace) + inner);
+  Problem q = make_problem(x, idx, codebook, tmp, M, N, K, v, C, idx_bytes, rows_per_codebook, N);
+  const int st2 = run(q, VQG_LAYOUT_BL, VQG_PATH_AUTO, need ? workspace : nullptr, need, s);
+  if (st2 != VQG_OK) return st2;
+  return launch_swiglu(tmp, static_cast<__half*>(y), M, N_out, N_out, s);
+}
+
 int vqg_gemm_small_batch_noalloc(const void* x, const void* idx, const void* codebook, void* y, int M, int N, int K,
                                  int v, int C, int idx_bytes, int rows_per_codebook, void* stream) {
   const int st = check_common(x, idx, codebook, y, M, N, K, v, C, idx_bytes, VQG_LAYOUT_BL);

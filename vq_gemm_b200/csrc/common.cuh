@@ -68,7 +68,10 @@ int launch_dense_pair(const __half* x, const __half* w_nk, __half* y, int M, int
                       int n_peers, __half* const* peer_y, cudaStream_t s);
 bool tensor_ts_supported(const Problem& p);
 size_t tensor_ts_workspace_bytes(const Problem& p);
-int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s);     // weights through tensor memory (A operand)
+// gated: weight rows are (gate, up) pairs and Y[M, N/2] = SiLU(X g) * (X u)
+int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s, bool gated = false);
+// elementwise SiLU(g) * u over interleaved columns: in [M, 2*n_out] -> out [M, n_out] (leading dimension ld_out)
+int launch_swiglu(const __half* in, __half* out, int M, int n_out, long long ld_out, cudaStream_t s);     // weights through tensor memory (A operand)
 bool small_ts_supported(const Problem& p);
 size_t small_ts_workspace_bytes(const Problem& p);
 int launch_small_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s);   // M <= 128, stream-K

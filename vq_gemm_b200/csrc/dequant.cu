@@ -305,4 +305,29 @@ int launch_generic(const Problem& p, int layout, cudaStream_t s) {
   return cuda_status(cudaGetLastError());
 }
 
+namespace {
+// out[m, i] = SiLU(in[m, 2i]) * in[m, 2i+1], fp32 arithmetic on fp16 inputs (the route for shapes the fused
+// epilogue does not take)
+__global__ void swiglu_kernel(const __half* __restrict__ in, __half* __restrict__ out, int M, int n_out, long long ld_out) {
+  const long long total = static_cast<long long>(M) * n_out;
+  for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+       e += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long m = e / n_out;
+    const int i = static_cast<int>(e - m * n_out);
+    const float2 gu = __half22float2(*reinterpret_cast<const __half2*>(in + (m * n_out + i) * 2));
+    out[m * ld_out + i] = __float2half_rn(gu.x / (1.0f + __expf(-gu.x)) * gu.y);
+  }
+}
+}  // namespace
+
+int launch_swiglu(const __half* in, __half* out, int M, int n_out, long long ld_out, cudaStream_t s) {
+  if (M <= 0 || n_out <= 0) return VQG_OK;
+  const long long total = static_cast<long long>(M) * n_out;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  swiglu_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(in, out, M, n_out, ld_out);
+  count_launch();
+  return cuda_status(cudaGetLastError());
+}
+
 }  // namespace vqg

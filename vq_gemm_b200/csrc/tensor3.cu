@@ -170,7 +170,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 
 // KS: 64-wide K sub-tiles per pipeline stage (a stage is KS*64 K values: fewer barrier round trips and
 // commits per MMA for the single issuing thread).
-template <int V, int STAGES, int KS>
+// fp32 SiLU(g) * u of one (gate, up) pair of accumulators
+__device__ __forceinline__ float swiglu(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+
+// GATED: weight rows come in (gate, up) pairs -- row 2i is gate row i, row 2i+1 is up row i -- and the
+// epilogue writes SiLU(X g_i) * (X u_i) into output column i, so Y is [M, N/2] and the two products of a
+// gated MLP's first half never reach memory.
+template <int V, int STAGES, int KS, bool GATED = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ PeerMaps peer_maps,
                     const TsParams p) {
@@ -312,13 +318,16 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       return done;
     };
     volatile int* last_flag = reinterpret_cast<volatile int*>(base_ptr + L::kTmemSlot + 8);
+    constexpr int OUT_COLS = GATED ? BNH / 2 : BNH;      // output columns of this CTA's half tile
+    constexpr int ROW_BYTES = OUT_COLS * 2;              // one staged row of the tile
     constexpr size_t kPartialFloats = static_cast<size_t>(BM) * BNH;   // one CTA's share of a pair tile
     bool from_back = ends_inside_tile;
     for (int lo = u_begin, hi = u_end; ok && lo < hi;) {
       const Segment g = take_segment(lo, hi, from_back, p);
       const int tile = g.tile;
       const int m0 = (tile % p.m_tiles) * BM;
-      const int n0 = (tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH;
+      const int n0 = ((tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH) / (GATED ? 2 : 1);   // first output column
+      const int n_out = GATED ? p.N / 2 : p.N;
       if (!(ok = mbar_wait_cluster(bar_acc_full, acc_phase, p.status, DS_ACC_FULL_TIMEOUT))) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -328,9 +337,23 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         // and stored, and tensor memory is handed back as soon as the last load has landed
         uint32_t ra[32], rb[32];
         auto put = [&](int c, const uint32_t (&r)[32]) {
-          __half* col = reinterpret_cast<__half*>(stg) + (c * 32) * 128 + quarter * 32 + lane;   // T[m][weight row]
+          if constexpr (GATED) {
+            // lanes 2i / 2i+1 hold gate / up row i: the even lane takes its neighbour's value and writes column i
+            __half* col = reinterpret_cast<__half*>(stg) + (c * 32) * OUT_COLS + ((quarter * 32 + lane) >> 1);
+            // one exchange per two batch columns: the even lane finishes column j, the odd lane column j + 1
+            const bool odd = (lane & 1) != 0;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) col[j * 128] = __float2half_rn(__uint_as_float(r[j]));
+            for (int j = 0; j < 32; j += 2) {
+              const float send = odd ? __uint_as_float(r[j]) : __uint_as_float(r[j + 1]);
+              const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+              const float y = odd ? swiglu(recv, __uint_as_float(r[j + 1])) : swiglu(__uint_as_float(r[j]), recv);
+              col[(j + (odd ? 1 : 0)) * OUT_COLS] = __float2half_rn(y);
+            }
+          } else {
+            __half* col = reinterpret_cast<__half*>(stg) + (c * 32) * 128 + quarter * 32 + lane;   // T[m][weight row]
+#pragma unroll
+            for (int j = 0; j < 32; ++j) col[j * 128] = __float2half_rn(__uint_as_float(r[j]));
+          }
         };
         tmem_ld32_async(t_row, ra);
 #pragma unroll 1
@@ -416,11 +439,16 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             }
 #pragma unroll
             for (int j = 0; j < INFL; ++j) {
-              const __half2 lo2 = __floats2half2_rn(sum[j].x, sum[j].y), hi2 = __floats2half2_rn(sum[j].z, sum[j].w);
-              uint2 o;
-              o.x = *reinterpret_cast<const uint32_t*>(&lo2);
-              o.y = *reinterpret_cast<const uint32_t*>(&hi2);
-              *reinterpret_cast<uint2*>(stg + (4 * (i0 + j) + msub) * 256 + row4 * 2) = o;
+              if constexpr (GATED) {   // the thread's four weight rows are two (gate, up) pairs
+                const __half2 o2 = __floats2half2_rn(swiglu(sum[j].x, sum[j].y), swiglu(sum[j].z, sum[j].w));
+                *reinterpret_cast<uint32_t*>(stg + (4 * (i0 + j) + msub) * ROW_BYTES + row4) = *reinterpret_cast<const uint32_t*>(&o2);
+              } else {
+                const __half2 lo2 = __floats2half2_rn(sum[j].x, sum[j].y), hi2 = __floats2half2_rn(sum[j].z, sum[j].w);
+                uint2 o;
+                o.x = *reinterpret_cast<const uint32_t*>(&lo2);
+                o.y = *reinterpret_cast<const uint32_t*>(&hi2);
+                *reinterpret_cast<uint2*>(stg + (4 * (i0 + j) + msub) * 256 + row4 * 2) = o;
+              }
             }
           }
         }
@@ -434,13 +462,14 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         tma_store_commit();
       }
       {
-        const int half_row = lane >> 4, chunk = lane & 15;   // a warp instruction covers two 256-byte rows
+        constexpr int LPR = ROW_BYTES / 16, RPW = 32 / LPR;   // lanes per staged row, rows per warp instruction
+        const int rsel = lane / LPR, chunk = lane % LPR;
         const int ncol = n0 + chunk * 8;
 #pragma unroll 4
-        for (int i = 0; i < BM / 8; ++i) {
-          const int m = 8 * i + 2 * quarter + half_row;
-          if (m0 + m < p.M && ncol < p.N) {
-            const uint4 v = *reinterpret_cast<const uint4*>(stg + m * 256 + chunk * 16);
+        for (int i = 0; i < BM / (4 * RPW); ++i) {
+          const int m = (4 * i + quarter) * RPW + rsel;
+          if (m0 + m < p.M && ncol < n_out) {
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + m * ROW_BYTES + chunk * 16);
             *reinterpret_cast<uint4*>(p.y + static_cast<size_t>(m0 + m) * p.ld_y + ncol) = v;
           }
         }
@@ -652,8 +681,9 @@ size_t tensor_ts_workspace_bytes(const Problem& p) {
   return kCounterBytes + static_cast<size_t>(sm_count() / 2) * kPairPartialBytes;
 }
 
-int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s) {
+int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s, bool gated) {
   if (!tensor_ts_supported(p)) return VQG_ERR_UNSUPPORTED;
+  if (gated && (p.n_peers != 0 || p.N % 2 != 0)) return VQG_ERR_UNSUPPORTED;
   CUtensorMap mx;
   if (!make_map(&mx, p.x, p.M, p.K)) return VQG_ERR_LAUNCH;
   PeerMaps pm{};
@@ -700,6 +730,7 @@ int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s
     count_launch();
     return cuda_status(cudaGetLastError());
   };
+  if (gated) return p.v == 4 ? launch(vq_tensor_ts_kernel<4, S, KS, true>) : launch(vq_tensor_ts_kernel<8, S, KS, true>);
   if (p.v == 4) return launch(vq_tensor_ts_kernel<4, S, KS>);
   return launch(vq_tensor_ts_kernel<8, S, KS>);
 }

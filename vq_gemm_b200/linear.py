@@ -33,6 +33,21 @@ def _(x, indices, codebook, rows_per_codebook):
     return x.new_empty((x.shape[0], indices.shape[0]))
 
 
+@torch.library.custom_op("vq_gemm_b200::vq_swiglu", mutates_args=(), device_types="cuda")
+def vq_swiglu(x: torch.Tensor, indices: torch.Tensor, codebook: torch.Tensor, rows_per_codebook: int) -> torch.Tensor:
+    """x [M, K]; indices [2*N_out, K/v] with (gate, up) row pairs -> SiLU(x g^T) * (x u^T), [M, N_out] fp16."""
+    return ops.vq_gemm_swiglu(x, indices, codebook, rows_per_codebook=rows_per_codebook)
+
+
+@vq_swiglu.register_fake
+def _(x, indices, codebook, rows_per_codebook):
+    if x.dim() != 2 or indices.dim() != 2 or codebook.dim() != 3 or indices.shape[0] % 2:
+        raise RuntimeError("vq_swiglu expects x [M, K], indices [2*N_out, K/v], codebook [G, C, v]")
+    if indices.shape[1] * codebook.shape[2] != x.shape[1]:
+        raise RuntimeError("indices [2*N_out, K/v] and codebook [G, C, v] do not match x [M, K]")
+    return x.new_empty((x.shape[0], indices.shape[0] // 2))
+
+
 class VQLinear(nn.Module):
     """``y = x @ dequant(indices, codebook)^T (+ bias)`` with the weight kept in compressed form.
 
@@ -94,3 +109,47 @@ class VQLinear(nn.Module):
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, v={self.v}, "
                 f"entries={self.codebook.shape[1]}, rows_per_codebook={self.rows_per_codebook}, bias={self.bias is not None}")
+
+
+class VQGatedUp(nn.Module):
+    """First half of a gated MLP with compressed weights: ``SiLU(x W_gate^T) * (x W_up^T)``.
+
+    ``indices`` [2 * intermediate, in_features / v] holds the two projections row-interleaved
+    (row 2i = gate row i, row 2i+1 = up row i; ``ops.interleave_gate_up`` builds that order), one
+    codebook per ``rows_per_codebook`` of those interleaved rows.  For more than 128 input rows the
+    combination happens in the GEMM kernel's epilogue and the two products never reach memory."""
+
+    def __init__(self, indices: torch.Tensor, codebook: torch.Tensor, rows_per_codebook: int = 0):
+        super().__init__()
+        if indices.dim() != 2 or indices.shape[0] % 2 or codebook.dim() not in (2, 3):
+            raise ValueError("indices must be [2*N_out, K/v] and codebook [G, C, v] (or [C, v])")
+        cb = codebook if codebook.dim() == 3 else codebook.unsqueeze(0)
+        self.v = cb.shape[2]
+        self.in_features = indices.shape[1] * self.v
+        self.out_features = indices.shape[0] // 2
+        self.rows_per_codebook = int(rows_per_codebook)
+        self.register_buffer("indices", indices.contiguous())
+        self.register_buffer("codebook", cb.to(torch.float16).contiguous())
+
+    @classmethod
+    def from_weights(cls, gate: torch.Tensor, up: torch.Tensor, *, v: int = 8, entries: int = 256,
+                     rows_per_codebook: int = 128, iters: int = 10, seed: int = 0) -> "VQGatedUp":
+        """Quantises two dense [intermediate, in_features] fp16 CUDA weights, interleaved, with k-means."""
+        from .quantize import kmeans_quantize
+        w = ops.interleave_gate_up(gate, up)
+        idx, cb = kmeans_quantize(w, v=v, entries=entries, rows_per_codebook=rows_per_codebook, iters=iters, seed=seed)
+        return cls(idx, cb, rows_per_codebook)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.shape[-1] != self.in_features:
+            raise RuntimeError(f"last dimension {x.shape[-1]} != in_features {self.in_features}")
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.in_features)
+        if x2.dtype != torch.float16:
+            x2 = x2.to(torch.float16)
+        y = torch.ops.vq_gemm_b200.vq_swiglu(x2.contiguous(), self.indices, self.codebook, self.rows_per_codebook)
+        return y.reshape(*lead, self.out_features)
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, v={self.v}, "
+                f"entries={self.codebook.shape[1]}, rows_per_codebook={self.rows_per_codebook}")

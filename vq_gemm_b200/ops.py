@@ -3,6 +3,7 @@
     e2e_gemm(input, w, codebook) -> o      same positional signature as the reference
     gemm(input, w) -> o                    dense fp16 product, w given as [K, N]
     vq_gemm(x, indices, codebook, ...)     generalised entry point (both weight formats)
+    vq_gemm_swiglu(x, indices, codebook)   gated product SiLU(X g) * (X u) over (gate, up) row pairs
     dequant(indices, codebook, ...)        bit-exact dequantised weights
 
 All tensors must be CUDA tensors on one device; the output is allocated by the callee on that
@@ -107,6 +108,51 @@ def vq_gemm(x: torch.Tensor, indices: torch.Tensor, codebook: torch.Tensor, *, r
                                rows_per_codebook, lay, pth, ws.data_ptr() if ws is not None else None,
                                ws.numel() if ws is not None else 0, _stream_ptr(dev))
     _lib.check(st, "vq_gemm")
+    return out
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Row-interleaves two [N, ...] tensors (dense weights or index matrices) into the [2N, ...] order
+    the gated product expects: row 2i = gate row i, row 2i+1 = up row i."""
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise RuntimeError("gate and up must have the same shape and dtype")
+    return torch.stack((gate, up), dim=1).reshape(2 * gate.shape[0], *gate.shape[1:]).contiguous()
+
+
+def vq_gemm_swiglu(x: torch.Tensor, indices: torch.Tensor, codebook: torch.Tensor, *,
+                   rows_per_codebook: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Y[M, N/2] = SiLU(X g_i^T) * (X u_i^T) for a BL-format weight whose rows are (gate, up) pairs
+    (see :func:`interleave_gate_up`); fp32 accumulation and combination, one rounding to fp16."""
+    lib = _lib.load()
+    dev = _require_cuda(x, indices, codebook)
+    if x.dtype != torch.float16 or codebook.dtype != torch.float16:
+        raise RuntimeError("x and codebook must be float16")
+    M, K = x.shape
+    ib = _idx_bytes(indices)
+    N = indices.shape[0]
+    if N % 2:
+        raise RuntimeError("the gated product needs an even number of weight rows (gate, up pairs)")
+    cb3 = codebook if codebook.dim() == 3 else codebook.unsqueeze(0)
+    G, C, v = cb3.shape
+    if indices.dim() != 2 or indices.shape[1] * v != K:
+        raise RuntimeError(f"indices [N, K/v] = {tuple(indices.shape)} does not match K={K}, v={v}")
+    if rows_per_codebook is None:
+        rows_per_codebook = 0 if G == 1 else N // G
+    need_groups = 1 if rows_per_codebook <= 0 else -(-N // rows_per_codebook)
+    if G < need_groups:
+        raise RuntimeError(f"{G} codebooks given, {need_groups} needed")
+    n_out = N // 2
+    if out is None:
+        out = torch.empty((M, n_out), dtype=torch.float16, device=dev)
+    elif tuple(out.shape) != (M, n_out) or out.dtype != torch.float16 or not out.is_contiguous() or out.device != dev:
+        raise RuntimeError("out must be a contiguous float16 [M, N/2] tensor on the inputs' device")
+    with torch.cuda.device(dev):
+        nbytes = lib.vqg_swiglu_workspace_bytes(M, n_out, K, v, C, ib, rows_per_codebook)
+        ws = _ws(dev, nbytes)
+        st = lib.vqg_gemm_swiglu(x.data_ptr(), indices.data_ptr(), codebook.data_ptr(), out.data_ptr(), M, n_out, K, v, C, ib,
+                                 rows_per_codebook, ws.data_ptr() if ws is not None else None,
+                                 ws.numel() if ws is not None else 0, _stream_ptr(dev))
+    _lib.check(st, "vq_gemm_swiglu")
     return out
 
 

@@ -18,6 +18,7 @@ each rank owns N/G output columns and the fp16 output is assembled on every rank
                the M <= 16 workloads), from CUDA-event time of the kernel alone.
 ``shapes``     (N=1 only) the other single-GPU configurations, each with its own roofline, and
                cuBLAS fp16 (torch.matmul) on pre-dequantised weights for the prefill shapes.
+``gated_mlp_up`` (N=1 only) SiLU(X g) * (X u) fused into the GEMM epilogue on the 70B gate+up shape.
 ``quantizer``  (N=1 only) the step before the product on a C4-sized layer: nearest-entry search
                against the fp32 pipe, one exact k-means update, 12-bit pack/unpack against HBM.
 ``cpu_baseline`` the torch CPU oracle (gather + fp32-accumulated matmul) on a bounded sample.
@@ -276,6 +277,43 @@ def _quantizer(peaks, clocks_mhz):
             "pack12": {"ms": t_pack, "gbs": pack_bytes / t_pack / 1e6, "frac_of_hbm": pack_bytes / t_pack / 1e6 / peaks["hbm_gbs"]},
             "unpack12": {"ms": t_unpack, "gbs": pack_bytes / t_unpack / 1e6,
                          "frac_of_hbm": pack_bytes / t_unpack / 1e6 / peaks["hbm_gbs"]}}
+
+
+def _gated(V, peaks):
+    """First half of a Llama-3-70B MLP on C5's shape: gate and up projections (2 x 28672 rows, interleaved)
+    with SiLU(g) * u fused into the GEMM epilogue, against the product followed by an elementwise pass."""
+    from vq_gemm_b200.formats import VQShape, make_inputs
+    shape = VQShape("mlp70b_gate_up", 2048, 8192, 57344, 8, 256, 128, 1, "tensor")
+    x, idx, cb = make_inputs(shape, seed=0, device="cuda")
+    out = torch.empty((shape.M, shape.N // 2), dtype=torch.float16, device="cuda")
+    full = torch.empty((shape.M, shape.N), dtype=torch.float16, device="cuda")
+    e0, e1 = _events()
+
+    def fused():
+        V.vq_gemm_swiglu(x, idx, cb, rows_per_codebook=128, out=out)
+
+    def unfused():
+        V.vq_gemm(x, idx, cb, rows_per_codebook=128, layout="bl", out=full)
+        torch.mul(torch.nn.functional.silu(full[:, 0::2]), full[:, 1::2], out=out)
+
+    def block(fn, n=10):
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    for fn in (fused, unfused):
+        block(fn, 3)
+    tf, tu = [], []
+    for _ in range(3):
+        tf.append(block(fused))
+        tu.append(block(unfused))
+    f_ms, u_ms = statistics.median(tf), statistics.median(tu)
+    return {"workload": shape.name, "M": shape.M, "K": shape.K, "N_out": shape.N // 2, "v": 8, "C": 256,
+            "fused_ms": f_ms, "tflops": shape.flops / f_ms / 1e9, "frac_of_measured_peak": shape.flops / f_ms / 1e9 / peaks["tflops"],
+            "product_then_elementwise_ms": u_ms, "speedup": u_ms / f_ms, "timing": "alternating blocks of 10"}
 
 
 def _reference_cuda_kernels(V):
@@ -563,6 +601,10 @@ def main():
             except Exception as e:  # keep the headline line even if a side measurement fails
                 shapes.append({"workload": name, "error": repr(e)})
         line["shapes"] = shapes
+        try:
+            line["gated_mlp_up"] = _gated(V, peaks)
+        except Exception as e:
+            line["gated_mlp_up"] = {"error": repr(e)}
         try:
             line["quantizer"] = _quantizer(peaks, line["clocks"].get("sm_max_mhz") or 1965.0)
         except Exception as e:

@@ -187,6 +187,14 @@ VQG_API int vqg_quantize_update(const void* w, const void* idx, void* codebook_i
 VQG_API int vqg_pack12(const void* idx_u16, void* packed_out, long long values, void* stream);
 VQG_API int vqg_unpack12(const void* packed, void* idx_u16_out, long long values, void* stream);
 
+/* Failure-path self-test (no counterpart in the reference, whose kernels wait without bound,
+ * e.g. the cuda::barrier waits of strategy_3/wasp/src.cu:262-319): launches one small kernel that
+ * waits on an mbarrier nobody signals, with the same bounded-wait routine the pipelined kernels use
+ * and a limit of `limit_cycles` SM cycles (1e3 .. 2e9, i.e. at most about a second).  The kernel
+ * records code 10 in the status word and returns normally; vqg_device_status() then reports
+ * VQG_ERR_DEVICE_TIMEOUT with that code, and the device stays usable. */
+VQG_API int vqg_selftest_bounded_wait(long long limit_cycles, void* stream);
+
 /* Reads and clears the device-side status word of the current device: 0 if no bounded wait has
  * run out since the last call, else a code naming the wait.  Synchronises the device. */
 VQG_API int vqg_device_status(int* code_out);

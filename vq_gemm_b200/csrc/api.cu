@@ -340,6 +340,11 @@ int vqg_unpack12(const void* packed, void* idx_u16_out, long long values, void* 
   return launch_pack12(packed, idx_u16_out, values, false, static_cast<cudaStream_t>(stream));
 }
 
+int vqg_selftest_bounded_wait(long long limit_cycles, void* stream) {
+  if (ensure_status_word() != cudaSuccess) return VQG_ERR_NO_DEVICE;
+  return launch_selftest_wait(limit_cycles, static_cast<cudaStream_t>(stream));
+}
+
 int vqg_device_status(int* code_out) {
   if (!code_out) return VQG_ERR_BAD_ARG;
   *code_out = 0;

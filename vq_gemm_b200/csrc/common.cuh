@@ -38,6 +38,7 @@ enum DeviceStatus : int {
   DS_DEQUANT_SYNC_TIMEOUT = 7,
   DS_PEER_READY_TIMEOUT = 8, // pair leader waited for the second CTA's operands
   DS_EPILOGUE_SYNC_TIMEOUT = 9,
+  DS_SELFTEST_TIMEOUT = 10,  // the self-test kernel's wait on a barrier nobody signals
 };
 int* device_status_ptr();          // device address of the status word of the current device
 cudaError_t ensure_status_word();  // looks its address up on first use (per device); allocates nothing
@@ -82,6 +83,7 @@ int launch_quantize_assign(const __half* w, const __half* cb, void* idx, int N, 
 int launch_quantize_update(const __half* w, const void* idx, __half* cb, void* ws, size_t ws_bytes, int N, int K, int v,
                            int C, int idx_bytes, int rows_per_cb, cudaStream_t s);
 int launch_pack12(const void* in, void* out, long long values, bool pack, cudaStream_t s);
+int launch_selftest_wait(long long limit_cycles, cudaStream_t s);   // see vqg_selftest_bounded_wait
 int launch_transpose(const __half* in, __half* out, int rows, int cols, cudaStream_t s);
 
 constexpr size_t kCounterBytes = 64 * 1024;  // arrival counters at the head of a workspace

@@ -31,9 +31,9 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (after recording `code`) when the limit is reached or when another
+// Bounded wait.  Returns false (after recording `code`) when `limit` cycles have passed or when another
 // role has already recorded a failure.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, int* status, int code, long long limit) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
@@ -41,12 +41,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     if (mbar_try(bar, parity)) return true;
     if ((++spins & 63u) == 0) {
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-      if (clock64() - t0 > kWaitCycles) {
+      if (clock64() - t0 > limit) {
         atomicCAS(status, 0, code);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+  return mbar_wait_limit(bar, parity, status, code, kWaitCycles);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile(

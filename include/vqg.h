@@ -147,6 +147,30 @@ VQG_API int vqg_gemm_small_batch_noalloc(const void* x, const void* idx, const v
                                  int M, int N, int K, int v, int C, int idx_bytes,
                                  int rows_per_codebook, void* stream);
 
+/* ---- Row-parallel (K-sharded) product with reduce-scatter (no counterpart in the reference) ----
+ * The second half of a tensor-parallel MLP: rank r holds K_local = K/G input features -- x_local
+ * [M, K_local] (what the N-sharded first half left on this rank) and idx_local [N, K_local/v] (its
+ * K slice of every weight row) -- and all codebooks.  Every rank computes a partial [M, N]; the
+ * output columns are cut into G blocks of N/G (a multiple of 128) and rank o owns block o.
+ *
+ * vqg_gemm_rowparallel: writes this rank's partial of block o, fp16 [M, N/G], to part_of_owner[o]
+ *   for every o (host array of G device pointers; part_of_owner[rank] is local memory, the others
+ *   are peer-mapped).  By convention part_of_owner[o] is slot `rank` of owner o's buffer
+ *   [G][M][N/G].  For M > 128 the prefill kernel stores each finished tile straight to its owner
+ *   with a TMA tensor store (no multicast); other shapes compute into scratch and scatter.
+ * After a barrier across the ranks (all partials have landed):
+ * vqg_reduce_slots: y_local[M, cols] = sum over the G slots of part_local [G][M][cols], fp32
+ *   accumulation in slot order (deterministic), one rounding to fp16.
+ * Workspace: vqg_rowparallel_workspace_bytes(), 1024-byte aligned, zeroed once, one per stream. */
+VQG_API size_t vqg_rowparallel_workspace_bytes(int M, int N, int K_local, int v, int C, int idx_bytes,
+                                               int rows_per_codebook);
+VQG_API int vqg_gemm_rowparallel(const void* x_local, const void* idx_local, const void* codebook,
+                                 void* const* part_of_owner, int nranks, int M, int N, int K_local, int v,
+                                 int C, int idx_bytes, int rows_per_codebook, void* workspace,
+                                 size_t workspace_bytes, void* stream);
+VQG_API int vqg_reduce_slots(const void* part_local, void* y_local, int nranks, int M, int cols,
+                             long long ld_y, void* stream);
+
 /* ---- Gated product: the step after the path in a gated MLP (no counterpart in the reference) ----
  * The weight matrix holds (gate, up) row pairs: row 2i is gate row i and row 2i+1 is up row i
  * (BL layout, idx [2*N_out, K/v], one codebook per `rows_per_codebook` of those interleaved rows).

@@ -13,13 +13,39 @@ from oracle import vq_oracle as O  # noqa: E402
 from vq_gemm_b200.sharded import ShardedVQGemm, shard_weights  # noqa: E402
 
 
+def rowparallel(rank, world, dev):
+    """K-sharded product + reduce-scatter against the oracle's column block; three steps in a row reuse the
+    alternating slot sets and must give the same bits."""
+    from vq_gemm_b200.sharded import RowParallelVQGemm, shard_weights_k
+    ok = True
+    for (M, K, N, v, C, rpc) in [(300, 2048, 512, 8, 256, 128), (24, 1024, 256, 4, 256, 128), (1024, 4096, 1024, 8, 256, 128)]:
+        x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=17)
+        kl, nl = K // world, N // world
+        op = RowParallelVQGemm(M, N, device=dev)
+        xl = x[:, rank * kl:(rank + 1) * kl].contiguous().to(dev)
+        il = shard_weights_k(idx, world, rank).to(dev)
+        outs = [op(xl, il, cb.to(dev), rpc).clone() for _ in range(3)]
+        torch.cuda.synchronize()
+        ref = O.vq_gemm_bl(x, idx, cb, rpc)[:, rank * nl:(rank + 1) * nl]
+        tol = O.check_tolerance(outs[0].cpu(), ref)["ok"]
+        same = all(torch.equal(o.view(torch.int16), outs[0].view(torch.int16)) for o in outs[1:])
+        if not (tol and same):
+            ok = False
+            print(f"rank {rank}: ROWPARALLEL MISMATCH shape={(M, K, N, v)} tol={tol} deterministic={same}", flush=True)
+    return ok
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     ok = True
-    for (M, K, N, v, C, rpc) in [(256, 512, 1024, 4, 256, 128), (4, 1024, 512, 8, 256, 128), (512, 1024, 2048, 8, 256, 128)]:
+    cases = [(256, 512, 1024, 4, 256, 128), (4, 1024, 512, 8, 256, 128), (512, 1024, 2048, 8, 256, 128)]
+    if os.environ.get("VQG_WORKER_MODE") == "rowparallel":
+        ok = rowparallel(rank, world, dev)
+        cases = []
+    for (M, K, N, v, C, rpc) in cases:
         x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=5)
         # the single-GPU result, block by block: a block computed alone has the same shape, hence the same
         # schedule and summation order, as the one a rank computes (the whole-N product may cut its K loops

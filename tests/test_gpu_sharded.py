@@ -93,3 +93,52 @@ def test_prefill_kernel_writes_every_rank_buffer():
         assert torch.equal(bits(b[:M]), bits(bufs[0][:M]))
     for b in bufs:
         assert bool((b[M:] == 7.0).all())        # nothing written past row M
+
+
+@pytest.mark.parametrize("M,K,N,v", [
+    (300, 2048, 512, 8),      # prefill kernel: tiles stored to their owners with TMA tensor stores
+    (40, 2048, 512, 4),       # small shapes: product into scratch, then the scatter kernel
+])
+def test_row_parallel_two_ranks_emulated_on_one_gpu(M, K, N, v):
+    # rank r multiplies its K slice and writes block o of its partial to slot r of owner o; each owner sums
+    import ctypes
+    from vq_gemm_b200 import _lib
+    from vq_gemm_b200.sharded import shard_weights_k
+    G = 2
+    x, idx, cb = O.make_bl_inputs(M, K, N, v, 256, 128, seed=21)
+    full = O.vq_gemm_bl(x, idx, cb, 128)
+    lib = _lib.load()
+    nl, kl = N // G, K // G
+    parts = [torch.full((G, M, nl), 9.0, dtype=torch.float16, device="cuda") for _ in range(G)]   # owner o's slots
+    cbd = cb.cuda()
+    nbytes = lib.vqg_rowparallel_workspace_bytes(M, N, kl, v, 256, 1, 128)
+    ws = torch.zeros(max(nbytes, 1), dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    for r in range(G):
+        xl = x[:, r * kl:(r + 1) * kl].contiguous().cuda()
+        il = shard_weights_k(idx, G, r).cuda()
+        arr = (ctypes.c_void_p * G)(*[parts[o][r].data_ptr() for o in range(G)])
+        st = lib.vqg_gemm_rowparallel(xl.data_ptr(), il.data_ptr(), cbd.data_ptr(), arr, G, M, N, kl, v, 256, 1, 128,
+                                      ws.data_ptr() if nbytes else None, nbytes, stream)
+        assert st == 0
+        torch.cuda.synchronize()
+    assert V.device_status() == 0
+    ys = []
+    for o in range(G):
+        y = torch.empty(M, nl, dtype=torch.float16, device="cuda")
+        assert lib.vqg_reduce_slots(parts[o].data_ptr(), y.data_ptr(), G, M, nl, nl, stream) == 0
+        ys.append(y)
+    torch.cuda.synchronize()
+    assert_within_tolerance(torch.cat(ys, dim=1).cpu(), full)
+    # slot sums are exactly the fp32 sum of the fp16 partials, in slot order
+    want = (parts[0][0].float() + parts[0][1].float()).half()
+    assert torch.equal(bits(ys[0]), bits(want))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_row_parallel_two_ranks_over_nvlink():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", VQG_WORKER_MODE="rowparallel")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29512", os.path.join(ROOT, "tests", "_sharded_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert p.returncode == 0 and "SHARDED_OK" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]

@@ -76,3 +76,54 @@ def test_two_rank_gather_equals_single_rank(rpc):
     for p in procs:
         p.join(timeout=60)
     assert res == [(0, True), (1, True)]
+
+
+def test_k_slices_cover_the_matrix():
+    from vq_gemm_b200.sharded import shard_weights_k
+    _, idx, _ = O.make_bl_inputs(1, 256, 64, 4, 256, 0, seed=0)
+    parts = [shard_weights_k(idx, 4, r) for r in range(4)]
+    assert all(p.is_contiguous() and p.shape == (64, 16) for p in parts)
+    assert torch.equal(torch.cat(parts, dim=1), idx)
+    with pytest.raises(ValueError):
+        shard_weights_k(idx, 3, 0)      # 64 index columns do not split 3 ways
+    with pytest.raises(ValueError):
+        shard_weights_k(idx, 2, 2)
+
+
+def _rowparallel_worker(rank, world, port, M, K, N, v, C, rpc, q):
+    # the row-parallel protocol with the oracle standing in for the CUDA kernels: every rank multiplies its K
+    # slice, rounds its partial blocks to fp16, "stores" block o into slot `rank` of owner o (an all-to-all
+    # here), and every owner sums its slots in fp32 in rank order
+    from vq_gemm_b200.sharded import shard_weights_k
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=13)
+    kl = K // world
+    partial = O.vq_gemm_bl(x[:, rank * kl:(rank + 1) * kl].contiguous(), shard_weights_k(idx, world, rank), cb, rpc)
+    nl = N // world
+    send = [partial[:, o * nl:(o + 1) * nl].contiguous() for o in range(world)]
+    # gloo has no all_to_all: gather every rank's blocks and pick mine
+    everything = [torch.empty(world, M, nl, dtype=torch.float16) for _ in range(world)]
+    dist.all_gather(everything, torch.stack(send))
+    slots = [everything[r][rank] for r in range(world)]
+    acc = torch.zeros(M, nl, dtype=torch.float32)
+    for s in slots:
+        acc += s.float()
+    y_local = acc.half()
+    full = O.vq_gemm_bl(x, idx, cb, rpc)[:, rank * nl:(rank + 1) * nl]
+    q.put((rank, bool(O.check_tolerance(y_local, full)["ok"])))
+    dist.destroy_process_group()
+
+
+def test_two_rank_row_parallel_reduce_scatter():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rowparallel_worker, args=(r, 2, port, 6, 256, 512, 8, 256, 128, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert res == [(0, True), (1, True)]

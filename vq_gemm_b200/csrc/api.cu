@@ -298,6 +298,53 @@ int vqg_gemm_swiglu(const void* x, const void* idx, const void* codebook, void* 
   return launch_swiglu(tmp, static_cast<__half*>(y), M, N_out, N_out, s);
 }
 
+size_t vqg_rowparallel_workspace_bytes(int M, int N, int K_local, int v, int C, int idx_bytes, int rows_per_codebook) {
+  if (M <= 0 || N <= 0 || K_local <= 0) return 0;
+  void* dummy = reinterpret_cast<void*>(static_cast<uintptr_t>(1024));
+  Problem p = make_problem(dummy, dummy, dummy, dummy, M, N, K_local, v, C, idx_bytes, rows_per_codebook, N);
+  if (p.M > 128 && tensor_ts_supported(p)) return tensor_ts_workspace_bytes(p);
+  const size_t inner = vqg_workspace_bytes(M, N, K_local, v, C, idx_bytes, rows_per_codebook, VQG_LAYOUT_BL, VQG_PATH_AUTO);
+  return swiglu_scratch_offset(inner) + static_cast<size_t>(M) * N * 2;
+}
+
+int vqg_gemm_rowparallel(const void* x_local, const void* idx_local, const void* codebook, void* const* part_of_owner,
+                         int nranks, int M, int N, int K_local, int v, int C, int idx_bytes, int rows_per_codebook,
+                         void* workspace, size_t workspace_bytes, void* stream) {
+  if (nranks < 1 || nranks > 8 || !part_of_owner || N < 0 || (N > 0 && N % (nranks * 128) != 0)) return VQG_ERR_BAD_ARG;
+  for (int o = 0; o < nranks; ++o)
+    if (!part_of_owner[o] || !aligned(part_of_owner[o], 16)) return VQG_ERR_BAD_ARG;
+  const int st = check_common(x_local, idx_local, codebook, part_of_owner[0], M, N, K_local, v, C, idx_bytes, VQG_LAYOUT_BL);
+  if (st != VQG_OK) return st;
+  if (M == 0 || N == 0) return VQG_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int cols = N / nranks;
+  Problem p = make_problem(x_local, idx_local, codebook, part_of_owner[0], M, N, K_local, v, C, idx_bytes, rows_per_codebook, N);
+  if (p.M > 128 && tensor_ts_supported(p)) {
+    p.n_owners = nranks;
+    p.owner_cols = cols;
+    for (int o = 0; o < nranks; ++o) p.owner_part[o] = static_cast<__half*>(part_of_owner[o]);
+    if (ensure_status_word() != cudaSuccess) return VQG_ERR_NO_DEVICE;
+    return launch_tensor_ts(p, workspace, workspace_bytes, s, /*gated=*/false);
+  }
+  // other shapes: the product into scratch, then one kernel that hands every owner its block
+  const size_t need = vqg_workspace_bytes(M, N, K_local, v, C, idx_bytes, rows_per_codebook, VQG_LAYOUT_BL, VQG_PATH_AUTO);
+  const size_t inner = swiglu_scratch_offset(need);
+  if (!workspace || workspace_bytes < inner + static_cast<size_t>(M) * N * 2 || !aligned(workspace, 1024)) return VQG_ERR_WORKSPACE;
+  __half* tmp = reinterpret_cast<__half*>(static_cast<unsigned char*>(workspace) + inner);
+  Problem q = make_problem(x_local, idx_local, codebook, tmp, M, N, K_local, v, C, idx_bytes, rows_per_codebook, N);
+  const int st2 = run(q, VQG_LAYOUT_BL, VQG_PATH_AUTO, need ? workspace : nullptr, need, s);
+  if (st2 != VQG_OK) return st2;
+  __half* owners[8];
+  for (int o = 0; o < nranks; ++o) owners[o] = static_cast<__half*>(part_of_owner[o]);
+  return launch_scatter_blocks(tmp, owners, nranks, M, cols, s);
+}
+
+int vqg_reduce_slots(const void* part_local, void* y_local, int nranks, int M, int cols, long long ld_y, void* stream) {
+  if (!part_local || !y_local) return (M == 0 || cols == 0) ? VQG_OK : VQG_ERR_BAD_ARG;
+  return launch_reduce_slots(static_cast<const __half*>(part_local), static_cast<__half*>(y_local), nranks, M, cols, ld_y,
+                             static_cast<cudaStream_t>(stream));
+}
+
 int vqg_gemm_small_batch_noalloc(const void* x, const void* idx, const void* codebook, void* y, int M, int N, int K,
                                  int v, int C, int idx_bytes, int rows_per_codebook, void* stream) {
   const int st = check_common(x, idx, codebook, y, M, N, K, v, C, idx_bytes, VQG_LAYOUT_BL);

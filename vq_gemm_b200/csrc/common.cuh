@@ -24,6 +24,12 @@ struct Problem {
   // multi-GPU epilogue: additional copies of the output block (peer-mapped), may be 0
   int n_peers;
   __half* peer_y[8];
+  // row-parallel (K-sharded) mode: the output columns are cut into n_owners blocks of owner_cols columns and
+  // block o is written, as this rank's partial sum, to owner_part[o] ([M, owner_cols] fp16, possibly peer
+  // memory) instead of y.  0 = off.
+  int n_owners;
+  int owner_cols;
+  __half* owner_part[8];
 };
 
 // Device status word: 0 = fine; otherwise the code of the first bounded wait that ran out.
@@ -72,6 +78,10 @@ size_t tensor_ts_workspace_bytes(const Problem& p);
 // gated: weight rows are (gate, up) pairs and Y[M, N/2] = SiLU(X g) * (X u)
 int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s, bool gated = false);
 // elementwise SiLU(g) * u over interleaved columns: in [M, 2*n_out] -> out [M, n_out] (leading dimension ld_out)
+// y[M, cols] (leading dimension ld_y) = sum over s < slots of part[s][M][cols] (fp16 in, fp32 sum in slot order)
+int launch_reduce_slots(const __half* part, __half* y, int slots, int M, int cols, long long ld_y, cudaStream_t s);
+// tmp[M, n_owners*cols] -> owner_part[o][M, cols] for every o (plain stores, possibly to peer memory)
+int launch_scatter_blocks(const __half* tmp, __half* const* owner_part, int n_owners, int M, int cols, cudaStream_t s);
 int launch_swiglu(const __half* in, __half* out, int M, int n_out, long long ld_out, cudaStream_t s);     // weights through tensor memory (A operand)
 bool small_ts_supported(const Problem& p);
 size_t small_ts_workspace_bytes(const Problem& p);

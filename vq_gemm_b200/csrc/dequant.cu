@@ -330,4 +330,75 @@ int launch_swiglu(const __half* in, __half* out, int M, int n_out, long long ld_
   return cuda_status(cudaGetLastError());
 }
 
+namespace {
+// Row-parallel mode, second step on the owner: y = sum over slots of the ranks' partial blocks.  fp16 in,
+// fp32 sum in slot (= rank) order, one rounding; 8 values per thread (16-byte loads).
+__global__ void reduce_slots_kernel(const __half* __restrict__ part, __half* __restrict__ y, int slots, int M, int cols,
+                                    long long ld_y) {
+  const long long vec_per_row = cols / 8;
+  const long long total = static_cast<long long>(M) * vec_per_row;
+  const long long slot_stride = static_cast<long long>(M) * cols;
+  for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+       e += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long m = e / vec_per_row;
+    const long long c = (e - m * vec_per_row) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < slots; ++s) {
+      const uint4 v = *reinterpret_cast<const uint4*>(part + s * slot_stride + m * cols + c);
+      const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); acc[2 * i] += f.x; acc[2 * i + 1] += f.y; }
+    }
+    uint4 o;
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) oh[i] = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
+    *reinterpret_cast<uint4*>(y + m * ld_y + c) = o;
+  }
+}
+
+struct OwnerPtrs { __half* p[8]; };
+// tmp [M, n_owners*cols] -> block o to owner_part[o] [M, cols]; 16-byte stores (plain, possibly to peer memory)
+__global__ void scatter_blocks_kernel(const __half* __restrict__ tmp, OwnerPtrs owners, int n_owners, int M, int cols) {
+  const long long vec_per_row = static_cast<long long>(n_owners) * cols / 8;
+  const long long total = static_cast<long long>(M) * vec_per_row;
+  for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+       e += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long m = e / vec_per_row;
+    const long long c = (e - m * vec_per_row) * 8;
+    const int o = static_cast<int>(c / cols);
+    const uint4 v = *reinterpret_cast<const uint4*>(tmp + m * (static_cast<long long>(n_owners) * cols) + c);
+    *reinterpret_cast<uint4*>(owners.p[o] + m * cols + (c - static_cast<long long>(o) * cols)) = v;
+  }
+}
+}  // namespace
+
+int launch_reduce_slots(const __half* part, __half* y, int slots, int M, int cols, long long ld_y, cudaStream_t s) {
+  if (slots < 1 || M < 0 || cols < 0 || cols % 8 != 0 || ld_y % 8 != 0) return VQG_ERR_BAD_ARG;
+  if (M == 0 || cols == 0) return VQG_OK;
+  if (reinterpret_cast<uintptr_t>(part) % 16 || reinterpret_cast<uintptr_t>(y) % 16) return VQG_ERR_BAD_ARG;
+  const long long total = static_cast<long long>(M) * (cols / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  reduce_slots_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(part, y, slots, M, cols, ld_y);
+  count_launch();
+  return cuda_status(cudaGetLastError());
+}
+
+int launch_scatter_blocks(const __half* tmp, __half* const* owner_part, int n_owners, int M, int cols, cudaStream_t s) {
+  if (n_owners < 1 || n_owners > 8 || cols % 8 != 0) return VQG_ERR_BAD_ARG;
+  if (M <= 0 || cols <= 0) return VQG_OK;
+  OwnerPtrs o{};
+  for (int i = 0; i < n_owners; ++i) {
+    if (!owner_part[i] || reinterpret_cast<uintptr_t>(owner_part[i]) % 16) return VQG_ERR_BAD_ARG;
+    o.p[i] = owner_part[i];
+  }
+  const long long total = static_cast<long long>(M) * n_owners * (cols / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  scatter_blocks_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(tmp, o, n_owners, M, cols);
+  count_launch();
+  return cuda_status(cudaGetLastError());
+}
+
 }  // namespace vqg

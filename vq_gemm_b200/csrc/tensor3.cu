@@ -70,6 +70,9 @@ struct TsParams {
   int* ws_counter;           // [tile][rank] arrivals of contributors; zero between calls
   int n_peers;
   __half* peer_y[8];
+  // row-parallel mode: the tile goes, as this rank's partial sum, to the buffer of the rank that owns its
+  // columns (tensor map `owner` of PeerMaps, local or peer memory) and nowhere else
+  int n_owners, owner_cols;
 };
 
 __device__ __forceinline__ int pair_begin(int b, int q, int r) { return b * q + (b < r ? b : r); }
@@ -82,7 +85,7 @@ __device__ __forceinline__ int pair_of_unit(int u, int q, int r) {
 // Tensor maps of the other ranks' Y blocks (sharded mode): the staging tile goes to each of them with one
 // TMA tensor store (no multicast; an ordinary asynchronous bulk store whose destination is peer memory).
 struct alignas(64) PeerMaps {
-  CUtensorMap m[7];
+  CUtensorMap m[8];
 };
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
@@ -453,15 +456,22 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           }
         }
       }
-      if (p.n_peers > 0) fence_async_smem();   // this thread's staging writes become visible to the TMA unit
+      const bool tma_out = p.n_peers > 0 || p.n_owners > 0;
+      if (tma_out) fence_async_smem();   // this thread's staging writes become visible to the TMA unit
       if (!(ok = epi_sync())) break;   // the whole tile is in shared memory
-      if (p.n_peers > 0 && warp == 2 && lane == 0) {
-        // peers: one tensor store of the [256 x 128] tile per rank; rows beyond M and columns beyond the
-        // block are clipped by the tensor map.  The SM's load/store pipe stays free for the index loads.
-        for (int q = 0; q < p.n_peers; ++q) tma_store_2d(&peer_maps.m[q], n0, m0, smem_u32(stg));
+      if (tma_out && warp == 2 && lane == 0) {
+        if (p.n_owners > 0) {
+          // row-parallel: this rank's partial tile goes to the owner of these output columns
+          const int o = n0 / p.owner_cols;
+          tma_store_2d(&peer_maps.m[o], n0 - o * p.owner_cols, m0, smem_u32(stg));
+        } else {
+          // peers: one tensor store of the [256 x 128] tile per rank; rows beyond M and columns beyond the
+          // block are clipped by the tensor map.  The SM's load/store pipe stays free for the index loads.
+          for (int q = 0; q < p.n_peers; ++q) tma_store_2d(&peer_maps.m[q], n0, m0, smem_u32(stg));
+        }
         tma_store_commit();
       }
-      {
+      if (p.n_owners == 0) {
         constexpr int LPR = ROW_BYTES / 16, RPW = 32 / LPR;   // lanes per staged row, rows per warp instruction
         const int rsel = lane / LPR, chunk = lane % LPR;
         const int ncol = n0 + chunk * 8;
@@ -474,10 +484,10 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           }
         }
       }
-      if (p.n_peers > 0 && warp == 2 && lane == 0) tma_store_wait_read();   // the TMA unit has read the tile
+      if (tma_out && warp == 2 && lane == 0) tma_store_wait_read();   // the TMA unit has read the tile
       if (!(ok = epi_sync())) break;   // the tile is rewritten by the next tile's transposition
     }
-    if (p.n_peers > 0 && warp == 2 && lane == 0) tma_store_wait_all();   // peer stores done before the kernel ends
+    if ((p.n_peers > 0 || p.n_owners > 0) && warp == 2 && lane == 0) tma_store_wait_all();   // stores done before the kernel ends
   } else {
     // ------------------------------- dequant warps ------------------------------------------
     constexpr int ENTRY_LOG2 = (V == 4) ? 3 : 4;       // bytes per codebook entry
@@ -692,6 +702,15 @@ int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s
     if (reinterpret_cast<uintptr_t>(p.peer_y[q]) % 16) return VQG_ERR_BAD_ARG;
     if (!make_y_map(&pm.m[q], p.peer_y[q], p.M, p.N, p.ld_y)) return VQG_ERR_LAUNCH;
   }
+  if (p.n_owners > 0) {
+    if (p.n_peers != 0 || gated || p.n_owners > 8 || p.owner_cols % 128 != 0 ||
+        static_cast<long long>(p.n_owners) * p.owner_cols != p.N)
+      return VQG_ERR_UNSUPPORTED;
+    for (int o = 0; o < p.n_owners; ++o) {
+      if (!p.owner_part[o] || reinterpret_cast<uintptr_t>(p.owner_part[o]) % 16) return VQG_ERR_BAD_ARG;
+      if (!make_y_map(&pm.m[o], p.owner_part[o], p.M, p.owner_cols, p.owner_cols)) return VQG_ERR_LAUNCH;
+    }
+  }
   TsParams tp{};
   tp.idx = static_cast<const unsigned char*>(p.idx);
   tp.cb = p.cb;
@@ -704,6 +723,8 @@ int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s
   tp.n_tiles = (p.N + BN - 1) / BN;
   tp.n_peers = p.n_peers;
   for (int i = 0; i < 8; ++i) tp.peer_y[i] = p.peer_y[i];
+  tp.n_owners = p.n_owners;
+  tp.owner_cols = p.owner_cols;
   const int max_pairs = sm_count() / 2;
   const int tiles = tp.m_tiles * tp.n_tiles;
   const int ksteps = p.K / (2 * BK);

@@ -15,6 +15,13 @@ Two ways of assembling Y:
 ``mode="nccl"``   each rank computes its [M, N/G] block, NCCL all-gathers the blocks into
                   [G, M, N/G] and a re-layout copy interleaves them into [M, N].
 
+``RowParallelVQGemm`` is the K-sharded counterpart for the second half of a tensor-parallel MLP:
+each rank multiplies its slice of the input features by its K slice of the weights, the partial
+[M, N/G] blocks go straight to their owners (TMA tensor stores from the GEMM epilogue into slot
+``rank`` of the owner's symmetric buffer), one barrier, and every owner sums its G slots: a fused
+GEMM + reduce-scatter.  With the N-sharded first half leaving its output on the rank that
+computed it, the intermediate activation is never gathered.
+
 The reference has no multi-GPU code (device 0 is hard-coded, strategy_1/src.cu:343).
 """
 from __future__ import annotations
@@ -143,4 +150,80 @@ class ShardedVQGemm:
         vq_gemm(x, idx_local, cb_local, rows_per_codebook=rows_per_codebook, layout="bl", out=self._block)
         dist.all_gather_into_tensor(self._gathered.view(self.world * M, self.n_local), self._block, group=self.group)
         self.y.copy_(interleave_blocks(self._gathered))
+        return self.y
+
+
+def shard_weights_k(idx: torch.Tensor, world: int, rank: int) -> torch.Tensor:
+    """K slice of an index matrix [N, K/v] for the row-parallel product: columns
+    ``[rank * J/G, (rank + 1) * J/G)`` with ``J = K/v``, as a contiguous copy."""
+    J = idx.shape[1]
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError("bad rank / world size")
+    if J % world:
+        raise ValueError(f"K/v = {J} does not split into {world} equal slices")
+    j = J // world
+    return idx[:, rank * j:(rank + 1) * j].contiguous()
+
+
+class RowParallelVQGemm:
+    """Fused K-sharded product + reduce-scatter: ``y_local[M, N/G] = (sum_r x_r @ W_r^T)[:, block of this rank]``.
+
+    Collective construction (same M and N on every rank of ``group``).  The per-rank partial blocks
+    live in symmetric memory as two sets of G slots used in turn, so that one barrier per step (after
+    the stores, before the sum) is enough."""
+
+    def __init__(self, M: int, N: int, *, group: Optional[dist.ProcessGroup] = None, device: Optional[torch.device] = None):
+        if dist.is_available() and dist.is_initialized():
+            self.group = group if group is not None else dist.group.WORLD
+            self.world = dist.get_world_size(self.group)
+            self.rank = dist.get_rank(self.group)
+        else:
+            self.group, self.world, self.rank = None, 1, 0
+        if N % (self.world * 128):
+            raise ValueError(f"N={N} does not split into {self.world} blocks of a multiple of 128 columns")
+        self.M, self.N, self.n_local = M, N, N // self.world
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self._hdl = None
+        G = self.world
+        if G == 1:
+            self._part = torch.empty((1, 1, M, N), dtype=torch.float16, device=self.device)
+            self._bases = [self._part.data_ptr()]
+        else:
+            import torch.distributed._symmetric_memory as symm_mem
+            self._part = symm_mem.empty((2, G, M, self.n_local), dtype=torch.float16, device=self.device)
+            self._hdl = symm_mem.rendezvous(self._part, self.group)
+            self._bases = [int(p) for p in self._hdl.buffer_ptrs]
+            if self._bases[self.rank] != self._part.data_ptr():
+                raise RuntimeError("symmetric memory: local buffer pointer mismatch")
+        self.y = torch.empty((M, self.n_local), dtype=torch.float16, device=self.device)
+        self._step = 0
+        self._ws = None
+        slot_bytes = M * self.n_local * 2
+        self._arrs = [(ctypes.c_void_p * G)(*[b + (par * G + self.rank) * slot_bytes for b in self._bases])
+                      for par in range(2 if G > 1 else 1)]
+
+    def __call__(self, x_local: torch.Tensor, idx_local: torch.Tensor, codebook: torch.Tensor, rows_per_codebook: int = 0):
+        """x_local [M, K/G], idx_local [N, K/(G v)] (``shard_weights_k``), codebook: all groups.  Returns this
+        rank's block of the summed product; valid after the call on the current stream."""
+        lib = _lib.load()
+        M, K_local = x_local.shape
+        if M != self.M or idx_local.shape[0] != self.N:
+            raise RuntimeError("shapes do not match the buffers this object was built for")
+        cb3 = codebook if codebook.dim() == 3 else codebook.unsqueeze(0)
+        _, C, v = cb3.shape
+        ib = 1 if idx_local.dtype == torch.uint8 else 2
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        nbytes = lib.vqg_rowparallel_workspace_bytes(M, self.N, K_local, v, C, ib, rows_per_codebook)
+        if nbytes and (self._ws is None or self._ws.numel() < nbytes):
+            self._ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        par = (self._step & 1) if self.world > 1 else 0
+        self._step += 1
+        st = lib.vqg_gemm_rowparallel(x_local.data_ptr(), idx_local.data_ptr(), codebook.data_ptr(), self._arrs[par], self.world,
+                                      M, self.N, K_local, v, C, ib, rows_per_codebook,
+                                      self._ws.data_ptr() if nbytes else None, self._ws.numel() if nbytes else 0, stream)
+        _lib.check(st, "vqg_gemm_rowparallel")
+        if self._hdl is not None:
+            self._hdl.barrier()   # every rank's partial of my block has landed in my slots
+        st = lib.vqg_reduce_slots(self._part[par].data_ptr(), self.y.data_ptr(), self.world, M, self.n_local, self.n_local, stream)
+        _lib.check(st, "vqg_reduce_slots")
         return self.y

@@ -18,6 +18,8 @@ each rank owns N/G output columns and the fp16 output is assembled on every rank
                the M <= 16 workloads), from CUDA-event time of the kernel alone.
 ``shapes``     (N=1 only) the other single-GPU configurations, each with its own roofline, and
                cuBLAS fp16 (torch.matmul) on pre-dequantised weights for the prefill shapes.
+``mlp70b``     (every N) the whole tensor-parallel MLP: gated up half N-sharded without a gather, down half
+               K-sharded with the fused reduce-scatter; max over ranks.
 ``gated_mlp_up`` (N=1 only) SiLU(X g) * (X u) fused into the GEMM epilogue on the 70B gate+up shape.
 ``quantizer``  (N=1 only) the step before the product on a C4-sized layer: nearest-entry search
                against the fp32 pipe, one exact k-means update, 12-bit pack/unpack against HBM.
@@ -316,6 +318,38 @@ def _gated(V, peaks):
             "product_then_elementwise_ms": u_ms, "speedup": u_ms / f_ms, "timing": "alternating blocks of 10"}
 
 
+def _mlp(V, world, rank, dev, steps, warmup, barrier, reduce_max):
+    """Tensor-parallel Llama-3-70B MLP on M = 2048 tokens, all of it compressed (1 bit per weight): the gated
+    up half N-sharded (each rank keeps its slice of the activation, nothing is gathered) and the down half
+    K-sharded with the fused reduce-scatter.  Every rank ends with its [M, 8192/G] block of the output."""
+    from vq_gemm_b200.formats import VQShape, make_inputs
+    from vq_gemm_b200.sharded import RowParallelVQGemm, shard_weights_k
+    M, H, I = 2048, 8192, 28672
+    up = VQShape("up", M, H, 2 * I, 8, 256, 128, 1, "tensor")
+    down = VQShape("down", M, I, H, 8, 256, 128, 1, "tensor")
+    n_up = 2 * I // world
+    x, idx_u, cb_u = make_inputs(up, seed=1, device=dev, n_rows=n_up, row0=rank * n_up)
+    _, idx_d_full, cb_d = make_inputs(down, seed=2, device=dev)
+    idx_d = shard_weights_k(idx_d_full, world, rank)
+    del idx_d_full
+    act = torch.empty((M, n_up // 2), dtype=torch.float16, device=dev)
+    rp = RowParallelVQGemm(M, H, device=dev)
+
+    def step():
+        V.vq_gemm_swiglu(x, idx_u, cb_u, rows_per_codebook=128, out=act)
+        rp(act, idx_d, cb_d, 128)
+
+    def up_only():
+        V.vq_gemm_swiglu(x, idx_u, cb_u, rows_per_codebook=128, out=act)
+
+    ms = reduce_max(_time_loop(step, steps, warmup, barrier))
+    up_ms = reduce_max(_time_loop(up_only, max(5, steps // 2), 2, barrier))
+    flops = 2.0 * M * H * 2 * I + 2.0 * M * I * H
+    return {"workload": "llama3-70b MLP, M=2048, v=8, C=256: gated up (N-sharded, not gathered) + down (K-sharded, reduce-scatter)",
+            "ms_per_step": ms, "tflops": flops / ms / 1e9, "up_ms": up_ms, "down_and_reduce_scatter_ms": ms - up_ms,
+            "reduce_scatter_bytes_per_gpu": int(M * H * 2 * (world - 1) / world)}
+
+
 def _reference_cuda_kernels(V):
     """Optional baseline leg (--baselines): the reference's own CUDA kernels, rebuilt unmodified for
     sm_100a by oracle/build_ref.py, on data in the reference's format; and this library on the same data.
@@ -439,6 +473,7 @@ def main():
     ap.add_argument("--workload", default="c5_mlp70b")
     ap.add_argument("--mode", default="peer", choices=["peer", "nccl"], help="how the N-sharded output is assembled")
     ap.add_argument("--no-shapes", action="store_true", help="skip the per-configuration table")
+    ap.add_argument("--no-mlp", action="store_true", help="skip the tensor-parallel MLP measurement")
     ap.add_argument("--baselines", action="store_true",
                     help="also time the reference's own CUDA kernels from oracle/_ref (N=1 only)")
     args = ap.parse_args()
@@ -593,6 +628,12 @@ def main():
         "clocks": clocks.summary(),
         "device_status": status,
     }
+    if not args.no_mlp:
+        try:
+            mlp = _mlp(V, world, rank, dev, args.steps, args.warmup, barrier, reduce_max)
+        except Exception as e:
+            mlp = {"error": repr(e)}
+        line["mlp70b"] = mlp
     if world == 1 and rank == 0 and not args.no_shapes:
         shapes = []
         for name in ("c1_cpu_ref", "c2_decode", "c3_small_batch", "c4_prefill"):

@@ -56,7 +56,8 @@ enum {
   VQG_PATH_TENSOR = 3,   /* tcgen05 / TMEM / TMA warp-specialised kernel, fused dequant, 1 CTA  */
   VQG_PATH_TWO_PHASE = 4,/* dequantise to workspace, then the dense tcgen05 kernel              */
   VQG_PATH_TENSOR_PAIR = 5, /* the fused kernel on CTA pairs (tcgen05 cta_group::2, 256x256 tiles) */
-  VQG_PATH_TENSOR_TS = 6,  /* CTA pairs, dequantised weights as the MMA's tensor-memory operand    */
+  VQG_PATH_TENSOR_TS = 6,  /* CTA pairs, dequantised weights as the MMA's tensor-memory operand;
+                              with a workspace the K loops are dealt out evenly over the pairs    */
   VQG_PATH_SMALL_TS = 7    /* M <= 128: tensor-memory operand, K loop split evenly over the SMs    */
 };
 

@@ -82,12 +82,21 @@ int auto_path(const Problem& p, int layout) {
     return dense_supported(p.M, p.N, p.K) && p.M >= 32 ? VQG_PATH_TWO_PHASE : VQG_PATH_GENERIC;
   }
   if (p.K == 0) return VQG_PATH_GENERIC;
-  // Up to 16 batch rows the register-level kernel wins while the codebook is small enough for its
-  // replicated shared-memory image (measured 10-12 us against 17-20 us); with large codebooks, and from
-  // 17 to 128 batch rows, the tensor-memory kernel with the even split of K is faster (29 us against 47 us).
-  if (p.M <= 16 && decode_supported(p) && (p.C <= 256 || !small_ts_supported(p))) return VQG_PATH_DECODE;
-  if (p.M <= 128 && small_ts_supported(p)) return VQG_PATH_SMALL_TS;
-  if (p.M > 128 && tensor_ts_supported(p)) return VQG_PATH_TENSOR_TS;
+  // Measured routing (B200, CUDA events).  Register-level decode kernel: best up to 4 batch rows, and up to 16
+  // while the problem is small (C1: 10.9 us against 13.3 us) and the codebook fits its replicated image; its
+  // cost grows with the batch on large matrices (M = 16, 29 MB of indices: 115 us against 50 us).  The
+  // small-batch tensor-memory kernel takes over from there up to 96 rows; above that the pair kernel with its
+  // 256-row batch tile is as fast or faster even half empty (M = 128: 38 us against 46 us on the C4 weights).
+  const double index_bytes = static_cast<double>(p.N) * (p.K / (p.v > 0 ? p.v : 1)) * p.idx_bytes;
+  const bool small_ok = small_ts_supported(p);
+  if (p.M <= 16 && decode_supported(p)) {
+    const bool large = index_bytes >= (p.M <= 8 ? 20e6 : 8e6);
+    const bool prefer_small = small_ok && p.M > 4 && (large || p.C > 256);
+    if (!prefer_small) return VQG_PATH_DECODE;
+  }
+  if (p.M <= 96 && small_ok) return VQG_PATH_SMALL_TS;
+  if (p.M > 96 && tensor_ts_supported(p)) return VQG_PATH_TENSOR_TS;
+  if (p.M <= 128 && small_ok) return VQG_PATH_SMALL_TS;
   if (p.M > 128 && tensor_pair_supported(p)) return VQG_PATH_TENSOR_PAIR;
   if (p.M > 16 && tensor_supported(p)) return VQG_PATH_TENSOR;
   if (p.M > 16 && dense_supported(p.M, p.N, p.K) && (p.v == 2 || p.v == 4 || p.v == 8)) return VQG_PATH_TWO_PHASE;

@@ -99,6 +99,10 @@ def kmeans_quantize(weight: torch.Tensor, *, v: int = 8, entries: int = 256, row
     for _ in range(iters):
         kmeans_update(weight, idx, cb, rows_per_codebook)
         assign(weight, cb, rows_per_codebook, out=idx)
+    # The small-batch product kernels read their weights before they wait for the kernel ahead of them on the
+    # stream (programmatic dependent launch): weights must be complete before such a launch is made.  This
+    # is an offline step, so one host-side wait here makes the returned tensors safe to use immediately.
+    torch.cuda.current_stream(weight.device).synchronize()
     return idx, cb
 
 

@@ -86,7 +86,13 @@ VQG_API size_t vqg_workspace_counter_bytes(void);
  *   idx_bytes          1 (uint8) or 2 (uint16)
  *   rows_per_codebook  BL: output rows sharing a codebook, 0 = one codebook for the matrix
  *                      REF: ignored (8 output columns per codebook)
- *   stream             cudaStream_t (NULL = legacy default stream, as the reference uses) */
+ *   stream             cudaStream_t (NULL = legacy default stream, as the reference uses)
+ * Ordering: X, Y and the workspace follow the stream's order.  The WEIGHTS (idx, codebook) are
+ * taken to be constant: for M <= 128 the kernels are launched with programmatic stream
+ * serialisation and read indices and codebooks while the kernel ahead of them on the stream may
+ * still be finishing (they wait for it before touching X, Y or the workspace).  If another KERNEL
+ * on the same stream has just written the weights, put a synchronisation (event, host wait)
+ * between it and this call; copies (cudaMemcpyAsync) need nothing. */
 VQG_API int vqg_gemm(const void* x, const void* idx, const void* codebook, void* y,
              int M, int N, int K, int v, int C, int idx_bytes, int rows_per_codebook,
              int layout, void* workspace, size_t workspace_bytes, void* stream);

@@ -79,6 +79,11 @@ VQG_API size_t vqg_workspace_bytes(int M, int N, int K, int v, int C, int idx_by
                            int rows_per_codebook, int layout, int path);
 VQG_API size_t vqg_workspace_counter_bytes(void);
 
+/* The kernel (VQG_PATH_*) that VQG_PATH_AUTO resolves to for a problem with 1024-byte aligned operands
+ * and ld_y = N.  Routing is by measurement on B200: decode kernel up to 4 batch rows and for small
+ * matrices up to 16, small-batch tensor-memory kernel up to 96, CTA-pair kernel above. */
+VQG_API int vqg_auto_path(int M, int N, int K, int v, int C, int idx_bytes, int rows_per_codebook, int layout);
+
 /* Y = X * dequant(idx, codebook)^T.  Replaces `torch::Tensor e2e_gemm(input, w, codebook)`
  * (reference bind.cpp:3,7; host launchers strategy_2/bsz128/src.cu:255-316 and siblings).
  *   N                  output columns (BL: rows of idx; REF: 2*Nq)

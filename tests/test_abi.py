@@ -98,3 +98,20 @@ def test_python_layer_refuses_cpu_tensors():
         V.vq_gemm(x, idx, cb)
     with pytest.raises(RuntimeError, match="no CPU path"):
         V.gemm(x, x.t().contiguous())
+
+
+def test_routing_of_the_benchmark_configurations(lib):
+    P = _lib.PATHS
+    auto = lambda *a: lib.vqg_auto_path(*a)
+    assert auto(16, 4096, 4096, 4, 256, 1, 0, 0) == P["decode"]          # C1: small matrix, 16 rows
+    assert auto(1, 11008, 4096, 4, 256, 1, 128, 0) == P["decode"]        # C2
+    assert auto(16, 8192, 8192, 8, 4096, 2, 0, 0) == P["small_ts"]       # C3: 4096-entry codebook
+    assert auto(4096, 14336, 4096, 4, 256, 1, 128, 0) == P["tensor_ts"]  # C4
+    assert auto(2048, 28672, 8192, 8, 256, 1, 128, 0) == P["tensor_ts"]  # C5
+    assert auto(16, 28672, 8192, 8, 256, 1, 128, 0) == P["small_ts"]     # 16 rows on a large matrix
+    assert auto(4, 28672, 8192, 8, 256, 1, 128, 0) == P["decode"]
+    assert auto(64, 28672, 8192, 8, 256, 1, 128, 0) == P["small_ts"]
+    assert auto(128, 28672, 8192, 8, 256, 1, 128, 0) == P["tensor_ts"]
+    assert auto(130, 96, 192, 4, 256, 1, 32, 0) == P["two_phase"]        # ragged K: dequantise, then the dense kernel
+    assert auto(130, 96, 192, 3, 256, 1, 32, 0) == P["generic"]          # odd sub-vector length: CUDA-core kernel
+    assert auto(2048, 1280, 4096, 2, 256, 1, 0, 1) == P["two_phase"]     # the reference's own format

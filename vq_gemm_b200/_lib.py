@@ -35,6 +35,7 @@ SIGNATURES = {
     "vqg_rowparallel_workspace_bytes": (c_size_t, [c_int] * 7),
     "vqg_gemm_rowparallel": (c_int, [c_void_p] * 3 + [POINTER(c_void_p)] + [c_int] * 8 + [c_void_p, c_size_t, c_void_p]),
     "vqg_reduce_slots": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p]),
+    "vqg_auto_path": (c_int, [c_int] * 8),
     "vqg_selftest_bounded_wait": (c_int, [c_longlong, c_void_p]),
     "vqg_quantize_assign": (c_int, [c_void_p] * 3 + [c_int] * 6 + [c_void_p]),
     "vqg_quantize_workspace_bytes": (c_size_t, [c_int] * 4),

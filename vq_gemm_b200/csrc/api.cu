@@ -171,6 +171,13 @@ const char* vqg_status_string(int status) {
   }
 }
 
+int vqg_auto_path(int M, int N, int K, int v, int C, int idx_bytes, int rows_per_codebook, int layout) {
+  if (M <= 0 || N <= 0 || K < 0) return VQG_PATH_GENERIC;
+  void* dummy = reinterpret_cast<void*>(static_cast<uintptr_t>(1024));
+  Problem p = make_problem(dummy, dummy, dummy, dummy, M, N, K, v, C, idx_bytes, rows_per_codebook, N);
+  return auto_path(p, layout);
+}
+
 size_t vqg_workspace_counter_bytes(void) { return kCounterBytes; }
 
 size_t vqg_workspace_bytes(int M, int N, int K, int v, int C, int idx_bytes, int rows_per_codebook, int layout,

@@ -22,6 +22,8 @@ pytestmark = pytest.mark.gpu
     (64, 1024, 512, 8, 256, 256, torch.uint8),        # 64 batch columns, 256 rows per codebook
     (128, 2048, 1024, 4, 256, 128, torch.uint8),      # 128 batch columns
     (100, 256, 19072, 4, 100, 128, torch.uint8),      # more tiles than SMs, ragged batch, C not a power of two
+    (16, 9728, 8192, 8, 256, 128, torch.uint8),       # large matrix: 256-wide pipeline stages (38 per tile, 64 tiles)
+    (40, 5120, 15360, 4, 256, 128, torch.uint8),      # the same with v = 4 and 64 batch columns
 ])
 def test_small_batch_matches_oracle(M, K, N, v, C, rpc, dt):
     x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=M * 7 + N, idx_dtype=dt, cb_sigma=0.05)

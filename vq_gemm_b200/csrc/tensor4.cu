@@ -21,7 +21,8 @@
 //                every 4th 64-wide K sub-step: 16-byte index load, lookups in the (replicated,
 //                conflict-free when C <= 256) codebook image, one tcgen05.st of 32 columns
 //
-// Work split: the (128-row tile, 128-wide K stage) pairs are numbered tile-major and divided evenly over
+// Work split: the (128-row tile, K stage) pairs (a stage is 128 K values, 256 on large matrices) are numbered
+// tile-major and divided evenly over
 // the CTAs, so every SM gets the same number of stages whatever N and K are; a CTA's range touches one
 // to a few tiles ("segments").  Every mbarrier wait is bounded (see tensor2.cu).
 //
@@ -36,7 +37,6 @@ namespace {
 
 constexpr int BNROWS = 128;      // weight rows per tile (TMEM lanes)
 constexpr int BK = 64;           // K values per sub-step
-constexpr int KS = 2;            // sub-steps per pipeline stage
 constexpr int kThreads = 800;    // 25 warps
 constexpr int kMmaWarps = 4;     // MMA-issuing warps (one lane each), each with its own accumulator
 constexpr int kEpiWarp0 = 1 + kMmaWarps;
@@ -44,7 +44,6 @@ constexpr int kDequantWarp0 = kEpiWarp0 + 4;
 constexpr int kDequantWarps = 16;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAColsPerSub = BK / 2;             // 32 columns: two fp16 per 32-bit column
-constexpr uint32_t kAColsPerStage = KS * kAColsPerSub;
 
 struct SmallParams {
   const unsigned char* idx;
@@ -66,18 +65,20 @@ struct SmallParams {
 // The X tiles are tiny at small M (4 KiB per stage for 16 batch columns) but every TMA load still takes
 // about a microsecond, far longer than the ~256 cycles a stage of lookups needs: X gets its own, deeper
 // ring (up to 16 stages) so that the loads run well ahead of the 4-stage tensor-memory ring of A.
-template <int NB>
+// KS: 64-wide sub-steps per pipeline stage.  2 by default; 4 (256-wide stages, half the hand-overs per K) for
+// matrices large enough that every CTA still gets many stages -- measured 14 % faster there, slower elsewhere.
+template <int NB, int KS>
 struct SmallSmem {
   static constexpr uint32_t kXSub = NB * BK * 2;                 // one 64-wide sub-tile of X
   static constexpr uint32_t kXStage = KS * kXSub;
   static constexpr uint32_t kXSubAligned = (kXSub + 1023u) & ~1023u;
   static constexpr uint32_t kXStageAligned = KS * kXSubAligned;
-  static constexpr int kXStages = NB <= 16 ? 16 : (NB <= 32 ? 12 : (NB <= 64 ? 6 : 4));
+  static constexpr int kXStages = (NB <= 16 ? 16 : (NB <= 32 ? 12 : (NB <= 64 ? 6 : 4))) * 2 / KS;
   static constexpr uint32_t kImage = kXStages * kXStageAligned;
   // A stages in tensor memory: what the 512 columns leave after the accumulators (4 x NB columns up to 64
   // batch columns, 2 x 128 above).  Measured: 7 stages are no faster than 4, and 2 issuing warps no slower
   // than 4 -- neither the ring depth nor the issue rate of one thread bounds this kernel
-  static constexpr int kStages = NB <= 16 ? 7 : (NB <= 32 ? 6 : 4);
+  static constexpr int kStages = KS == 2 ? (NB <= 16 ? 7 : (NB <= 32 ? 6 : 4)) : (NB <= 32 ? 3 : 2);
   static constexpr int kBarriers = 2 * kXStages + 2 * kStages + 3;
 };
 
@@ -123,10 +124,11 @@ __device__ __forceinline__ int cta_of_stage(int s, int q, int r) {
 }
 
 // V: sub-vector length; IB: index bytes; NB: batch columns of the MMA (16..128); REPL: replicated image.
-template <int V, int IB, int NB, bool REPL>
+template <int V, int IB, int NB, bool REPL, int KS>
 __global__ void __launch_bounds__(kThreads, 1)
 vq_small_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallParams p) {
-  using L = SmallSmem<NB>;
+  using L = SmallSmem<NB, KS>;
+  constexpr uint32_t kAColsPerStage = KS * kAColsPerSub;
   constexpr int ENTRY_LOG2 = (V == 4) ? 3 : 4;
   constexpr int REP_LOG2 = REPL ? (7 - ENTRY_LOG2) : 0;
   constexpr int ENTRY_SHIFT = ENTRY_LOG2 + REP_LOG2;
@@ -494,7 +496,7 @@ int sm_count() {
   return sms;
 }
 
-struct Plan { int ntiles, ksteps, grid, q, r, max_slots; bool repl; int nb; };
+struct Plan { int ntiles, ksteps, grid, q, r, max_slots; bool repl; int nb; int ks; };
 
 bool make_plan(const Problem& p, Plan& pl) {
   if (p.M < 1 || p.M > 128 || p.N < 1 || p.K < 128) return false;
@@ -512,10 +514,12 @@ bool make_plan(const Problem& p, Plan& pl) {
   if (!pl.repl && p.v != 8) return false;       // large codebooks only with 16-byte entries (64 KiB image)
   pl.nb = p.M <= 16 ? 16 : (p.M <= 32 ? 32 : (p.M <= 64 ? 64 : 128));
   pl.ntiles = p.N / 128;
-  pl.ksteps = p.K / 128;
+  const int sms = sm_count();
+  // 256-wide stages where a CTA still gets at least 16 of them (replicated codebooks only)
+  pl.ks = (pl.repl && p.K % 256 == 0 && static_cast<long long>(pl.ntiles) * (p.K / 256) >= 16LL * sms) ? 4 : 2;
+  pl.ksteps = p.K / (pl.ks * BK);
   const long long total = static_cast<long long>(pl.ntiles) * pl.ksteps;
   if (total > (1 << 30)) return false;
-  const int sms = sm_count();
   pl.grid = static_cast<int>(total < sms ? total : sms);
   pl.q = static_cast<int>(total / pl.grid);
   pl.r = static_cast<int>(total % pl.grid);
@@ -580,13 +584,19 @@ int launch_small_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s)
     count_launch();
     return cuda_status(e == cudaSuccess ? cudaGetLastError() : e);
   };
-#define VQG_SMALL(V_, IB_, NB_, R_) launch(vq_small_ts_kernel<V_, IB_, NB_, R_>, SmallSmem<NB_>::kImage, SmallSmem<NB_>::kBarriers)
-#define VQG_SMALL_NB(V_, IB_, R_)                                        \
-  (pl.nb == 16 ? VQG_SMALL(V_, IB_, 16, R_) : pl.nb == 32 ? VQG_SMALL(V_, IB_, 32, R_) \
-   : pl.nb == 64 ? VQG_SMALL(V_, IB_, 64, R_) : VQG_SMALL(V_, IB_, 128, R_))
-  if (p.v == 4) return VQG_SMALL_NB(4, 1, true);
-  if (p.idx_bytes == 1) return VQG_SMALL_NB(8, 1, true);
-  return pl.repl ? VQG_SMALL_NB(8, 2, true) : VQG_SMALL_NB(8, 2, false);
+#define VQG_SMALL(V_, IB_, NB_, R_, KS_) \
+  launch(vq_small_ts_kernel<V_, IB_, NB_, R_, KS_>, SmallSmem<NB_, KS_>::kImage, SmallSmem<NB_, KS_>::kBarriers)
+#define VQG_SMALL_NB(V_, IB_, R_, KS_)                                                           \
+  (pl.nb == 16 ? VQG_SMALL(V_, IB_, 16, R_, KS_) : pl.nb == 32 ? VQG_SMALL(V_, IB_, 32, R_, KS_) \
+   : pl.nb == 64 ? VQG_SMALL(V_, IB_, 64, R_, KS_) : VQG_SMALL(V_, IB_, 128, R_, KS_))
+  if (pl.ks == 4) {   // replicated codebooks only
+    if (p.v == 4) return VQG_SMALL_NB(4, 1, true, 4);
+    if (p.idx_bytes == 1) return VQG_SMALL_NB(8, 1, true, 4);
+    return VQG_SMALL_NB(8, 2, true, 4);
+  }
+  if (p.v == 4) return VQG_SMALL_NB(4, 1, true, 2);
+  if (p.idx_bytes == 1) return VQG_SMALL_NB(8, 1, true, 2);
+  return pl.repl ? VQG_SMALL_NB(8, 2, true, 2) : VQG_SMALL_NB(8, 2, false, 2);
 #undef VQG_SMALL_NB
 #undef VQG_SMALL
 }

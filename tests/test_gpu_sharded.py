@@ -66,8 +66,8 @@ def test_two_ranks_equal_single_gpu():
 
 
 def test_prefill_kernel_writes_every_rank_buffer():
-    # three ranks emulated on one GPU: the prefill kernel stores its block into its own buffer with plain
-    # stores and into the two others with TMA tensor stores (clipped at M = 300 and at the block's edge)
+    # three ranks emulated on one GPU: the prefill kernel stores its block into its own buffer and into the
+    # two others (rows beyond M = 300 and columns beyond the block's edge are not touched)
     import ctypes
     from vq_gemm_b200 import _lib
     M, K, N, G = 300, 1024, 1536, 3

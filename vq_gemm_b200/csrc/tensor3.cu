@@ -82,8 +82,8 @@ __device__ __forceinline__ int pair_of_unit(int u, int q, int r) {
   return u < big ? u / (q + 1) : r + (u - big) / q;
 }
 
-// Tensor maps of the other ranks' Y blocks (sharded mode): the staging tile goes to each of them with one
-// TMA tensor store (no multicast; an ordinary asynchronous bulk store whose destination is peer memory).
+// Tensor maps of the owners' partial-sum buffers (row-parallel mode): a finished tile goes to its owner with
+// one TMA tensor store (no multicast; an ordinary asynchronous bulk store whose destination may be peer memory).
 struct alignas(64) PeerMaps {
   CUtensorMap m[8];
 };
@@ -456,19 +456,14 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           }
         }
       }
-      const bool tma_out = p.n_peers > 0 || p.n_owners > 0;
+      const bool tma_out = p.n_owners > 0;
       if (tma_out) fence_async_smem();   // this thread's staging writes become visible to the TMA unit
       if (!(ok = epi_sync())) break;   // the whole tile is in shared memory
       if (tma_out && warp == 2 && lane == 0) {
-        if (p.n_owners > 0) {
-          // row-parallel: this rank's partial tile goes to the owner of these output columns
-          const int o = n0 / p.owner_cols;
-          tma_store_2d(&peer_maps.m[o], n0 - o * p.owner_cols, m0, smem_u32(stg));
-        } else {
-          // peers: one tensor store of the [256 x 128] tile per rank; rows beyond M and columns beyond the
-          // block are clipped by the tensor map.  The SM's load/store pipe stays free for the index loads.
-          for (int q = 0; q < p.n_peers; ++q) tma_store_2d(&peer_maps.m[q], n0, m0, smem_u32(stg));
-        }
+        // row-parallel: this rank's partial tile goes to the owner of these output columns with one tensor
+        // store (rows beyond M are clipped by the tensor map)
+        const int o = n0 / p.owner_cols;
+        tma_store_2d(&peer_maps.m[o], n0 - o * p.owner_cols, m0, smem_u32(stg));
         tma_store_commit();
       }
       if (p.n_owners == 0) {
@@ -480,14 +475,19 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           const int m = (4 * i + quarter) * RPW + rsel;
           if (m0 + m < p.M && ncol < n_out) {
             const uint4 v = *reinterpret_cast<const uint4*>(stg + m * ROW_BYTES + chunk * 16);
-            *reinterpret_cast<uint4*>(p.y + static_cast<size_t>(m0 + m) * p.ld_y + ncol) = v;
+            const size_t off = static_cast<size_t>(m0 + m) * p.ld_y + ncol;
+            *reinterpret_cast<uint4*>(p.y + off) = v;
+            // gather mode: the same 16 bytes to every peer's copy of Y.  (One TMA tensor store per peer from
+            // the staging tile was measured slower: 265 against 219 us per step on 8 GPUs, 223 against 217 on
+            // 4 -- the queued 64 KiB stores hold up the TMA loads of X.)
+            for (int q = 0; q < p.n_peers; ++q) *reinterpret_cast<uint4*>(p.peer_y[q] + off) = v;
           }
         }
       }
       if (tma_out && warp == 2 && lane == 0) tma_store_wait_read();   // the TMA unit has read the tile
       if (!(ok = epi_sync())) break;   // the tile is rewritten by the next tile's transposition
     }
-    if ((p.n_peers > 0 || p.n_owners > 0) && warp == 2 && lane == 0) tma_store_wait_all();   // stores done before the kernel ends
+    if (p.n_owners > 0 && warp == 2 && lane == 0) tma_store_wait_all();   // stores done before the kernel ends
   } else {
     // ------------------------------- dequant warps ------------------------------------------
     constexpr int ENTRY_LOG2 = (V == 4) ? 3 : 4;       // bytes per codebook entry
@@ -698,10 +698,8 @@ int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s
   if (!make_map(&mx, p.x, p.M, p.K)) return VQG_ERR_LAUNCH;
   PeerMaps pm{};
   if (p.n_peers < 0 || p.n_peers > 7) return VQG_ERR_BAD_ARG;
-  for (int q = 0; q < p.n_peers; ++q) {
+  for (int q = 0; q < p.n_peers; ++q)
     if (reinterpret_cast<uintptr_t>(p.peer_y[q]) % 16) return VQG_ERR_BAD_ARG;
-    if (!make_y_map(&pm.m[q], p.peer_y[q], p.M, p.N, p.ld_y)) return VQG_ERR_LAUNCH;
-  }
   if (p.n_owners > 0) {
     if (p.n_peers != 0 || gated || p.n_owners > 8 || p.owner_cols % 128 != 0 ||
         static_cast<long long>(p.n_owners) * p.owner_cols != p.N)

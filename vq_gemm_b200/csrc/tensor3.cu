@@ -23,13 +23,20 @@
 //   warp 1      pair leader (rank 0): issues tcgen05.mma.cta_group::2 [d], [a_tmem], b_desc and commits
 //               stage-free / accumulator-ready mbarriers in both CTAs; in the other CTA the same warp
 //               forwards "my X half and my A stage are in place" with a remote mbarrier arrive
-//   warps 2..5  epilogue: tcgen05.ld of D^T (lane = weight row), fp16, transpose through a per-warp
-//               shared-memory tile, 16-byte row-major stores of Y (and peer copies).  Tensor memory is
-//               handed back to the MMA warp as soon as it has been read, before the write-out.
+//   warps 2..5  epilogue: tcgen05.ld of D^T (lane = weight row; the load of the next 32 columns overlaps the
+//               conversion of the previous 32), fp16, transposed through one shared [256][128] staging tile,
+//               256-byte row segments of Y written with 16-byte stores (and the same to peers in gather
+//               mode).  Tensor memory is handed back to the MMA warp as soon as it has been read, before the
+//               write-out.  Variants: GATED (SiLU(gate) * up over neighbouring lanes, [256][64] tile) and
+//               row-parallel mode (the tile goes to the owner of its columns with one TMA tensor store).
 //   warps 6..9  dequant: thread (quarter, lane) owns weight row 32*quarter + lane
 //
-// TMEM columns: [0, 256) accumulator, [256 + 32*s, +32) A stage s.  No TMA load uses cluster multicast.
-// Every mbarrier wait is bounded (see tensor2.cu).
+// Schedule: the K loops of all tiles are cut into units and dealt out evenly over the CTA pairs; a pair's
+// two partial pieces are computed first, go to the workspace as fp32 and are summed in pair order by the
+// contributor that arrives last (see take_segment and the epilogue).  Without a workspace: whole tiles.
+//
+// TMEM columns: [0, 256) accumulator, [256 + 64*s, +64) A stage s (two 64-wide K sub-steps).  No TMA load uses
+// cluster multicast.  Every mbarrier wait is bounded (see tensor2.cu).
 #include "tc_ptx.cuh"
 
 namespace vqg {

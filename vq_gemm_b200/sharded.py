@@ -128,12 +128,12 @@ class ShardedVQGemm:
             key = (K, v, C, ib, rows_per_codebook)
             plan = self._plans.get(key)
             if plan is None:
-                ws_ptr, ws_n = self._workspace(
-                    lib.vqg_workspace_bytes(M, self.n_local, K, v, C, ib, rows_per_codebook, _lib.LAYOUT_BL, _lib.PATH_AUTO))
+                nbytes = lib.vqg_workspace_bytes(M, self.n_local, K, v, C, ib, rows_per_codebook, _lib.LAYOUT_BL, _lib.PATH_AUTO)
                 arrs = [(ctypes.c_void_p * self.world)(*[p + par * self.M * self.N * 2 for p in self._ptrs])
                         for par in range(2 if self._hdl is not None else 1)]
-                plan = self._plans[key] = (ws_ptr, ws_n, arrs)
-            ws_ptr, ws_n, arrs = plan
+                plan = self._plans[key] = (nbytes, arrs)
+            nbytes, arrs = plan
+            ws_ptr, ws_n = self._workspace(nbytes)   # looked up every call: the buffer may have been regrown
             arr = arrs[0]
             if self._hdl is not None:
                 par = self._step & 1

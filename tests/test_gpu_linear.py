@@ -97,3 +97,33 @@ def test_gated_module_and_operator():
     w = V.dequant(q.indices, q.codebook, rows_per_codebook=128).float()
     ref = torch.nn.functional.silu(xs.float() @ w[0::2].t()) * (xs.float() @ w[1::2].t())
     assert float((q(xs).float() - ref).abs().max()) <= 2e-2 * (float(ref.abs().max()) + 1)
+
+
+def test_graph_with_layers_whose_scratch_grows_during_capture(monkeypatch):
+    # the first layer is captured with a small scratch buffer, the second needs a much larger one: the small
+    # one must stay alive (its address is baked into the graph) and keep its counters zero across replays
+    from vq_gemm_b200 import ops
+    monkeypatch.setattr(ops, "_MIN_WORKSPACE", 1 << 20)
+    monkeypatch.setattr(ops, "_workspaces", {})      # torch hands out pooled streams: start without cached buffers
+    monkeypatch.setattr(ops, "_retired", [])
+    xa, ia, ca = O.make_bl_inputs(4, 8192, 512, 8, 256, 128, seed=31)        # split-K counters + partials
+    xb, ib, cb = O.make_bl_inputs(300, 1024, 1280, 8, 256, 128, seed=32)     # prefill kernel: 37 MiB of partial tiles
+    la, lb = VQLinear(ia, ca, 128).cuda(), VQLinear(ib, cb, 128).cuda()
+    sa, sb = xa.cuda(), xb.cuda()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            ya = la(sa)
+            yb = lb(sb)
+            ya2 = la(sa)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    assert V.device_status() == 0
+    assert_within_tolerance(ya.cpu(), O.vq_gemm_bl(xa, ia, ca, 128))
+    assert_within_tolerance(yb.cpu(), O.vq_gemm_bl(xb, ib, cb, 128))
+    assert torch.equal(bits(ya2), bits(ya))
+    assert len(ops._retired) >= 1

@@ -21,17 +21,24 @@ from . import _lib
 from .formats import infer_layout
 
 _workspaces: dict = {}
+_retired: list = []          # outgrown workspaces, kept alive (see _ws)
+_MIN_WORKSPACE = 64 << 20    # covers the prefill kernel's partial tiles (37 MiB) and typical split-K partials
 
 
 def _ws(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
-    """Cached, zero-initialised scratch per (device, stream); grown geometrically.  The library
-    keeps the counter region zero between calls."""
+    """Cached, zero-initialised scratch per (device, stream).  The library keeps the counter region zero
+    between calls.  A workspace that has to grow is replaced by a larger one but never freed: a CUDA graph
+    captured earlier may still hold its address, and memory handed back to the allocator could be given
+    to another tensor of the same graph."""
     if nbytes == 0:
         return None
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
     cur = _workspaces.get(key)
     if cur is None or cur.numel() < nbytes:
-        cur = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        if cur is not None:
+            _retired.append(cur)
+        size = max(nbytes, _MIN_WORKSPACE, 2 * cur.numel() if cur is not None else 0)
+        cur = torch.zeros(size, dtype=torch.uint8, device=device)
         _workspaces[key] = cur
     return cur
 

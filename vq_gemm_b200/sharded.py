@@ -103,12 +103,15 @@ class ShardedVQGemm:
             self._block = torch.empty((M, self.n_local), dtype=torch.float16, device=self.device)
             self._gathered = torch.empty((self.world, M, self.n_local), dtype=torch.float16, device=self.device)
         self._ws = None
+        self._retired = []
         self._plans = {}
 
     def _workspace(self, nbytes: int):
         if nbytes == 0:
             return None, 0
         if self._ws is None or self._ws.numel() < nbytes:
+            if self._ws is not None:
+                self._retired.append(self._ws)   # a captured graph may still hold its address
             self._ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         return self._ws.data_ptr(), self._ws.numel()
 
@@ -198,6 +201,7 @@ class RowParallelVQGemm:
         self.y = torch.empty((M, self.n_local), dtype=torch.float16, device=self.device)
         self._step = 0
         self._ws = None
+        self._retired = []
         slot_bytes = M * self.n_local * 2
         self._arrs = [(ctypes.c_void_p * G)(*[b + (par * G + self.rank) * slot_bytes for b in self._bases])
                       for par in range(2 if G > 1 else 1)]
@@ -215,6 +219,8 @@ class RowParallelVQGemm:
         stream = torch.cuda.current_stream(self.device).cuda_stream
         nbytes = lib.vqg_rowparallel_workspace_bytes(M, self.N, K_local, v, C, ib, rows_per_codebook)
         if nbytes and (self._ws is None or self._ws.numel() < nbytes):
+            if self._ws is not None:
+                self._retired.append(self._ws)   # a captured graph may still hold its address
             self._ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         par = (self._step & 1) if self.world > 1 else 0
         self._step += 1

@@ -7,7 +7,10 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <map>
 #include <mutex>
+#include <utility>
+#include <vector>
 #include <unordered_map>
 
 #include "../../include/vqg.h"
@@ -18,14 +21,20 @@ void check(int st, const char* what) {
   TORCH_CHECK(st == VQG_OK, what, ": ", vqg_status_string(st), " (status ", st, ")");
 }
 
-// per-device scratch, zero-initialised once (the library keeps its counter region zero)
+// Scratch per (device, stream), zero-initialised once (the library keeps its counter region zero).  Calls on
+// different streams may overlap on the GPU, so they must not share a buffer; a buffer that has to grow is
+// replaced but kept alive, because a CUDA graph captured earlier may still hold its address.
 at::Tensor workspace(const at::Device& dev, size_t bytes) {
   static std::mutex mu;
-  static std::unordered_map<int, at::Tensor> cache;
+  static std::map<std::pair<int, void*>, at::Tensor> cache;
+  static std::vector<at::Tensor> retired;
+  constexpr size_t kMin = size_t(64) << 20;
+  void* stream = static_cast<void*>(at::cuda::getCurrentCUDAStream(dev.index()).stream());
   std::lock_guard<std::mutex> lk(mu);
-  auto& t = cache[dev.index()];
+  auto& t = cache[{static_cast<int>(dev.index()), stream}];
   if (!t.defined() || static_cast<size_t>(t.numel()) < bytes) {
-    t = torch::zeros({static_cast<int64_t>(std::max<size_t>(bytes, size_t(1) << 20))},
+    if (t.defined()) retired.push_back(t);
+    t = torch::zeros({static_cast<int64_t>(std::max<size_t>(bytes, kMin))},
                      torch::TensorOptions().dtype(torch::kUInt8).device(dev));
   }
   return t;

@@ -126,7 +126,9 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
   constexpr int ENTRY_LOG2 = (V == 4) ? 3 : 4;
   constexpr int REP_LOG2 = REPL ? (7 - ENTRY_LOG2) : 0;  // replicas fill a 128-byte line, or none at all
   constexpr int ENTRY_SHIFT = ENTRY_LOG2 + REP_LOG2;
-  constexpr int PFB = (FORM == 1) ? 6 : (FORM == 2 ? 3 : 2);  // items per batch
+  // items per batch: every batch ends with two barriers, the cross-warp reduction and (K > 4096) the split-K
+  // hand-over, so large matrices want long batches; with 16-byte entries the index registers are few
+  constexpr int PFB = (FORM == 1) ? 6 : (FORM == 2 ? (V == 8 ? 6 : 3) : (V == 8 ? 4 : 2));
   constexpr int XR = (FORM == 1) ? 16 : (FORM == 2 ? 32 : 64);  // X fragment registers per thread
   constexpr int XSLOT = XR + 4;                      // staging words per thread (16-byte aligned, bank-spread)
   static_assert(NIDX * V == 64, "a thread-unit spans 64 K values");
@@ -547,7 +549,7 @@ bool fill_params(const Problem& p, DecodeParams& d, size_t& smem_bytes) {
   while (rl > 1 && ((p.N / 16) % rl != 0 || blocks_per_group % rl != 0)) --rl;
   d.rl = rl;
   d.nrbg = p.N / (16 * rl);
-  const int pfb = p.M <= 4 ? 6 : (p.M <= 8 ? 3 : 2);
+  const int pfb = p.M <= 4 ? 6 : (p.M <= 8 ? (p.v == 8 ? 6 : 3) : (p.v == 8 ? 4 : 2));   // = PFB of the kernel
   d.ipg = blocks_per_group / rl;
   // lanes per output in the reduction: as many as keep all outputs of a batch in one pass
   const int outs_max = pfb * rl * p.M * 16;

@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own oracle code on CPU.
 
-Run it in a container that has the reference tree (default /root/reference):
+Run it where the reference tree is checked out (its location is taken from VQG_REFERENCE_DIR):
 
     python tests/golden/make_golden.py
 

@@ -25,6 +25,10 @@ pytestmark = pytest.mark.gpu
     (7, 1024, 64, 8, 300, 32, torch.int16),         # small codebook behind uint16 indices
     (4, 2048, 128, 4, 256, 128, torch.uint8),       # largest batch of the two-columns-per-row form
     (12, 1024, 96, 8, 256, 32, torch.uint8),        # batch rows above 8 with v = 8
+    (3, 8192, 14336, 8, 256, 128, torch.uint8),     # many row blocks, 2 chunks: a CTA keeps its rows' sums across chunks
+    (16, 12288, 14336, 4, 256, 128, torch.uint8),   # the same with 3 chunks, 16 batch rows, v = 4
+    (8, 8192, 14336, 8, 4096, 0, torch.int16),      # the same with a single large codebook
+    (2, 8192 + 512, 14464, 4, 256, 128, torch.uint8),  # the same with a short last chunk and row blocks not a multiple of the SM count
 ])
 def test_decode_matches_oracle(M, K, N, v, C, rpc, dt):
     x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=M * 131 + N, idx_dtype=dt, cb_sigma=0.05)

@@ -64,6 +64,11 @@ struct DecodeParams {
   int inv_m, inv_rl;   // ceil(65536 / M), ceil(65536 / rl): t / M == (t * inv_m) >> 16 for t < 4096
   int n_peers;
   __half* peer_y[8];
+  // K > 4096 on matrices with many row blocks: a CTA owns a range of row blocks for ALL K chunks (items_q/r then
+  // partition the row blocks), walks the chunks one after the other and keeps the running sums of its rows in
+  // shared memory at byte offset acc_offset -- no partial sums in global memory, no counters, no hand-over.
+  int row_owned;
+  int acc_offset;
 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -153,12 +158,22 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
   // static contiguous partition of the items (chunk-major so X stays in registers); the host supplies
   // quotient and remainder so that no 64-bit division runs on the device
   const int bid = blockIdx.x;
-  const int it_begin = bid * p.items_q + min(bid, p.items_r);
-  const int it_end = it_begin + p.items_q + (bid < p.items_r ? 1 : 0);
+  int it_begin = bid * p.items_q + min(bid, p.items_r);
+  int it_end = it_begin + p.items_q + (bid < p.items_r ? 1 : 0);
   // the next kernel in the stream may be scheduled as soon as SMs free up (it waits as below before it
   // touches anything this kernel reads or writes)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (it_end <= it_begin) return;
+  // row blocks this CTA walks: all of them (items then run over chunks and row blocks, chunk-major), or its
+  // own range once per chunk
+  int r_begin = 0, r_end = p.nrbg;
+  if (p.row_owned) {
+    r_begin = it_begin;
+    r_end = it_end;
+    it_begin = 0;
+    it_end = (r_end - r_begin) * p.nchunks;
+  }
+  float* accbuf = reinterpret_cast<float*>(smem + p.acc_offset);   // [row block - r_begin][rl][M][16], row-owned mode
 
   // warp role inside a chunk: (slice, row lane)
   const int nsl_full = min(kWarps, p.nslices);
@@ -181,7 +196,7 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
     b.chunk = chunk; b.rbg = rbg; b.gpos = gpos; b.group = group;
     int c = it_end - it;
     c = min(c, PFB);
-    c = min(c, p.nrbg - rbg);
+    c = min(c, r_end - rbg);
     c = min(c, p.nslots * p.ipg - gpos);   // a batch touches at most `nslots` consecutive groups
     b.cnt = c > 0 ? c : 0;
     return b;
@@ -311,7 +326,8 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
   Batch nb;
   {
     int chunk0 = 0, rbg0 = it;
-    while (rbg0 >= p.nrbg) { rbg0 -= p.nrbg; ++chunk0; }
+    if (p.row_owned) rbg0 = r_begin;
+    else while (rbg0 >= p.nrbg) { rbg0 -= p.nrbg; ++chunk0; }
     const int group0 = rbg0 / p.ipg;
     nb = make_batch(it, chunk0, rbg0, rbg0 - group0 * p.ipg, group0);
   }
@@ -326,7 +342,7 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
     {
       int rbg = b.rbg + b.cnt, chunk = b.chunk, gpos = b.gpos + b.cnt, group = b.group;
       while (gpos >= p.ipg) { gpos -= p.ipg; ++group; }
-      if (rbg >= p.nrbg) { rbg = 0; gpos = 0; group = 0; ++chunk; }
+      if (rbg >= r_end) { rbg = r_begin; group = r_begin / p.ipg; gpos = r_begin - group * p.ipg; ++chunk; }
       nb = make_batch(it, chunk, rbg, gpos, group);
     }
 
@@ -458,7 +474,8 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
     const int outs = b.cnt * p.rl * p.M * 16;
     const int q = tid & (p.lpo - 1);
     const int outs_per_pass = kThreads >> p.lpo_log2;
-    const bool split = p.nchunks > 1;
+    const bool split = p.nchunks > 1 && !p.row_owned;
+    const bool carry = p.nchunks > 1 && p.row_owned;   // running sums over the chunks in shared memory
     for (int o0 = 0; o0 < outs; o0 += outs_per_pass) {
       const int o = o0 + (tid >> p.lpo_log2);
       float sum = 0.f;
@@ -476,7 +493,19 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
         for (int sl = q; sl < nsl; sl += p.lpo) sum += src[sl * warp_stride];
       }
       for (int d = p.lpo >> 1; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
-      if (valid && q == 0) {
+      if (valid && q == 0 && carry) {
+        // place of this output in the CTA's accumulator: the same for every chunk
+        float* a = accbuf + (static_cast<size_t>(row >> 4) - static_cast<size_t>(r_begin) * p.rl) * (p.M * 16) + m * 16 + (row & 15);
+        if (b.chunk > 0) sum += *a;
+        if (b.chunk + 1 < p.nchunks) {
+          *a = sum;
+        } else {
+          const __half h = __float2half_rn(sum);
+          const size_t o_off = static_cast<size_t>(m) * p.ld_y + row;
+          p.y[o_off] = h;
+          for (int pq = 0; pq < p.n_peers; ++pq) p.peer_y[pq][o_off] = h;
+        }
+      } else if (valid && q == 0) {
         if (!split) {
           const __half h = __float2half_rn(sum);
           const size_t o_off = static_cast<size_t>(m) * p.ld_y + row;
@@ -591,11 +620,37 @@ size_t decode_workspace_bytes(const Problem& p) {
   return kCounterBytes + static_cast<size_t>(d.nchunks) * p.M * p.N * sizeof(float);
 }
 
+namespace {
+int device_sms() {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms > 0 ? sms : 148;
+}
+// Row-owned walk of the K chunks (see DecodeParams::row_owned): worth it when there are several chunks and
+// enough row blocks that an even split of them over the SMs is balanced (at least six per CTA: measured 20 %
+// faster at 12 per CTA and K = 8192, but 12 % slower at 3.5 per CTA and K = 28672), and when the running sums of
+// a CTA's rows fit shared memory next to everything else.
+bool plan_row_owned(DecodeParams& d, size_t& smem, int M) {
+  if (d.nchunks <= 1) return false;
+  const int sms = device_sms();
+  if (d.nrbg < 6 * sms) return false;
+  const int per_cta = (d.nrbg + sms - 1) / sms;
+  const size_t acc_bytes = static_cast<size_t>(per_cta) * d.rl * M * 16 * sizeof(float);
+  const size_t off = (smem + 15) & ~static_cast<size_t>(15);
+  if (off + acc_bytes > 220 * 1024) return false;
+  d.row_owned = 1;
+  d.acc_offset = static_cast<int>(off);
+  smem = off + acc_bytes;
+  return true;
+}
+}  // namespace
+
 int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s) {
   DecodeParams d{};
   size_t smem;
   if (!fill_params(p, d, smem)) return VQG_ERR_UNSUPPORTED;
-  if (d.nchunks > 1) {
+  const bool row_owned = plan_row_owned(d, smem, p.M);
+  if (d.nchunks > 1 && !row_owned) {
     const size_t need = decode_workspace_bytes(p);
     if (ws == nullptr || ws_bytes < need) return VQG_ERR_WORKSPACE;
     if (static_cast<size_t>(d.nrbg) * sizeof(int) > kCounterBytes) return VQG_ERR_UNSUPPORTED;
@@ -604,10 +659,9 @@ int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s) {
   }
   d.status = device_status_ptr();
 
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const long long items = static_cast<long long>(d.nchunks) * d.nrbg;
+  const int sms = device_sms();
+  // what is dealt out over the CTAs: (chunk, row block) items, or row blocks in the row-owned mode
+  const long long items = row_owned ? d.nrbg : static_cast<long long>(d.nchunks) * d.nrbg;
   const int grid = static_cast<int>(items < sms ? items : sms);
   d.items_q = static_cast<int>(items / grid);
   d.items_r = static_cast<int>(items % grid);

@@ -409,8 +409,19 @@ def _reference_cuda_kernels(V):
     return out
 
 
+def _use_all_host_threads():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU legs are meant to use every core
+    this process may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+
+
 def _cpu_sample(shape, seconds_budget=20.0):
     """Torch CPU oracle on a column block of the workload (full M and K)."""
+    _use_all_host_threads()
     from oracle import vq_oracle as O
     from vq_gemm_b200.formats import make_inputs
     rpc = shape.rows_per_codebook
@@ -438,6 +449,7 @@ def run_reference(args, shape):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    _use_all_host_threads()
     from oracle import vq_oracle as O
     from vq_gemm_b200.formats import make_inputs
     rpc = shape.rows_per_codebook

@@ -518,7 +518,21 @@ def main():
     x_h, idx_h, cb_h = make_inputs(shape, seed=0, n_rows=n_local if rpc > 0 else None, row0=row0)
     x_h, idx_h, cb_h = x_h.pin_memory(), idx_h.pin_memory(), cb_h.pin_memory()
     x, idx, cb = x_h.to(dev), idx_h.to(dev), cb_h.to(dev)
-    op = ShardedVQGemm(shape.M, shape.N, mode=args.mode, device=dev)
+    # peer mode needs symmetric memory; if it cannot be set up on this box every rank falls back to NCCL together
+    mode = args.mode
+    try:
+        op = ShardedVQGemm(shape.M, shape.N, mode=mode, device=dev)
+        failed = 0
+    except Exception as e:  # noqa: BLE001
+        op, failed = None, 1
+        print(f"rank {rank}: {mode} mode unavailable ({e!r})", file=sys.stderr)
+    if world > 1:
+        t = torch.tensor([failed], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        failed = int(t.item())
+    if failed:
+        mode = "nccl"
+        op = ShardedVQGemm(shape.M, shape.N, mode=mode, device=dev)
 
     # clock warm-up: the SM clock idles at a few hundred MHz
     a = torch.randn(4096, 4096, device=dev, dtype=torch.float16)
@@ -546,7 +560,7 @@ def main():
         # streams (copy-in, compute, copy-out) over double-buffered device inputs and outputs, so step i+1's
         # input copy and step i-1's output copy overlap step i's kernel.  Every step still moves all of its
         # inputs (X, indices, codebooks) from pinned host memory and its output block back to pinned memory.
-        ops = [op, ShardedVQGemm(shape.M, shape.N, mode=args.mode, device=dev)]
+        ops = [op, ShardedVQGemm(shape.M, shape.N, mode=mode, device=dev)]
         y_h = [torch.empty((shape.M, n_local), dtype=torch.float16).pin_memory() for _ in range(2)]
         ins = [(torch.empty_like(x), torch.empty_like(idx), torch.empty_like(cb)) for _ in range(2)]
         s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
@@ -629,7 +643,7 @@ def main():
         "dtype": "f16", "data": "synthetic",
         "config": {"workload": shape.name, "M": shape.M, "K": shape.K, "N": shape.N, "v": shape.v, "C": shape.C,
                    "rows_per_codebook": rpc, "idx_bytes": shape.idx_bytes, "parallelism": f"N-sharded x{world}",
-                   "gather": args.mode if world > 1 else "none",
+                   "gather": mode if world > 1 else "none",
                    "l2": "working set (indices + X + Y = 180 MB) larger than the 126 MB L2"},
         "e2e": {"value": flops / ems / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ems, "steps": e2e_steps,

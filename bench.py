@@ -24,6 +24,16 @@ each rank owns N/G output columns and the fp16 output is assembled on every rank
 ``quantizer``  (N=1 only) the step before the product on a C4-sized layer: nearest-entry search
                against the fp32 pipe, one exact k-means update, 12-bit pack/unpack against HBM.
 ``cpu_baseline`` the torch CPU oracle (gather + fp32-accumulated matmul) on a bounded sample.
+``sustained``  (N=1 only) the headline kernel launched back to back for at least two seconds with the clocks
+               sampled: TFLOP/s against the sustained dense 16-bit peak, median SM clock, time x clock.
+``cublas``     (N=1 only) cuBLAS fp16 (torch.matmul) on pre-dequantised weights for the two prefill shapes,
+               fp32 and fp16 accumulation, in alternating blocks with this library's kernel.
+``reference_cuda_kernels`` (N=1 only, when oracle/_ref holds them) the reference's own CUDA kernels rebuilt
+               for sm_100a, on data in the reference's format, and this library on the same data.
+The line ends with the compact per-configuration table (``shapes``); long per-kernel detail is under ``detail``.
+
+``--profile-case NAME --launches n [--path p]`` runs n launches of one configuration and exits: the command to
+put under a profiler.
 
 ``--impl reference`` times the reference's torch path restated for CPU (oracle/vq_oracle.py) on
 the host cores, same metric and workload, bounded sample per step.
@@ -52,6 +62,20 @@ def _peaks():
         return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"], "tflops_sustained": d.get("bf16_tflops_sustained"),
                 "source": "measured"}
     return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def _traffic(kernel: str, workload: str):
+    """DRAM bytes per launch of a kernel on a workload from the tracked record of ncu captures
+    (dram__bytes_read.sum + dram__bytes_write.sum of one launch); None if there is no entry."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.txt")
+    try:
+        for ln in open(path):
+            f = ln.split()
+            if len(f) >= 4 and not ln.startswith("#") and f[0] == kernel and f[1] == workload:
+                return {"bytes": float(f[2]), "source": f"profiles/dram_traffic.txt (ncu capture at commit {f[3]})"}
+    except OSError:
+        pass
+    return None
 
 
 class ClockSampler:
@@ -133,8 +157,16 @@ def _time_loop(fn, steps, warmup, barrier=None, counter=None):
     return (ms, counter() - c0) if counter else ms
 
 
+def _lookup_floor_us(shape, sm_mhz=1965.0, sms=148):
+    """Time the shared-memory lookups alone would take: one 2v-byte codebook read per index at 128 bytes per
+    clock and SM, conflict-free (the secondary roofline of the M <= 16 configurations)."""
+    lookups = shape.N * (shape.K // shape.v)
+    return lookups * 2.0 * shape.v / 128.0 / sms / sm_mhz
+
+
 def _single_shape(V, shape, peaks, steps, warmup):
-    """One single-GPU configuration: kernel time over a ring of index buffers larger than L2."""
+    """One single-GPU configuration: kernel time over a ring of index buffers larger than L2.  Returns the
+    compact entry for the table at the end of the line and the per-path detail."""
     from vq_gemm_b200.formats import make_inputs
     x, idx, cb = make_inputs(shape, seed=0, device="cuda")
     ring = 1
@@ -175,13 +207,14 @@ def _single_shape(V, shape, peaks, steps, warmup):
 
     ms = graph_ms("auto")
     e0, e1 = _events()
-    res = {"workload": shape.name, "M": shape.M, "K": shape.K, "N": shape.N, "v": shape.v, "C": shape.C,
-           "us_per_launch": ms * 1e3, "tflops": shape.flops / ms / 1e9, "gbs_compressed": shape.bytes_algorithmic / ms / 1e6,
-           "ring_buffers": ring, "timing": "cuda-graph replay, CUDA events"}
+    compact = {"workload": shape.name, "M": shape.M, "K": shape.K, "N": shape.N, "us": round(ms * 1e3, 3)}
+    detail = {"workload": shape.name, "v": shape.v, "C": shape.C, "ring_buffers": ring,
+              "timing": "cuda-graph replay, CUDA events", "path": _path_name(V, shape)}
     if shape.bound == "hbm":
         a = shape.bytes_algorithmic / ms / 1e6
-        res["roofline"] = {"bound": "hbm", "achieved": a, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                           "frac": a / peaks["hbm_gbs"], "frac_of_nominal_8000": a / 8000.0}
+        compact.update({"gbs": round(a, 1), "bound": "hbm", "frac": round(a / peaks["hbm_gbs"], 4),
+                        "frac_of_8000": round(a / 8000.0, 4), "bytes": shape.bytes_algorithmic,
+                        "lookup_floor_us": round(_lookup_floor_us(shape), 2)})
         # both small-batch kernels, whichever the library picks by itself for this shape
         for alt in ("decode", "small_ts"):
             try:
@@ -189,11 +222,11 @@ def _single_shape(V, shape, peaks, steps, warmup):
             except RuntimeError:
                 continue
             ams = graph_ms(alt)
-            res["path_" + alt] = {"us": ams * 1e3, "gbs_compressed": shape.bytes_algorithmic / ams / 1e6}
+            detail["path_" + alt] = {"us": ams * 1e3, "gbs_compressed": shape.bytes_algorithmic / ams / 1e6}
     else:
         a = shape.flops / ms / 1e9
-        res["roofline"] = {"bound": "tensor", "achieved": a, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                           "frac": a / peaks["tflops"], "frac_of_nominal_2250": a / 2250.0}
+        compact.update({"tflops": round(a, 1), "bound": "tensor", "frac": round(a / peaks["tflops"], 4),
+                        "frac_of_2250": round(a / 2250.0, 4)})
         # the other routes through the library: single-CTA fused kernel, and dequantise-then-dense
         for alt in ("tensor", "tensor_pair", "two_phase"):
             for _ in range(3):
@@ -206,38 +239,99 @@ def _single_shape(V, shape, peaks, steps, warmup):
             e1.record()
             torch.cuda.synchronize()
             ams = e0.elapsed_time(e1) / n
-            res["path_" + alt] = {"tflops": shape.flops / ams / 1e9, "us": ams * 1e3}
-        # cuBLAS fp16 on pre-dequantised weights (the reference's ref_gemm comparator).  The two are timed in
-        # alternating blocks of equal length so that both see the same clocks under the power cap.
-        w = V.dequant(idx, cb, rows_per_codebook=shape.rows_per_codebook)
-        wt = w.t()
+            detail["path_" + alt] = {"tflops": shape.flops / ams / 1e9, "us": ams * 1e3}
+    return compact, detail
 
-        def ours():
-            V.vq_gemm(x, idx, cb, rows_per_codebook=shape.rows_per_codebook, layout="bl", out=out)
 
-        def cublas():
-            torch.matmul(x, wt)
+def _path_name(V, shape):
+    from vq_gemm_b200 import _lib
+    code = _lib.load().vqg_auto_path(shape.M, shape.N, shape.K, shape.v, shape.C, shape.idx_bytes, shape.rows_per_codebook, 0)
+    return {v: k for k, v in _lib.PATHS.items()}.get(code, str(code))
 
-        def block(fn, n=20):
-            e0.record()
-            for _ in range(n):
-                fn()
-            e1.record()
-            torch.cuda.synchronize()
-            return e0.elapsed_time(e1) / n
 
-        for fn in (ours, cublas):
-            block(fn, 5)
-        t_ours, t_cublas = [], []
-        for _ in range(5):
-            t_ours.append(block(ours))
-            t_cublas.append(block(cublas))
-        oms, cms = statistics.median(t_ours), statistics.median(t_cublas)
-        res["alternating_blocks"] = {"blocks": 5, "launches_per_block": 20, "us": oms * 1e3, "tflops": shape.flops / oms / 1e9}
-        res["cublas_fp16_dequantised"] = {"tflops": shape.flops / cms / 1e9, "us": cms * 1e3,
-                                          "speedup_vs_cublas": cms / oms, "timing": "alternating blocks with ours"}
-        del w, wt
+def _cublas_compare(V, shape, x=None, idx=None, cb=None):
+    """cuBLAS fp16 on pre-dequantised weights (the reference's ref_gemm comparator, ref_gemm/cublas_gemm_fp16.cu:36-46)
+    against this library's fused kernel, in alternating blocks of equal length so that all see the same clocks
+    under the power cap.  Two cuBLAS accumulate modes: fp32 (like ours) and fp16 (CUBLAS_COMPUTE_16F, what the
+    reference's wrapper asks for).  Dequantisation time is not charged to cuBLAS."""
+    from vq_gemm_b200.formats import make_inputs
+    if x is None:
+        x, idx, cb = make_inputs(shape, seed=0, device="cuda")
+    rpc = shape.rows_per_codebook
+    out = torch.empty((shape.M, shape.N), dtype=torch.float16, device=x.device)
+    w = V.dequant(idx, cb, rows_per_codebook=rpc)
+    wt = w.t()
+    ref = torch.empty((shape.M, shape.N), dtype=torch.float16, device=x.device)
+    e0, e1 = _events()
+    has16 = hasattr(torch.backends.cuda.matmul, "allow_fp16_accumulation")
+
+    def ours():
+        V.vq_gemm(x, idx, cb, rows_per_codebook=rpc, layout="bl", out=out)
+
+    def cublas32():
+        torch.matmul(x, wt, out=ref)
+
+    def cublas16():
+        torch.backends.cuda.matmul.allow_fp16_accumulation = True
+        try:
+            torch.matmul(x, wt, out=ref)
+        finally:
+            torch.backends.cuda.matmul.allow_fp16_accumulation = False
+
+    def block(fn, n=20):
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    fns = [("ours", ours), ("cublas_acc32", cublas32)] + ([("cublas_acc16", cublas16)] if has16 else [])
+    for _, fn in fns:
+        block(fn, 5)
+    t = {k: [] for k, _ in fns}
+    for _ in range(5):
+        for k, fn in fns:
+            t[k].append(block(fn))
+    med = {k: statistics.median(v) for k, v in t.items()}
+    res = {"workload": shape.name, "blocks": 5, "launches_per_block": 20, "timing": "alternating blocks",
+           "ours_us": round(med["ours"] * 1e3, 1), "ours_tflops": round(shape.flops / med["ours"] / 1e9, 1)}
+    for k in ("cublas_acc32", "cublas_acc16"):
+        if k in med:
+            res[k] = {"us": round(med[k] * 1e3, 1), "tflops": round(shape.flops / med[k] / 1e9, 1),
+                      "speedup_ours": round(med[k] / med["ours"], 3)}
+    del w, wt, ref
     return res
+
+
+def _sustained(V, shape, x, idx, cb, peaks, device_index, seconds=2.5):
+    """The headline kernel launched back to back for `seconds` with the clocks sampled: the rate the chip
+    sustains under its power cap, to set against the sustained dense 16-bit peak."""
+    rpc = shape.rows_per_codebook
+    out = torch.empty((shape.M, idx.shape[0]), dtype=torch.float16, device=x.device)
+    e0, e1 = _events()
+    for _ in range(5):
+        V.vq_gemm(x, idx, cb, rows_per_codebook=rpc, layout="bl", out=out)
+    torch.cuda.synchronize()
+    n = 0
+    with ClockSampler(device_index) as cs:
+        t0 = time.perf_counter()
+        e0.record()
+        while time.perf_counter() - t0 < seconds:
+            for _ in range(50):
+                V.vq_gemm(x, idx, cb, rows_per_codebook=rpc, layout="bl", out=out)
+            n += 50
+            torch.cuda.synchronize()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    c = cs.summary()
+    tf = shape.flops / ms / 1e9
+    return {"workload": shape.name, "launches": n, "seconds": round(ms * n / 1e3, 2), "us": round(ms * 1e3, 1),
+            "tflops": round(tf, 1), "sm_mhz_median": c["sm_mhz"], "reasons": c["reasons"],
+            "us_x_mhz": round(ms * 1e3 * c["sm_mhz"], 0) if c["sm_mhz"] else None,
+            "frac_of_sustained_peak": round(tf / peaks["tflops_sustained"], 4) if peaks["tflops_sustained"] else None,
+            "frac_of_burst_peak": round(tf / peaks["tflops"], 4)}
 
 
 def _quantizer(peaks, clocks_mhz):
@@ -351,7 +445,7 @@ def _mlp(V, world, rank, dev, steps, warmup, barrier, reduce_max):
 
 
 def _reference_cuda_kernels(V):
-    """Optional baseline leg (--baselines): the reference's own CUDA kernels, rebuilt unmodified for
+    """Baseline leg (N=1, whenever oracle/_ref holds them): the reference's own CUDA kernels, rebuilt unmodified for
     sm_100a by oracle/build_ref.py, on data in the reference's format; and this library on the same data.
     The reference launchers print to stdout and (PROFILING 1) run 50 + 100 launches per call, so stdout is
     parked on /dev/null around them and the event time of one call is divided by 150."""
@@ -375,7 +469,7 @@ def _reference_cuda_kernels(V):
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / 20
-        row = {"shape": tag, "M": M, "K": K, "Nq": Nq, "ours": {"us": ms * 1e3, "tflops": flops / ms / 1e9}}
+        row = {"shape": tag, "M": M, "K": K, "Nq": Nq, "ours": {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1)}}
         for variant, per_call in launches.items():
             path = os.path.join(ref_dir, f"vq_gemm_cuda_{variant}.so")
             if not os.path.exists(path):
@@ -403,8 +497,8 @@ def _reference_cuda_kernels(V):
                 os.close(devnull)
             rms = e0.elapsed_time(e1) / (calls * per_call)
             diff = float((theirs.float() - ours.float()).abs().max() / ours.float().abs().max())
-            row[variant] = {"us": rms * 1e3, "tflops": flops / rms / 1e9, "speedup_ours": rms / ms,
-                            "max_rel_diff_vs_ours": diff, "launches_per_call": per_call}
+            row[variant] = {"us": round(rms * 1e3, 1), "tflops": round(flops / rms / 1e9, 1),
+                            "speedup_ours": round(rms / ms, 2), "rel_diff": round(diff, 4)}
         out.append(row)
     return out
 
@@ -486,12 +580,28 @@ def main():
     ap.add_argument("--mode", default="peer", choices=["peer", "nccl"], help="how the N-sharded output is assembled")
     ap.add_argument("--no-shapes", action="store_true", help="skip the per-configuration table")
     ap.add_argument("--no-mlp", action="store_true", help="skip the tensor-parallel MLP measurement")
-    ap.add_argument("--baselines", action="store_true",
-                    help="also time the reference's own CUDA kernels from oracle/_ref (N=1 only)")
+    ap.add_argument("--no-baselines", action="store_true",
+                    help="skip cuBLAS, the reference's own CUDA kernels (oracle/_ref) and the sustained leg")
+    ap.add_argument("--profile-case", default=None, metavar="NAME",
+                    help="run --launches launches of one configuration on cuda:0 and exit (for use under a profiler)")
+    ap.add_argument("--launches", type=int, default=8)
+    ap.add_argument("--path", default="auto")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
     from vq_gemm_b200.formats import CONFIGS, make_inputs
+    if args.profile_case:
+        import vq_gemm_b200 as V
+        sc = CONFIGS[args.profile_case]
+        x, idx, cb = make_inputs(sc, seed=0, device="cuda")
+        y = None
+        for _ in range(args.launches):
+            y = V.vq_gemm(x, idx, cb, rows_per_codebook=sc.rows_per_codebook, layout="bl", path=args.path)
+        torch.cuda.synchronize()
+        if V.device_status() != 0:
+            raise SystemExit("device status word set")
+        print("ok", args.profile_case, args.path, float(y.float().abs().mean()))
+        return
     shape = CONFIGS[args.workload]
     if args.impl == "reference":
         run_reference(args, shape)
@@ -540,6 +650,21 @@ def main():
     while time.time() - t0 < 0.5:
         a @ a
     torch.cuda.synchronize()
+
+    # The microsecond configurations are latency-bound: their time scales with the SM clock, which sits near its
+    # maximum in a decode loop but stays low for a while after a power-capped GEMM phase.  They are therefore
+    # measured first, before the long tensor-bound loops.
+    solo = world == 1 and rank == 0
+    shapes, detail = [], {}
+    if solo and not args.no_shapes:
+        detail["shapes"] = []
+        for name in ("c1_cpu_ref", "c2_decode", "c3_small_batch"):
+            try:
+                compact, det = _single_shape(V, CONFIGS[name], peaks, max(args.steps, 200), args.warmup)
+                shapes.append(compact)
+                detail["shapes"].append(det)
+            except Exception as e:  # keep the headline line even if a side measurement fails
+                shapes.append({"workload": name, "error": repr(e)})
 
     def step():
         op(x, idx, cb, rpc)
@@ -595,7 +720,7 @@ def main():
             for b in range(2):
                 cur.wait_event(out_free[b])
 
-        e2e_steps = max(6, args.steps // 4)
+        e2e_steps = args.steps
         e2e_run(4)
         if barrier:
             barrier()
@@ -622,11 +747,11 @@ def main():
     d2h = y_h[0].numel() * 2
     flops = shape.flops
     kflops = 2.0 * shape.M * n_local * shape.K
+    tr = _traffic("vq_tensor_ts_kernel" if shape.bound == "tensor" else "vq_decode_kernel", shape.name) if world == 1 else None
     if shape.bound == "tensor":
         ach = kflops / kms / 1e9
         roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"],
-                # ncu dram__bytes_read+write per launch of this kernel on this workload (profiles/), N=1 only
-                "traffic": 295.6e6 if (world == 1 and shape.name == "c5_mlp70b") else None,
+                "traffic": tr["bytes"] if tr else None, "traffic_source": tr["source"] if tr else None,
                 "traffic_algorithmic": shape.bytes_algorithmic if world == 1 else None,
                 "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
                 "frac_of_sustained": ach / peaks["tflops_sustained"] if peaks["tflops_sustained"] else None,
@@ -635,7 +760,8 @@ def main():
         b = shape.bytes_algorithmic / world
         ach = b / kms / 1e6
         roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
-                "traffic": None, "peak_source": peaks["source"], "kernel": "vq_decode_kernel", "kernel_us": kms * 1e3}
+                "traffic": tr["bytes"] if tr else None, "traffic_source": tr["source"] if tr else None,
+                "peak_source": peaks["source"], "kernel": "vq_decode_kernel", "kernel_us": kms * 1e3}
 
     line = {
         "metric": "vq_gemm_tflops", "value": flops / ms / 1e9, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -660,33 +786,53 @@ def main():
         except Exception as e:
             mlp = {"error": repr(e)}
         line["mlp70b"] = mlp
-    if world == 1 and rank == 0 and not args.no_shapes:
-        shapes = []
-        for name in ("c1_cpu_ref", "c2_decode", "c3_small_batch", "c4_prefill"):
+    if solo and not args.no_shapes:
+        for name in ("c4_prefill",):
             try:
-                shapes.append(_single_shape(V, CONFIGS[name], peaks, max(args.steps, 200), args.warmup))
+                compact, det = _single_shape(V, CONFIGS[name], peaks, max(args.steps, 200), args.warmup)
+                shapes.append(compact)
+                detail["shapes"].append(det)
             except Exception as e:  # keep the headline line even if a side measurement fails
                 shapes.append({"workload": name, "error": repr(e)})
-        line["shapes"] = shapes
         try:
-            line["gated_mlp_up"] = _gated(V, peaks)
+            detail["gated_mlp_up"] = _gated(V, peaks)
         except Exception as e:
-            line["gated_mlp_up"] = {"error": repr(e)}
+            detail["gated_mlp_up"] = {"error": repr(e)}
         try:
-            line["quantizer"] = _quantizer(peaks, line["clocks"].get("sm_max_mhz") or 1965.0)
+            detail["quantizer"] = _quantizer(peaks, line["clocks"].get("sm_max_mhz") or 1965.0)
         except Exception as e:
-            line["quantizer"] = {"error": repr(e)}
-    if world == 1 and rank == 0 and args.baselines:
+            detail["quantizer"] = {"error": repr(e)}
+    if detail:
+        line["detail"] = detail
+    if rank == 0 and world == 1:
         try:
-            line["reference_cuda_kernels"] = _reference_cuda_kernels(V)
+            line["cpu_baseline"] = _cpu_sample(shape)
         except Exception as e:
-            line["reference_cuda_kernels"] = {"error": repr(e)}
-    if rank == 0:
-        if world == 1:
+            line["cpu_baseline"] = {"error": repr(e)}
+    # the compact records the line ends with
+    if solo and not args.no_baselines:
+        if os.path.exists(os.path.join(ROOT, "oracle", "_ref", "vq_gemm_cuda_s1.so")):
             try:
-                line["cpu_baseline"] = _cpu_sample(shape)
+                line["reference_cuda_kernels"] = _reference_cuda_kernels(V)
             except Exception as e:
-                line["cpu_baseline"] = {"error": repr(e)}
+                line["reference_cuda_kernels"] = {"error": repr(e)}
+        else:
+            line["reference_cuda_kernels"] = {"unavailable": "oracle/_ref not built (python oracle/build_ref.py)"}
+        try:
+            line["sustained"] = _sustained(V, shape, x, idx, cb, peaks, local)
+        except Exception as e:
+            line["sustained"] = {"error": repr(e)}
+        cub = []
+        for name in ("c4_prefill", "c5_mlp70b"):
+            try:
+                same = name == shape.name
+                cub.append(_cublas_compare(V, CONFIGS[name], *((x, idx, cb) if same else ())))
+            except Exception as e:
+                cub.append({"workload": name, "error": repr(e)})
+        line["cublas"] = cub
+    if shapes:
+        line["shapes"] = shapes
+    if rank == 0:
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

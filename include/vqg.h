@@ -43,7 +43,8 @@ enum {
   VQG_ERR_LAUNCH = 4,         /* the CUDA runtime or driver refused a call                      */
   VQG_ERR_DEVICE_TIMEOUT = 5, /* a bounded device-side wait ran out (see vqg_device_status)     */
   VQG_ERR_NO_DEVICE = 6,      /* no usable sm_100 device / driver                                */
-  VQG_ERR_TOO_LARGE = 7       /* problem needs more scratch than the built-in static buffer has */
+  VQG_ERR_TOO_LARGE = 7,      /* problem needs more scratch than the built-in static buffer has */
+  VQG_ERR_NO_MEMORY = 8       /* the device had no memory left to load this library's code and data */
 };
 
 enum { VQG_LAYOUT_BL = 0, VQG_LAYOUT_REF = 1 };
@@ -52,7 +53,7 @@ enum { VQG_LAYOUT_BL = 0, VQG_LAYOUT_REF = 1 };
 enum {
   VQG_PATH_AUTO = 0,
   VQG_PATH_GENERIC = 1,  /* shape-agnostic CUDA-core kernel                                     */
-  VQG_PATH_DECODE = 2,   /* M <= 16: index streaming + codebook lookups + mma.sync, split-K     */
+  VQG_PATH_DECODE = 2,   /* M <= 16: TMA index tiles + codebook lookups + mma.sync, split-K      */
   VQG_PATH_TENSOR = 3,   /* tcgen05 / TMEM / TMA warp-specialised kernel, fused dequant, 1 CTA  */
   VQG_PATH_TWO_PHASE = 4,/* dequantise to workspace, then the dense tcgen05 kernel              */
   VQG_PATH_TENSOR_PAIR = 5, /* the fused kernel on CTA pairs (tcgen05 cta_group::2, 256x256 tiles) */
@@ -80,8 +81,9 @@ VQG_API size_t vqg_workspace_bytes(int M, int N, int K, int v, int C, int idx_by
 VQG_API size_t vqg_workspace_counter_bytes(void);
 
 /* The kernel (VQG_PATH_*) that VQG_PATH_AUTO resolves to for a problem with 1024-byte aligned operands
- * and ld_y = N.  Routing is by measurement on B200: decode kernel up to 4 batch rows and for small
- * matrices up to 16, small-batch tensor-memory kernel up to 96, CTA-pair kernel above. */
+ * and ld_y = N.  Routing is by measurement on B200: decode kernel up to 8 batch rows, and up to 16 when
+ * K <= 4096 and the codebook has at most 256 entries; small-batch tensor-memory kernel up to 96;
+ * CTA-pair kernel above. */
 VQG_API int vqg_auto_path(int M, int N, int K, int v, int C, int idx_bytes, int rows_per_codebook, int layout);
 
 /* Y = X * dequant(idx, codebook)^T.  Replaces `torch::Tensor e2e_gemm(input, w, codebook)`
@@ -145,12 +147,19 @@ VQG_API int vqg_gemm_sharded(const void* x, const void* idx, const void* codeboo
  * The call itself makes no cudaMalloc / cudaFree and calls no allocating library routine.
  *
  * Limits and rules:
- *   - same shapes as the decode path of vqg_gemm (BL layout, M <= 16, K % 256 == 0, N % 16 == 0);
- *     anything else returns VQG_ERR_UNSUPPORTED -- there is no other kernel behind this entry;
- *   - the scratch a problem needs is 64 KiB + ceil(K/4096) * M * N * 4 bytes when K > 4096 and
- *     nothing otherwise; beyond VQG_NOALLOC_SCRATCH_BYTES the call returns VQG_ERR_TOO_LARGE;
+ *   - same shapes as the decode path of vqg_gemm (BL layout, M <= 16, K > 0, K % 256 == 0,
+ *     N % 8 == 0, whole 16-row tiles per codebook); anything else returns VQG_ERR_UNSUPPORTED --
+ *     there is no other kernel behind this entry (K == 0 writes zeros, as vqg_gemm does);
+ *   - the scratch a problem needs is what vqg_workspace_bytes(..., VQG_PATH_DECODE) reports: nothing
+ *     up to K = 4096 and for large matrices, whose CTAs keep their rows' running sums on chip;
+ *     64 KiB + ceil(K/4096) * M * N * 4 bytes for K > 4096 on matrices with few rows.  Beyond
+ *     VQG_NOALLOC_SCRATCH_BYTES the call returns VQG_ERR_TOO_LARGE;
  *   - the first call on each device looks up the device address of the array (the device must be
- *     current); make that first call before any stream capture on that device;
+ *     current).  With CUDA's lazy module loading that lookup is also the moment the runtime puts
+ *     this library's code and the array itself onto the device, so it needs those few MiB to be
+ *     free: make the first call on every device BEFORE the host hands the rest of the memory to
+ *     its pool, and before any stream capture on that device.  If the memory is already gone the
+ *     call returns VQG_ERR_NO_MEMORY.  Later calls leave the amount of free memory unchanged;
  *   - all calls on a device share the one array and it keeps the previous call's contents (the
  *     call re-zeroes the counters it needs on `stream`): two calls that overlap on the GPU -- on
  *     different streams, or from different threads -- race.  Serialise them. */

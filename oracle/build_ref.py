@@ -10,13 +10,20 @@ It does not run the reference's build script (compile_kernels.py uses setuptools
 compile_kernels.py:6-17 re-targeted to ``-gencode arch=compute_100a,code=sm_100a``
 (strategy_3 needs the explicit gencode form because of ``setmaxnreg``).
 
+It also places an unmodified copy of the reference's harness (its ``bench.py``) in
+``oracle/_ref/`` so that a GPU test can run that file itself against this build's modules on
+a machine where the reference tree is not checked out (the copy is an output like the
+``.so`` files: git-ignored, never committed).
+
 Usage:  python oracle/build_ref.py [--ref /path/to/reference] [--only s1,s2_128] [-j 6]
-Outputs ``oracle/_ref/vq_gemm_cuda_<variant>.so`` (git-ignored, shipped to the GPU box).
+        (the reference's location defaults to the environment variable VQG_REFERENCE_DIR)
+Outputs ``oracle/_ref/vq_gemm_cuda_<variant>.so`` and ``oracle/_ref/bench.py``.
 """
 from __future__ import annotations
 
 import argparse
 import os
+import shutil
 import subprocess
 import sys
 import sysconfig
@@ -75,15 +82,18 @@ def build_one(ref: str, variant: str, force: bool) -> tuple[str, int, str]:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("VQG_REFERENCE_DIR", "/root/reference"))
+    ap.add_argument("--ref", default=os.environ.get("VQG_REFERENCE_DIR", ""))
     ap.add_argument("--only", default="")
     ap.add_argument("-j", type=int, default=6)
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args(argv)
-    if not os.path.isdir(a.ref):
-        print(f"reference tree {a.ref} not present; nothing built")
+    if not a.ref or not os.path.isdir(a.ref):
+        print(f"reference tree {a.ref!r} not present (set VQG_REFERENCE_DIR or pass --ref); nothing built")
         return 0
     os.makedirs(OUT, exist_ok=True)
+    harness = os.path.join(a.ref, "bench.py")
+    if os.path.exists(harness):
+        shutil.copyfile(harness, os.path.join(OUT, "bench.py"))
     variants = [v for v in (a.only.split(",") if a.only else VARIANTS) if v]
     rc = 0
     with ThreadPoolExecutor(max_workers=a.j) as ex:

@@ -15,7 +15,9 @@ on a CPU-only machine:
   bit-exactly) and returns the fp32-accumulated product rounded to fp16.
 
 The fixtures hold inputs, the reference's gathered weights and that product, for small
-REF-layout cases.  BL-layout cases (no reference implementation exists) are written by
+REF-layout cases.  One of them (``ref_nq4_bridge``, Nq = 4) is at the same time a BL-layout case:
+with a single codebook the reference's gather equals the generalised rule with v = 2, so the
+BL gather is checked against bytes the reference's code produced.  BL-layout cases (no reference implementation exists) are written by
 the scalar-loop rule in oracle/vq_oracle.py so that later changes to the vectorised
 oracle or to the kernels are caught.
 """
@@ -29,10 +31,12 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("VQG_REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("VQG_REFERENCE_DIR")
 
 
 def import_reference_bench():
+    if not REF or not os.path.isdir(REF):
+        raise SystemExit("set VQG_REFERENCE_DIR to the reference checkout")
     captured = {}
 
     def gemm(inp, w):
@@ -66,6 +70,10 @@ def main():
         "ref_small": (128, 64, 64, 42),
         "ref_two_tiles": (256, 96, 128, 7),
         "ref_ragged": (5, 32, 8, 3),
+        # Nq = 4: the reference's gather uses ONE codebook for all four index columns, so its w_decoded [K, 8]
+        # is also what the generalised (BL) rule gives for idx = w read as [N = K rows, 4 indices], v = 2,
+        # single codebook -- the one case in which the reference's own code pins the BL gather
+        "ref_nq4_bridge": (16, 2048, 4, 11),
     }.items():
         x, w, cb = O.make_ref_inputs(M, K, Nq, seed=seed)
         y = bench.vq_gemm_reference(x, w, cb)

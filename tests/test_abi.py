@@ -82,6 +82,13 @@ def test_bad_arguments_are_rejected_without_cuda(lib):
     assert call(p, p, p, p, 4, 0, 8, 4, 256, 1, 0, 0, null, 0, null) == _lib.OK
     assert lib.vqg_dequant(p, p, p, 0, 8, 4, 256, 1, 0, 0, null) == _lib.OK
     assert lib.vqg_dequant(null, p, p, 8, 8, 4, 256, 1, 0, 0, null) == _lib.ERR_BAD_ARG
+    # misaligned pointers are refused with a status code, never handed to a kernel: 2-byte indices at an odd
+    # address, a codebook or an output that is not 16-byte aligned
+    odd = ctypes.c_void_p(4097)
+    off8 = ctypes.c_void_p(4096 + 8)
+    assert lib.vqg_dequant(odd, p, p, 8, 8, 4, 300, 2, 0, 0, null) == _lib.ERR_BAD_ARG
+    assert lib.vqg_dequant(p, off8, p, 8, 8, 8, 256, 1, 0, 0, null) == _lib.ERR_BAD_ARG
+    assert lib.vqg_dequant(p, p, off8, 8, 8, 8, 256, 1, 0, 0, null) == _lib.ERR_BAD_ARG
     assert lib.vqg_device_status(None) == _lib.ERR_BAD_ARG
     arr = (ctypes.c_void_p * 2)(4096, 8192)
     assert lib.vqg_gemm_sharded(p, p, p, arr, 2, 2, 1, 8, 8, 4, 256, 1, 0, null, 0, null) == _lib.ERR_BAD_ARG
@@ -110,6 +117,8 @@ def test_routing_of_the_benchmark_configurations(lib):
     assert auto(2048, 28672, 8192, 8, 256, 1, 128, 0) == P["tensor_ts"]  # C5
     assert auto(16, 28672, 8192, 8, 256, 1, 128, 0) == P["small_ts"]     # 16 rows on a large matrix
     assert auto(4, 28672, 8192, 8, 256, 1, 128, 0) == P["decode"]
+    assert auto(8, 28672, 8192, 8, 256, 1, 128, 0) == P["decode"]        # up to 8 rows the decode kernel wins everywhere
+    assert auto(16, 14336, 4096, 4, 256, 1, 128, 0) == P["decode"]       # 16 rows, one K chunk, replicated codebook
     assert auto(64, 28672, 8192, 8, 256, 1, 128, 0) == P["small_ts"]
     assert auto(128, 28672, 8192, 8, 256, 1, 128, 0) == P["tensor_ts"]
     assert auto(130, 96, 192, 4, 256, 1, 32, 0) == P["two_phase"]        # ragged K: dequantise, then the dense kernel

@@ -17,7 +17,18 @@ def test_bl_golden(tag):
     assert torch.equal(bits(w), bits(g["w_decoded"]))
 
 
-@pytest.mark.parametrize("tag", ["ref_small", "ref_two_tiles", "ref_ragged"])
+def test_bl_dequant_matches_bytes_gathered_by_the_reference():
+    # Nq = 4: the reference's gather (bench.py:46-55) with its single codebook IS the generalised rule with v = 2
+    g = load_golden("ref_nq4_bridge")
+    w = V.dequant(g["w"].cuda(), g["codebook"][0].contiguous().cuda(), rows_per_codebook=0, layout="bl")
+    assert torch.equal(bits(w), bits(g["w_decoded"]))
+    # and a product through that gather: Y = X8 @ W^T with W = the reference's bytes
+    x8 = g["x"][:, :8].contiguous()
+    y = V.vq_gemm(x8.cuda(), g["w"].cuda(), g["codebook"][0].contiguous().cuda(), rows_per_codebook=0, layout="bl")
+    assert O.check_tolerance(y.cpu(), O.matmul_fp32acc(x8, g["w_decoded"]))["ok"]
+
+
+@pytest.mark.parametrize("tag", ["ref_small", "ref_two_tiles", "ref_ragged", "ref_nq4_bridge"])
 def test_ref_golden_from_reference_gather(tag):
     g = load_golden(tag)
     w = V.dequant(g["w"].cuda(), g["codebook"].cuda(), layout="ref")

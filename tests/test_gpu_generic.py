@@ -47,3 +47,34 @@ def test_empty_and_zero_k():
     y = V.vq_gemm(torch.zeros(4, 0, dtype=torch.float16).cuda(), torch.zeros(8, 0, dtype=torch.uint8).cuda(), cb,
                   layout="bl")
     assert y.shape == (4, 8) and float(y.abs().max()) == 0.0
+
+
+def test_misaligned_codebook_is_routed_or_refused_never_faulted():
+    """A codebook whose address is not a multiple of its entry size (2v bytes) cannot be read by the kernels
+    that fetch whole entries: the automatic route then takes the half-by-half generic kernel, and asking for the
+    dequantising route explicitly returns a status code.  (A misaligned-address fault would lose the context.)"""
+    import ctypes
+    from vq_gemm_b200 import _lib
+    lib = _lib.load()
+    M, K, N, v, C, rpc = 130, 256, 256, 8, 256, 128
+    x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=5)
+    raw = torch.zeros(cb.numel() + 8, dtype=torch.float16, device="cuda")
+    cb_off = raw[4:4 + cb.numel()].view(cb.shape)            # 8 bytes past a 16-byte boundary
+    cb_off.copy_(cb)
+    assert cb_off.data_ptr() % 16 == 8
+    xd, idd = x.cuda(), idx.cuda()
+    y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    need = lib.vqg_workspace_bytes(M, N, K, v, C, 1, rpc, 0, _lib.PATH_TWO_PHASE)
+    ws_raw = torch.zeros(need + 1024, dtype=torch.uint8, device="cuda")
+    ws_ptr = (ws_raw.data_ptr() + 1023) // 1024 * 1024       # workspaces are 1024-byte aligned
+    st = lib.vqg_gemm(xd.data_ptr(), idd.data_ptr(), cb_off.data_ptr(), y.data_ptr(), M, N, K, v, C, 1, rpc, 0,
+                      ws_ptr, need, s)
+    assert st == _lib.OK
+    torch.cuda.synchronize()
+    assert_within_tolerance(y.cpu(), O.vq_gemm_bl(x, idx, cb, rpc))
+    before = lib.vqg_launch_count()
+    st = lib.vqg_gemm_path(xd.data_ptr(), idd.data_ptr(), cb_off.data_ptr(), y.data_ptr(), M, N, K, v, C, 1, rpc, 0,
+                           _lib.PATH_TWO_PHASE, ws_ptr, need, s)
+    assert st == _lib.ERR_BAD_ARG and lib.vqg_launch_count() == before
+    assert V.device_status() == 0

@@ -16,7 +16,7 @@ def _load(path):
     return {k: torch.from_numpy(z[k]) for k in z.files}
 
 
-@pytest.mark.parametrize("tag", ["ref_small", "ref_two_tiles", "ref_ragged"])
+@pytest.mark.parametrize("tag", ["ref_small", "ref_two_tiles", "ref_ragged", "ref_nq4_bridge"])
 def test_ref_layout_matches_reference_gather(golden_dir, tag):
     g = _load(os.path.join(golden_dir, tag + ".npz"))
     wdec = O.dequant_ref_layout(g["w"], g["codebook"])
@@ -36,10 +36,23 @@ def test_bl_layout_matches_fixture(golden_dir, tag):
     assert (y.float() - g["y"].float()).abs().max() <= 2e-3  # same algorithm; only summation order may differ
 
 
+def test_bl_gather_matches_bytes_gathered_by_the_reference(golden_dir):
+    """With Nq = 4 the reference's gather (bench.py:46-55) uses one codebook for every index column, and its
+    w_decoded [K, 8] is the generalised rule applied to idx = w read as [N = K, 4], v = 2, single codebook:
+    the BL gather against bytes produced by the reference's own code."""
+    g = _load(os.path.join(golden_dir, "ref_nq4_bridge.npz"))
+    assert g["w"].shape[1] == 4 and g["codebook"].shape[0] == 1
+    a = O.dequant_bl_layout(g["w"], g["codebook"][0], 0)
+    assert a.shape == g["w_decoded"].shape
+    assert torch.equal(a.view(torch.int16), g["w_decoded"].view(torch.int16))
+    b = O.dequant_bl_scalar(g["w"][:64], g["codebook"][0], 0)
+    assert torch.equal(b.view(torch.int16), g["w_decoded"][:64].view(torch.int16))
+
+
 def test_golden_files_all_covered(golden_dir):
     tags = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(golden_dir, "*.npz")))
-    assert tags == ["bl_v4_c256_groups", "bl_v8_c256_groups", "bl_v8_c4096_single", "ref_ragged", "ref_small",
-                    "ref_two_tiles"]
+    assert tags == ["bl_v4_c256_groups", "bl_v8_c256_groups", "bl_v8_c4096_single", "ref_nq4_bridge", "ref_ragged",
+                    "ref_small", "ref_two_tiles"]
 
 
 @pytest.mark.parametrize("N,K,v,C,rpc,dtype", [

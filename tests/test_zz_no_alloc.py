@@ -78,11 +78,50 @@ def test_noalloc_entry_without_split_k_and_limits():
     assert torch.equal(bits(a), bits(b))
     s = torch.cuda.current_stream().cuda_stream
     p = ctypes.c_void_p(xd.data_ptr())
-    # 16 x 65536 outputs over 4 chunks of K = 16 MiB of partial sums > 4 MiB: refused, nothing launched
+    # few rows and a very long K: the chunks of K are handed over through scratch, 8 chunks x 16 x 12288 outputs
+    # x 4 bytes = 6 MiB > 4 MiB: refused, nothing launched.  (Real buffers of the right size, so that a refusal
+    # that failed to happen would still be a well-formed call.)
+    Mb, Nb, Kb = 16, 12288, 32768
+    need = lib.vqg_workspace_bytes(Mb, Nb, Kb, 8, 256, 1, 128, _lib.LAYOUT_BL, _lib.PATH_DECODE)
+    assert need > (4 << 20)
+    xb = torch.zeros((Mb, Kb), dtype=torch.float16, device="cuda")
+    ib_ = torch.zeros((Nb, Kb // 8), dtype=torch.uint8, device="cuda")
+    cbb = torch.zeros((Nb // 128, 256, 8), dtype=torch.float16, device="cuda")
+    yb = torch.zeros((Mb, Nb), dtype=torch.float16, device="cuda")
     before = lib.vqg_launch_count()
-    st = lib.vqg_gemm_small_batch_noalloc(p, p, p, p, 16, 65536, 16384, 8, 256, 1, 128, s)
+    st = lib.vqg_gemm_small_batch_noalloc(xb.data_ptr(), ib_.data_ptr(), cbb.data_ptr(), yb.data_ptr(), Mb, Nb, Kb, 8, 256, 1,
+                                          128, s)
     assert st == _lib.ERR_TOO_LARGE and "static buffer" in _lib.status_string(st)
     assert lib.vqg_launch_count() == before
+    del xb, ib_, cbb, yb
     # shapes outside the small-batch kernel are refused too (no other kernel behind this entry)
     assert lib.vqg_gemm_small_batch_noalloc(p, p, p, p, 17, 1024, 4096, 4, 256, 1, 128, s) == _lib.ERR_UNSUPPORTED
     assert lib.vqg_gemm_small_batch_noalloc(p, p, p, p, 4, 1024, 4096 + 64, 4, 256, 1, 128, s) == _lib.ERR_UNSUPPORTED
+
+
+def test_noalloc_calls_leave_free_device_memory_unchanged():
+    """After the first call on the device (which is when the runtime loads the library's module and its fixed
+    array), further calls must not change the amount of free device memory: a host that has given the rest of
+    the GPU to its own pool can keep calling."""
+    lib = _lib.load()
+    M, K, N, v, C, rpc = 4, 8192, 512, 4, 256, 128          # split-K through the fixed array
+    x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=31)
+    xd, idd, cbd = x.cuda(), idx.cuda(), cb.cuda()
+    y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        st = lib.vqg_gemm_small_batch_noalloc(xd.data_ptr(), idd.data_ptr(), cbd.data_ptr(), y.data_ptr(), M, N, K, v, C, 1,
+                                              rpc, s)
+        assert st == _lib.OK, _lib.status_string(st)
+        torch.cuda.synchronize()
+
+    call()                                                   # first call: module load, address lookup
+    free0 = torch.cuda.mem_get_info()[0]
+    call()
+    free1 = torch.cuda.mem_get_info()[0]
+    call()
+    free2 = torch.cuda.mem_get_info()[0]
+    assert free0 == free1 == free2
+    assert_within_tolerance(y.cpu(), O.vq_gemm_bl(x, idx, cb, rpc))
+    assert "memory" in _lib.status_string(8)                 # VQG_ERR_NO_MEMORY has its own message

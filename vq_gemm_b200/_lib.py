@@ -11,7 +11,7 @@ from ctypes import c_char_p, c_int, c_longlong, c_size_t, c_ulonglong, c_void_p,
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libvqg_b200.so")
 
-OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_LAUNCH, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE = range(8)
+OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_LAUNCH, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE, ERR_NO_MEMORY = range(9)
 LAYOUT_BL, LAYOUT_REF = 0, 1
 PATH_AUTO, PATH_GENERIC, PATH_DECODE, PATH_TENSOR, PATH_TWO_PHASE, PATH_TENSOR_PAIR, PATH_TENSOR_TS, PATH_SMALL_TS = range(8)
 PATHS = {"auto": PATH_AUTO, "generic": PATH_GENERIC, "decode": PATH_DECODE, "tensor": PATH_TENSOR,

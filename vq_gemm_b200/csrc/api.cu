@@ -82,16 +82,15 @@ int auto_path(const Problem& p, int layout) {
     return dense_supported(p.M, p.N, p.K) && p.M >= 32 ? VQG_PATH_TWO_PHASE : VQG_PATH_GENERIC;
   }
   if (p.K == 0) return VQG_PATH_GENERIC;
-  // Measured routing (B200, CUDA events).  Register-level decode kernel: best up to 4 batch rows, and up to 16
-  // while the problem is small (C1: 10.9 us against 13.3 us) and the codebook fits its replicated image; its
-  // cost grows with the batch on large matrices (M = 16, 29 MB of indices: 115 us against 50 us).  The
-  // small-batch tensor-memory kernel takes over from there up to 96 rows; above that the pair kernel with its
-  // 256-row batch tile is as fast or faster even half empty (M = 128: 38 us against 46 us on the C4 weights).
-  const double index_bytes = static_cast<double>(p.N) * (p.K / (p.v > 0 ? p.v : 1)) * p.idx_bytes;
+  // Measured routing (B200, CUDA-graph replay over index buffers larger than L2).  Register-level decode kernel:
+  // fastest up to 8 batch rows on every matrix tried (4 MB ... 29 MB of indices, 256- and 4096-entry codebooks), and
+  // up to 16 rows while K fits one chunk of its warps (K <= 4096) and the codebook its replicated image (C4 weights,
+  // M = 16: 16.9 us against 20.3 us); with more chunks or an unreplicated codebook its 16-row form loses (70B
+  // weights, M = 16: 54 us against 41 us).  The small-batch tensor-memory kernel takes over from there up to 96
+  // rows; above that the pair kernel with its 256-row batch tile is as fast or faster even half empty.
   const bool small_ok = small_ts_supported(p);
   if (p.M <= 16 && decode_supported(p)) {
-    const bool large = index_bytes >= (p.M <= 8 ? 20e6 : 8e6);
-    const bool prefer_small = small_ok && p.M > 4 && (large || p.C > 256);
+    const bool prefer_small = small_ok && p.M > 8 && (p.K > 4096 || p.C > 256);
     if (!prefer_small) return VQG_PATH_DECODE;
   }
   if (p.M <= 96 && small_ok) return VQG_PATH_SMALL_TS;
@@ -99,7 +98,11 @@ int auto_path(const Problem& p, int layout) {
   if (p.M <= 128 && small_ok) return VQG_PATH_SMALL_TS;
   if (p.M > 128 && tensor_pair_supported(p)) return VQG_PATH_TENSOR_PAIR;
   if (p.M > 16 && tensor_supported(p)) return VQG_PATH_TENSOR;
-  if (p.M > 16 && dense_supported(p.M, p.N, p.K) && (p.v == 2 || p.v == 4 || p.v == 8)) return VQG_PATH_TWO_PHASE;
+  // the dequantising kernels read whole codebook entries: a codebook that is not aligned to its entry size
+  // (2v bytes) goes to the generic kernel, which reads it half by half
+  if (p.M > 16 && dense_supported(p.M, p.N, p.K) && (p.v == 2 || p.v == 4 || p.v == 8) &&
+      aligned(p.cb, static_cast<size_t>(2 * p.v)))
+    return VQG_PATH_TWO_PHASE;
   return VQG_PATH_GENERIC;
 }
 
@@ -167,6 +170,7 @@ const char* vqg_status_string(int status) {
     case VQG_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
     case VQG_ERR_NO_DEVICE: return "no usable CUDA device";
     case VQG_ERR_TOO_LARGE: return "problem needs more scratch than the library's built-in static buffer holds";
+    case VQG_ERR_NO_MEMORY: return "out of device memory while loading the library's code and static data onto the device";
     default: return "unknown status";
   }
 }
@@ -222,8 +226,9 @@ int vqg_dequant(const void* idx, const void* codebook, void* w_out, int N, int K
   }
   if (layout != VQG_LAYOUT_BL) return VQG_ERR_BAD_ARG;
   if (v < 1 || C < 1 || K % v != 0) return VQG_ERR_BAD_ARG;
+  if (idx_bytes != 1 && idx_bytes != 2) return VQG_ERR_UNSUPPORTED;
   if (idx_bytes == 1 && C > 256) return VQG_ERR_BAD_ARG;
-  if (!aligned(w_out, 16) || !aligned(codebook, 16)) return VQG_ERR_BAD_ARG;
+  if (!aligned(w_out, 16) || !aligned(codebook, 16) || !aligned(idx, static_cast<size_t>(idx_bytes))) return VQG_ERR_BAD_ARG;
   const int rpc = (rows_per_codebook <= 0 || rows_per_codebook > N) ? N : rows_per_codebook;
   return launch_dequant_bl(idx, static_cast<const __half*>(codebook), static_cast<__half*>(w_out), N, K, v, C,
                            idx_bytes, rpc, s);
@@ -368,6 +373,7 @@ int vqg_gemm_small_batch_noalloc(const void* x, const void* idx, const void* cod
   if (M == 0 || N == 0) return VQG_OK;
   if (M > 16) return VQG_ERR_UNSUPPORTED;
   Problem p = make_problem(x, idx, codebook, y, M, N, K, v, C, idx_bytes, rows_per_codebook, N);
+  if (K == 0) return launch_generic(p, VQG_LAYOUT_BL, static_cast<cudaStream_t>(stream));   // Y = 0, as vqg_gemm gives
   return launch_decode_static(p, static_cast<cudaStream_t>(stream));
 }
 

@@ -1,79 +1,98 @@
 // Memory-bound VQ-GEMM for M <= 16 (decode / small batch), sm_100a.
 //
 // The problem is a GEMV-like stream over the index matrix: every index is read once from HBM
-// and costs one shared-memory codebook lookup.  The kernel is persistent (one 512-thread CTA per
-// SM) and works on items of 16 output rows x up to 4096 K values:
+// and costs one shared-memory codebook lookup.  What this kernel is built around:
 //
-//   * indices are streamed with 64-/128-bit loads straight into registers, one batch (2-3 items)
-//     ahead of use, so tens of KiB per SM are in flight;
-//   * the codebook of the item's group sits in shared memory as a REPLICATED image: entry c,
+//   * index tiles arrive by TMA (cp.async.bulk.tensor.2d, no multicast) behind mbarriers, into a
+//     PRIVATE ring of each warp: a warp owns one K slice (512 K values for M <= 4, 256 above) and
+//     walks over the row blocks of its CTA, so its tiles are [8 or 16 rows] x [one slice] = 1 KiB,
+//     several of them in flight, and no warp ever waits for another one while streaming.  The tile
+//     is stored with the TMA swizzle that matches its row length (32/64/128 bytes), which makes the
+//     16-byte reads of the eight rows of a unit conflict-free.  The first tiles are requested a few
+//     hundred cycles into the kernel, before anything else is set up;
+//   * the codebook of a row block's group sits in shared memory as a REPLICATED image: entry c,
 //     replica r at byte  c*(R*2v) + r*2v , lane uses replica lane % R.  With R = 64/v
 //     (C <= 256) a warp-wide lookup touches every bank exactly once per wavefront;
 //   * looked-up entries go into mma.sync.m16n8k16 operand registers AS THEY ARRIVE -- no
-//     conversion, shuffle or register move -- and accumulation is fp32 in the tensor core.  Every
-//     thread (g, t) of a warp owns weight row n0+g and the 64 K values [64t, 64t+64) of the
-//     warp's 256-wide K slice.  Two operand arrangements:
+//     conversion, shuffle or register move -- and accumulation is fp32 in the tensor core.  Thread
+//     (g, t) of a warp owns weight row n0+g and a contiguous quarter of the warp's K slice.
 //       form 1 (M <= 4)  16 bytes of codebook data (one v=8 entry, or two consecutive v=4 entries)
 //         are the 4 registers of an A fragment: MMA row g sees K pairs {0-1, 4-5} of them, MMA row
 //         g+8 sees pairs {2-3, 6-7}.  X is the B operand with two columns per batch row m:
 //         column 2m carries X for the pairs of row g, column 2m+1 those of row g+8, so that
-//         y[n0+g][m] = D[g][2m] + D[g+8][2m+1].  One MMA per 16 codebook bytes.
-//       form 2 (M <= 16) a v=4 entry (or half a v=8 entry) is the 2-register B fragment of
+//         y[n0+g][m] = D[g][2m] + D[g+8][2m+1].  One MMA per 16 codebook bytes.  256 threads and at
+//         most 128 registers: two launches fit an SM side by side, so with programmatic dependent
+//         launch the whole prologue of launch i+1 (tiles in flight, image built) hides behind launch i;
+//       forms 2/3 (M <= 8 / 16) a v=4 entry (or half a v=8 entry) is the 2-register B fragment of
 //         column g; X (batch rows g and g+8) is the A operand.  One MMA per 8 codebook bytes.
-//     The X fragments are loaded once and stay in registers;
-//   * each warp owns a 256-wide K slice; the 16 partial tiles of a CTA are summed in a fixed
-//     order through shared memory (deterministic), one barrier per batch, and K > 4096 adds a
-//     split-K step through a caller-provided workspace in which the last-arriving CTA of a row
-//     block sums the chunks in chunk order (also deterministic).
+//     The X fragments of a warp's slice are loaded once per K chunk, straight from global memory in
+//     register order, and stay in registers;
+//   * the partial tiles of a CTA's warps are summed in slice order through shared memory
+//     (deterministic), one barrier per batch of row blocks; K > 4096 either walks the chunks with
+//     running sums in shared memory (a CTA owns its rows for all of K) or, on matrices with few
+//     row blocks, hands fp32 partials over through a workspace in which the last-arriving CTA of
+//     a row block sums the chunks in chunk order (also deterministic).
 //
 // There is no reference counterpart: the reference requires M % 128 == 0
-// (strategy_1/src.cu:221).
+// (strategy_1/src.cu:221); the dequantisation rule is that of strategy_2/bsz128/src.cu:179-190.
 #include <mutex>
+#include <type_traits>
 
-#include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace vqg {
 
 namespace {
 
-constexpr int kThreads = 512;
-constexpr int kWarps = 16;
-constexpr int kSliceK = 256;     // K values per warp slice
-
 struct DecodeParams {
   const __half* x;
-  const void* idx;
   const __half* cb;
   __half* y;
-  float* ws_partial;   // [nchunks][M][N] fp32 (split-K only)
-  int* ws_counter;     // [items per chunk]
+  float* ws_partial;   // [nchunks][M][N] fp32 (split-K through the workspace only)
+  int* ws_counter;     // [row block groups]
   int* status;
   int M, N, K, C;
-  int rows_per_cb;
   long long ld_y;
-  int nslices;         // K / 256
-  int nchunks;         // ceil(nslices / 16)
-  int rl;              // 16-row blocks processed side by side by one CTA
-  int nrbg;            // N / (16 * rl)
-  int rep_log2;        // log2 of codebook replicas
+  int nslices;         // K / KS
+  int nchunks;         // ceil(nslices / warps)
+  int rl;              // row lanes: super-units processed side by side by one CTA (warps / slices when K is short)
+  int nrbg;            // items per chunk: ceil(N / (8 * SU * rl))
   int nslots;          // resident codebook images (1 or 2)
   int items_q, items_r; // items per CTA: q, and one more for the first r CTAs
   int ipg;             // items per codebook group
-  int lpo;             // lanes per output in the cross-warp reduction (power of two)
-  int lpo_log2;
-  int inv_m, inv_rl;   // ceil(65536 / M), ceil(65536 / rl): t / M == (t * inv_m) >> 16 for t < 4096
+  int stages;          // tiles in flight per warp
+  int batch;           // items per reduction batch (<= kMaxBatch)
+  int bar_offset, img_offset, part_offset, acc_offset;   // byte offsets into the 1024-aligned shared memory
+  unsigned inv_m, inv_rl;   // ceil(2^32 / M), ceil(2^32 / rl), 0 for a divisor of 1: t / M == umulhi(t, inv_m) for the small t in use
   int n_peers;
   __half* peer_y[8];
-  // K > 4096 on matrices with many row blocks: a CTA owns a range of row blocks for ALL K chunks (items_q/r then
-  // partition the row blocks), walks the chunks one after the other and keeps the running sums of its rows in
-  // shared memory at byte offset acc_offset -- no partial sums in global memory, no counters, no hand-over.
+  // K > 4096 on matrices with many row blocks: a CTA owns a range of items for ALL K chunks (items_q/r then
+  // partition the items of one chunk), walks the chunks one after the other and keeps the running sums of its
+  // rows in shared memory at acc_offset -- no partial sums in global memory, no counters, no hand-over.
   int row_owned;
-  int acc_offset;
+};
+
+constexpr int kMaxBatch = 16;
+
+
+// Geometry of one instantiation.
+template <int V, int IB, int FORM>
+struct Geo {
+  static constexpr int NW = (FORM == 1) ? 8 : 16;      // warps per CTA
+  static constexpr int NT = NW * 32;
+  static constexpr int KS = (FORM == 1) ? 512 : 256;   // K values per warp slice
+  static constexpr int TK = KS / 4;                    // K values per thread and unit (contiguous)
+  static constexpr int SLABB = KS / V * IB;            // index bytes per row and slice: 128, 64 or 32
+  static constexpr int TB = SLABB / 4;                 // index bytes per thread and row: 32, 16 or 8
+  static constexpr int SU = (SLABB >= 128) ? 1 : 2;    // 8-row units per tile
+  static constexpr int STAGE = 8 * SU * SLABB;         // tile bytes: 1024 (512 for 32-byte rows)
+  static constexpr int XR = (FORM == 1) ? TK / 4 : (FORM == 2 ? TK / 2 : TK);   // X fragment registers per thread
+  static constexpr int W64 = 64 / V * IB / 4;          // index words per 64 K values
 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -92,19 +111,16 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr, uint32_t epoch) {
   asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];  // %5" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr), "r"(epoch));
   return r;
 }
-
-template <int WORDS>
-struct IdxRegs { uint32_t w[WORDS]; };
-
-template <int WORDS>
-__device__ __forceinline__ void load_idx(IdxRegs<WORDS>& r, const void* p) {
-  if constexpr (WORDS == 2) {
-    uint2 t = __ldcs(reinterpret_cast<const uint2*>(p));
-    r.w[0] = t.x; r.w[1] = t.y;
-  } else {
-    uint4 t = __ldcs(reinterpret_cast<const uint4*>(p));
-    r.w[0] = t.x; r.w[1] = t.y; r.w[2] = t.z; r.w[3] = t.w;
-  }
+// Index words out of a TMA tile: volatile, they must stay behind the wait on the tile's mbarrier.
+__device__ __forceinline__ uint4 lds128_tile(uint32_t addr) {
+  uint4 r;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr) : "memory");
+  return r;
+}
+__device__ __forceinline__ uint2 lds64_tile(uint32_t addr) {
+  uint2 r;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(addr) : "memory");
+  return r;
 }
 
 template <int IB>
@@ -113,241 +129,286 @@ __device__ __forceinline__ uint32_t idx_at(const uint32_t* w, int i) {
   else return __byte_perm(w[i >> 1], 0, (i & 1) ? 0x4432 : 0x4410);
 }
 
-// V: sub-vector length (4 or 8); IB: index bytes (1 or 2; 2 only with V = 8);
-// FORM: 1 (M <= 4), 2 (M <= 8), 3 (M <= 16; form 2 with batch rows g+8 live);
-// REPL: codebook image replicated to fill 128-byte lines (conflict-free) or stored once.
-//
-// Items are processed in batches of up to PFB consecutive items of one K chunk.  While a batch is
-// being computed the index loads of the next batch are in flight; a batch ends with ONE block-wide
-// barrier and a parallel, fixed-order reduction of the 16 warps' partial tiles.  Up to two codebook
-// images (groups of even / odd number) are resident, so a batch may straddle a group boundary.
-//
-// Shared memory:  [image slot 0][image slot 1 (if it fits)][ X staging | reduction buffers ]
-template <int V, int IB, int FORM, bool REPL>
-__global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodeParams p) {
-  constexpr int UB = (IB == 1 && V == 8) ? 8 : 16;  // index bytes per thread and 8-row unit (= 64 K values)
-  constexpr int WORDS = UB / 4;
-  constexpr int NIDX = UB / IB;                      // indices per thread and unit
-  constexpr int ENTRY_LOG2 = (V == 4) ? 3 : 4;
-  constexpr int REP_LOG2 = REPL ? (7 - ENTRY_LOG2) : 0;  // replicas fill a 128-byte line, or none at all
-  constexpr int ENTRY_SHIFT = ENTRY_LOG2 + REP_LOG2;
-  // items per batch: every batch ends with two barriers, the cross-warp reduction and (K > 4096) the split-K
-  // hand-over, so large matrices want long batches; with 16-byte entries the index registers are few
-  constexpr int PFB = (FORM == 1) ? 6 : (FORM == 2 ? (V == 8 ? 6 : 3) : (V == 8 ? 4 : 2));
-  constexpr int XR = (FORM == 1) ? 16 : (FORM == 2 ? 32 : 64);  // X fragment registers per thread
-  constexpr int XSLOT = XR + 4;                      // staging words per thread (16-byte aligned, bank-spread)
-  static_assert(NIDX * V == 64, "a thread-unit spans 64 K values");
-  extern __shared__ __align__(16) unsigned char smem[];
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int g = lane >> 2, t4 = lane & 3;
-  const int J = p.K / V;
-
-  const uint32_t img_bytes = static_cast<uint32_t>(p.C) << ENTRY_SHIFT;
-  unsigned char* work = smem + static_cast<size_t>(p.nslots) * img_bytes;   // staging, then reduction buffers
-  float* red = reinterpret_cast<float*>(work);                              // [2][kWarps][warp_stride]
-  uint32_t* stage = reinterpret_cast<uint32_t*>(work);                      // [kWarps][32][XSLOT]
-  const int unit_floats = p.M * 8;                           // [m][8 rows]
-  const int warp_stride = PFB * 2 * unit_floats + 2;         // +2: slices land in different banks, 8-byte aligned
-  __shared__ int s_last[PFB];
-
-  // this lane's replica inside an image (32-bit shared address of slot 0)
-  const uint32_t img_lane = smem_u32(smem) + ((lane & ((1 << REP_LOG2) - 1)) << ENTRY_LOG2);
-  uint32_t epoch = 0;
-
-  // static contiguous partition of the items (chunk-major so X stays in registers); the host supplies
-  // quotient and remainder so that no 64-bit division runs on the device
-  const int bid = blockIdx.x;
-  int it_begin = bid * p.items_q + min(bid, p.items_r);
-  int it_end = it_begin + p.items_q + (bid < p.items_r ? 1 : 0);
-  // the next kernel in the stream may be scheduled as soon as SMs free up (it waits as below before it
-  // touches anything this kernel reads or writes)
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (it_end <= it_begin) return;
-  // row blocks this CTA walks: all of them (items then run over chunks and row blocks, chunk-major), or its
-  // own range once per chunk
-  int r_begin = 0, r_end = p.nrbg;
-  if (p.row_owned) {
-    r_begin = it_begin;
-    r_end = it_end;
-    it_begin = 0;
-    it_end = (r_end - r_begin) * p.nchunks;
-  }
-  float* accbuf = reinterpret_cast<float*>(smem + p.acc_offset);   // [row block - r_begin][rl][M][16], row-owned mode
-
-  // warp role inside a chunk: (slice, row lane)
-  const int nsl_full = min(kWarps, p.nslices);
-  const int wsl = warp % nsl_full;
-  const int wrl = warp / nsl_full;
-  const bool role_ok = wrl < p.rl;
-  const unsigned char* idx_lane = static_cast<const unsigned char*>(p.idx) +
-      (static_cast<size_t>(wrl * 16 + g) * J + static_cast<size_t>(t4) * NIDX) * IB;
-  const size_t row8_bytes = static_cast<size_t>(8) * J * IB;
-  const size_t item_bytes = static_cast<size_t>(p.rl) * 16 * J * IB;   // rows of one item
-
-  uint32_t xf[XR];
-  int loaded_chunk = -1;
-  int slot_group0 = -1, slot_group1 = -1;   // which group each image slot holds
-  bool active = false;
-
-  struct Batch { int cnt, chunk, rbg, gpos, group; };  // group/gpos: codebook group of the first item, position in it
-  auto make_batch = [&](int it, int chunk, int rbg, int gpos, int group) {
-    Batch b;
-    b.chunk = chunk; b.rbg = rbg; b.gpos = gpos; b.group = group;
-    int c = it_end - it;
-    c = min(c, PFB);
-    c = min(c, r_end - rbg);
-    c = min(c, p.nslots * p.ipg - gpos);   // a batch touches at most `nslots` consecutive groups
-    b.cnt = c > 0 ? c : 0;
-    return b;
-  };
-
-  IdxRegs<WORDS> cur[PFB][2];
-  auto issue_loads = [&](const Batch& b, IdxRegs<WORDS> (&dst)[PFB][2]) {
-    const int slice = b.chunk * kWarps + wsl;
-    if (role_ok && slice < p.nslices) {
-      const unsigned char* base = idx_lane + static_cast<size_t>(slice) * (kSliceK / V) * IB +
-                                  static_cast<size_t>(b.rbg) * item_bytes;
+// The products of one thread for 64 of its K values and one 8-row unit: `w` holds the indices of those K values,
+// `xf` the matching X fragment registers, `img` is the lane's replica inside the group's codebook image.
+template <int V, int IB, int FORM, int ENTRY_SHIFT>
+__device__ __forceinline__ void piece_mma(float (&acc)[4][4], const uint32_t* w, const uint32_t* xf,
+                                          uint32_t img, uint32_t epoch) {
+  if constexpr (FORM == 1) {
+    if constexpr (V == 4) {
+      uint2 e[16];
 #pragma unroll
-      for (int s = 0; s < PFB; ++s) {
-        if (s < b.cnt) {
-          load_idx<WORDS>(dst[s][0], base + s * item_bytes);
-          load_idx<WORDS>(dst[s][1], base + s * item_bytes + row8_bytes);
-        }
-      }
-    }
-  };
-
-  // Builds the image of `group` in slot `slot` (no barriers inside).
-  auto build_image = [&](int group, int slot) {
-    unsigned char* img = smem + static_cast<size_t>(slot) * img_bytes;
-    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.cb) +
-                               (static_cast<size_t>(group) * p.C << ENTRY_LOG2);
-    if constexpr (V == 4 && REPL) {   // one 16-byte store = two replicas of an 8-byte entry
-      const int units = p.C << (REP_LOG2 - 1);
-      for (int u0 = 0; u0 < units; u0 += 4 * kThreads) {
-        uint2 e[4];
+      for (int i = 0; i < 16; ++i) e[i] = lds64(img + (idx_at<IB>(w, i) << ENTRY_SHIFT), epoch);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int u = u0 + j * kThreads + tid;
-          if (u < units) e[j] = __ldg(reinterpret_cast<const uint2*>(src) + (u >> (REP_LOG2 - 1)));
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int u = u0 + j * kThreads + tid;
-          if (u < units) reinterpret_cast<uint4*>(img)[u] = make_uint4(e[j].x, e[j].y, e[j].x, e[j].y);
-        }
-      }
-    } else if constexpr (V == 4) {
-      for (int u = tid; u < p.C; u += kThreads)
-        reinterpret_cast<uint2*>(img)[u] = __ldg(reinterpret_cast<const uint2*>(src) + u);
+      for (int q = 0; q < 8; ++q)
+        mma_16816(acc[q & 3], e[2 * q].x, e[2 * q].y, e[2 * q + 1].x, e[2 * q + 1].y, xf[2 * q], xf[2 * q + 1]);
     } else {
-      const int units = p.C << REP_LOG2;
-      for (int u0 = 0; u0 < units; u0 += 4 * kThreads) {
+      uint4 e[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) e[i] = lds128(img + (idx_at<IB>(w, i) << ENTRY_SHIFT), epoch);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) mma_16816(acc[q & 3], e[q].x, e[q].y, e[q].z, e[q].w, xf[2 * q], xf[2 * q + 1]);
+    }
+  } else {
+    constexpr int XS = (FORM == 2) ? 2 : 4;
+    if constexpr (V == 4) {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {   // two halves of 8 lookups keep the register count down
+        uint2 e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = lds64(img + (idx_at<IB>(w, 8 * hf + i) << ENTRY_SHIFT), epoch);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int ii = 8 * hf + i;
+          if constexpr (FORM == 2) mma_16816(acc[i & 3], xf[XS * ii], 0u, xf[XS * ii + 1], 0u, e[i].x, e[i].y);
+          else mma_16816(acc[i & 3], xf[XS * ii], xf[XS * ii + 1], xf[XS * ii + 2], xf[XS * ii + 3], e[i].x, e[i].y);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {   // two halves of 4 lookups keep the register count down
         uint4 e[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int u = u0 + j * kThreads + tid;
-          if (u < units) e[j] = __ldg(reinterpret_cast<const uint4*>(src) + (u >> REP_LOG2));
-        }
+        for (int i = 0; i < 4; ++i) e[i] = lds128(img + (idx_at<IB>(w, 4 * hf + i) << ENTRY_SHIFT), epoch);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int u = u0 + j * kThreads + tid;
-          if (u < units) reinterpret_cast<uint4*>(img)[u] = e[j];
-        }
-      }
-    }
-  };
-
-  // Loads the chunk's X (M rows x up to 4096 K values) with coalesced 16-byte loads and scatters every
-  // piece into the staging slot of the thread(s) that own it, already in fragment-register order; then
-  // each thread reads its XR registers back with 16-byte loads.  Two barriers; the staging area is
-  // the same memory as the reduction buffers.
-  auto load_x_fragments = [&](int chunk) {
-    const int nsl = min(kWarps, p.nslices - chunk * kWarps);
-    const int kc8 = nsl * (kSliceK / 8);                       // 16-byte pieces per batch row
-    const __half* xbase = p.x + static_cast<size_t>(chunk) * kWarps * kSliceK;
-    __syncthreads();                                           // reduction buffers are no longer read
-    // rows in groups of four (four independent loads in flight per thread), pieces strided over the CTA
-#pragma unroll 1
-    for (int m0 = 0; m0 < p.M; m0 += 4) {
-#pragma unroll 1
-      for (int kg = tid; kg < kc8; kg += kThreads) {
-        uint4 v[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (m0 + j < p.M) v[j] = __ldg(reinterpret_cast<const uint4*>(xbase + static_cast<size_t>(m0 + j) * p.K) + kg);
-        const int slice = kg >> 5, tt = (kg >> 3) & 3, i2 = kg & 7;   // owner warp slice, t4, position
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int m = m0 + j;
-          if (m >= p.M) continue;
-          // all row lanes of a slice need the same X
-#pragma unroll 1
-          for (int lr = 0; lr < p.rl; ++lr) {
-            uint32_t* wbase = stage + static_cast<size_t>(lr * nsl_full + slice) * 32 * XSLOT;
-            if constexpr (FORM == 1) {
-              // lanes g = 2m (pairs 0, 2 of the 8-group) and g = 2m + 1 (pairs 1, 3)
-              uint32_t* d0 = wbase + ((2 * m) * 4 + tt) * XSLOT + 2 * i2;
-              uint32_t* d1 = wbase + ((2 * m + 1) * 4 + tt) * XSLOT + 2 * i2;
-              *reinterpret_cast<uint2*>(d0) = make_uint2(v[j].x, v[j].z);
-              *reinterpret_cast<uint2*>(d1) = make_uint2(v[j].y, v[j].w);
-            } else if constexpr (FORM == 2) {
-              // lane g = m: groups 2*i2, 2*i2+1 -> registers 4*i2 .. 4*i2+3 in order
-              *reinterpret_cast<uint4*>(wbase + (m * 4 + tt) * XSLOT + 4 * i2) = v[j];
-            } else {
-              // lane g = m & 7, upper row selects registers +1: group i -> regs 4i+u (pair 0), 4i+2+u (pair 1)
-              uint32_t* d = wbase + ((m & 7) * 4 + tt) * XSLOT + 8 * i2 + (m >> 3);
-              d[0] = v[j].x; d[2] = v[j].y; d[4] = v[j].z; d[6] = v[j].w;
-            }
+        for (int i = 0; i < 4; ++i) {
+          const int ii = 4 * hf + i;
+          if constexpr (FORM == 2) {
+            mma_16816(acc[(2 * i) & 3], xf[XS * 2 * ii], 0u, xf[XS * 2 * ii + 1], 0u, e[i].x, e[i].y);
+            mma_16816(acc[(2 * i + 1) & 3], xf[XS * (2 * ii + 1)], 0u, xf[XS * (2 * ii + 1) + 1], 0u, e[i].z, e[i].w);
+          } else {
+            mma_16816(acc[(2 * i) & 3], xf[XS * 2 * ii], xf[XS * 2 * ii + 1], xf[XS * 2 * ii + 2], xf[XS * 2 * ii + 3], e[i].x, e[i].y);
+            mma_16816(acc[(2 * i + 1) & 3], xf[XS * (2 * ii + 1)], xf[XS * (2 * ii + 1) + 1], xf[XS * (2 * ii + 1) + 2],
+                      xf[XS * (2 * ii + 1) + 3], e[i].z, e[i].w);
           }
         }
       }
     }
-    __syncthreads();
-    const uint4* mine4 = reinterpret_cast<const uint4*>(stage + static_cast<size_t>(warp * 32 + lane) * XSLOT);
-    const bool live = (FORM == 1) ? ((g >> 1) < p.M) : (g < p.M);
-#pragma unroll
-    for (int j = 0; j < XR / 4; ++j) {
-      uint4 t = make_uint4(0, 0, 0, 0);
-      if (live && role_ok && wsl < nsl) t = mine4[j];
-      xf[4 * j] = t.x; xf[4 * j + 1] = t.y; xf[4 * j + 2] = t.z; xf[4 * j + 3] = t.w;
+  }
+}
+
+// V: sub-vector length (4 or 8); IB: index bytes (1 or 2; 2 only with V = 8);
+// FORM: 1 (M <= 4), 2 (M <= 8), 3 (M <= 16; form 2 with batch rows g+8 live);
+// REPL: codebook image replicated to fill 128-byte lines (conflict-free) or stored once.
+//
+// An item is rl tiles side by side (8*SU rows each) of one K chunk; a CTA works through a contiguous
+// range of items, in batches of up to `batch` items of one chunk that touch at most `nslots`
+// consecutive codebook groups.  A batch ends with ONE block-wide barrier and a fixed-order sum of the
+// warps' partial tiles (double-buffered, so the next batch's lookups run meanwhile).
+//
+// Shared memory (1024-aligned):  [warp rings][mbarriers][image slot 0][image slot 1][partial tiles x2][running sums]
+template <int V, int IB, int FORM, bool REPL>
+__global__ void __launch_bounds__(Geo<V, IB, FORM>::NT, (FORM == 1) ? 2 : 1)
+vq_decode_kernel(const __grid_constant__ CUtensorMap idx_map, const DecodeParams p) {
+  using G = Geo<V, IB, FORM>;
+  constexpr int NW = G::NW, NT = G::NT, KS = G::KS, TK = G::TK, SLABB = G::SLABB, TB = G::TB, SU = G::SU;
+  constexpr int STAGE = G::STAGE, XR = G::XR, W64 = G::W64;
+  constexpr int ENTRY_LOG2 = (V == 4) ? 3 : 4;
+  constexpr int REP_LOG2 = REPL ? (7 - ENTRY_LOG2) : 0;  // replicas fill a 128-byte line, or none at all
+  constexpr int ENTRY_SHIFT = ENTRY_LOG2 + REP_LOG2;
+  constexpr int PIECES = TK / 64;                        // 64-K pieces per thread and unit
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ int s_last[kMaxBatch];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* smem = smem_raw + (base - smem_u32(smem_raw));
+
+  // the next kernel in the stream may be scheduled as soon as SMs have room (it waits as below before it
+  // touches anything this kernel reads or writes)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  // static contiguous partition of the items (chunk-major so X stays in registers); the host supplies
+  // quotient and remainder
+  const int bid = blockIdx.x;
+  int it0 = bid * p.items_q + min(bid, p.items_r);
+  int it1 = it0 + p.items_q + (bid < p.items_r ? 1 : 0);
+  if (it1 <= it0) return;
+  // items of one chunk this CTA walks: all of them (its range then runs over chunks and items, chunk-major), or
+  // its own range once per chunk
+  int div = p.nrbg, off = 0;
+  if (p.row_owned) {
+    off = it0;
+    div = it1 - it0;
+    it0 = 0;
+    it1 = div * p.nchunks;
+  }
+  const int nitems = it1 - it0;
+  const int r_end = off + div;
+
+  // warp role inside a chunk: (slice, row lane)
+  const int nsl_full = min(NW, p.nslices);
+  const int wsl = warp % nsl_full;
+  const int wrl = warp / nsl_full;
+  const bool role_ok = wrl < p.rl;
+  const int S = p.stages;
+  const uint32_t my_ring = base + static_cast<uint32_t>(warp * S) * STAGE;
+  const uint32_t my_bars = base + p.bar_offset + static_cast<uint32_t>(warp * S) * 8;
+
+  // ---- this warp's tile stream: requests run up to S tiles ahead of use -------------------------------
+  int p_left = nitems;            // items not yet looked at by the requester
+  int p_chunk = 0, p_rbg = off + it0;   // the next one
+  if (it0 >= div) {                     // only when (chunk, item) pairs are dealt out and this range starts in a later chunk
+    p_chunk = it0 / div;
+    p_rbg = it0 - p_chunk * div;
+  }
+  const int first_chunk = p_chunk, first_rbg = p_rbg;
+  int p_stage = 0, in_flight = 0;
+  auto request_tiles = [&]() {
+    while (p_left > 0 && in_flight < S) {
+      const int slice = p_chunk * NW + wsl;
+      if (role_ok && slice < p.nslices) {
+        if (lane == 0) {
+          const uint32_t bar = my_bars + p_stage * 8;
+          tc::mbar_expect_tx(bar, STAGE);
+          tc::tma_load_2d(my_ring + p_stage * STAGE, &idx_map, slice * SLABB, (p_rbg * p.rl + wrl) * (8 * SU), bar);
+        }
+        p_stage = (p_stage + 1 == S) ? 0 : p_stage + 1;
+        ++in_flight;
+      }
+      --p_left;
+      if (++p_rbg == r_end) { p_rbg = off; ++p_chunk; }
     }
-    if constexpr (FORM == 3) {
-      if (g + 8 >= p.M) {   // upper batch row absent: its registers were never written
+  };
+  if (lane == 0) {
+    for (int s = 0; s < S; ++s) tc::mbar_init(my_bars + s * 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  request_tiles();
+  int c_stage = 0;
+  uint32_t c_parity = 0;
+
+  const uint32_t img_bytes = static_cast<uint32_t>(p.C) << ENTRY_SHIFT;
+  // this lane's replica inside an image (32-bit shared address of slot 0)
+  const uint32_t img_lane = base + p.img_offset + ((lane & ((1 << REP_LOG2) - 1)) << ENTRY_LOG2);
+  uint32_t epoch = 0;
+  float* part = reinterpret_cast<float*>(smem + p.part_offset);       // [2][batch][NW][SU][M][8]
+  float* accbuf = reinterpret_cast<float*>(smem + p.acc_offset);      // [item - off][rl][SU][M][8], row-owned mode
+  const int item_floats = SU * p.M * 8;
+
+  // Builds the images of up to two groups (no barriers inside).  All global loads go out before the first
+  // store, so a build costs one round trip to memory.  Replicated image: a thread loads one entry and writes
+  // its copies, starting at a copy that depends on the entry so that a quarter warp's 16-byte stores fall into
+  // different banks.
+  using EntryT = typename std::conditional<V == 4, uint2, uint4>::type;
+  auto build_images = [&](int group_a, bool need_a, int group_b, bool need_b) {
+    unsigned char* img_a = smem + p.img_offset;
+    unsigned char* img_b = img_a + img_bytes;
+    const EntryT* src_a = reinterpret_cast<const EntryT*>(p.cb) + static_cast<size_t>(group_a) * p.C;
+    const EntryT* src_b = reinterpret_cast<const EntryT*>(p.cb) + static_cast<size_t>(group_b) * p.C;
+    if constexpr (REPL) {
+      auto put = [&](unsigned char* img, int c, const EntryT& e) {
+        uint4 q;
+        if constexpr (V == 4) q = make_uint4(e.x, e.y, e.x, e.y); else q = e;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) { xf[4 * i + 1] = 0; xf[4 * i + 3] = 0; }
+        for (int r = 0; r < 8; ++r) *reinterpret_cast<uint4*>(img + c * 128 + (((r + c) & 7) << 4)) = q;
+      };
+      for (int c = tid; c < p.C; c += NT) {
+        EntryT ea{}, eb{};
+        if (need_a) ea = __ldg(src_a + c);
+        if (need_b) eb = __ldg(src_b + c);
+        if (need_a) put(img_a, c, ea);
+        if (need_b) put(img_b, c, eb);
+      }
+    } else {
+      for (int pass = 0; pass < 2; ++pass) {
+        if (!(pass ? need_b : need_a)) continue;
+        const EntryT* src = pass ? src_b : src_a;
+        EntryT* img = reinterpret_cast<EntryT*>(pass ? img_b : img_a);
+        for (int c0 = 0; c0 < p.C; c0 += 8 * NT) {
+          EntryT e[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int c = c0 + j * NT + tid;
+            if (c < p.C) e[j] = __ldg(src + c);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int c = c0 + j * NT + tid;
+            if (c < p.C) img[c] = e[j];
+          }
+        }
       }
     }
-    __syncthreads();                                           // staging is free to become reduction buffers
   };
 
-  int it = it_begin;
-  Batch nb;
-  {
-    int chunk0 = 0, rbg0 = it;
-    if (p.row_owned) rbg0 = r_begin;
-    else while (rbg0 >= p.nrbg) { rbg0 -= p.nrbg; ++chunk0; }
-    const int group0 = rbg0 / p.ipg;
-    nb = make_batch(it, chunk0, rbg0, rbg0 - group0 * p.ipg, group0);
-  }
-  int parity = 0;
-  bool first_batch = true;
-
-  while (nb.cnt > 0) {
-    const Batch b = nb;
-    // all index loads of the batch go out first; everything up to the first lookup overlaps them
-    issue_loads(b, cur);
-    it += b.cnt;
-    {
-      int rbg = b.rbg + b.cnt, chunk = b.chunk, gpos = b.gpos + b.cnt, group = b.group;
-      while (gpos >= p.ipg) { gpos -= p.ipg; ++group; }
-      if (rbg >= r_end) { rbg = r_begin; group = r_begin / p.ipg; gpos = r_begin - group * p.ipg; ++chunk; }
-      nb = make_batch(it, chunk, rbg, gpos, group);
+  uint32_t xf[XR];
+  // X fragment registers of this thread for its quarter of the warp's slice in `chunk`, straight from global
+  // memory (L2) in register order.
+  auto load_x = [&](int chunk, bool active) {
+    const int kt = (chunk * NW + wsl) * KS + t4 * TK;
+    if constexpr (FORM == 1) {
+      // B fragment of column g = (batch row g/2, pair selector g%2): for each group q of 8 K values,
+      // register 0 = pair {0-1} or {2-3}, register 1 = pair {4-5} or {6-7}
+      const int m = g >> 1, h = g & 1;
+      const bool live = active && m < p.M;
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(p.x + static_cast<size_t>(live ? m : 0) * p.K + (live ? kt : 0)) + h;
+#pragma unroll
+      for (int q = 0; q < TK / 8; ++q) {
+        uint32_t v0 = 0u, v1 = 0u;
+        if (live) { v0 = __ldg(src + 4 * q); v1 = __ldg(src + 4 * q + 2); }
+        xf[2 * q] = v0;
+        xf[2 * q + 1] = v1;
+      }
+    } else {
+      // A fragment rows g (and g+8): 4 consecutive K values per MMA, so 16 bytes of a row are the row's registers
+      // of two MMAs, in order.  The warp reads its slice of eight batch rows with coalesced 16-byte loads (one
+      // row = 512 contiguous bytes per instruction), passes them through 4 KiB of its own in shared memory and
+      // every thread picks up the 128 bytes of row g that belong to its quarter of the slice.  Chunks of 16
+      // bytes are placed at (c & 7) ^ ((c >> 3) & 3) ^ ((row & 1) << 2) within their 128-byte line, which makes
+      // both the stores and the loads conflict-free.
+      const uint32_t sx = base + p.part_offset + warp * 4096;
+      const __half* xs = p.x + (chunk * NW + wsl) * KS + lane * 8;
+#pragma unroll
+      for (int pass = 0; pass < (FORM == 3 ? 2 : 1); ++pass) {
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = pass * 8 + i;
+          v[i] = make_uint4(0u, 0u, 0u, 0u);
+          if (active && r < p.M) v[i] = __ldg(reinterpret_cast<const uint4*>(xs + static_cast<size_t>(r) * p.K));
+        }
+        __syncwarp();   // the previous pass has been read
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t c = (lane & ~7u) | ((lane ^ (lane >> 3) ^ ((i & 1) << 2)) & 7u);
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sx + i * 512 + (c << 4)), "r"(v[i].x), "r"(v[i].y),
+                       "r"(v[i].z), "r"(v[i].w) : "memory");
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < TK / 8; ++j) {
+          const uint32_t lc = t4 * 8 + j;
+          const uint32_t c = (lc & ~7u) | ((lc ^ (lc >> 3) ^ ((g & 1) << 2)) & 7u);
+          const uint4 q = lds128_tile(sx + g * 512 + (c << 4));
+          if constexpr (FORM == 3) {
+            xf[8 * j + pass] = q.x; xf[8 * j + 2 + pass] = q.y; xf[8 * j + 4 + pass] = q.z; xf[8 * j + 6 + pass] = q.w;
+          } else {
+            xf[4 * j + 0] = q.x; xf[4 * j + 1] = q.y; xf[4 * j + 2] = q.z; xf[4 * j + 3] = q.w;
+          }
+        }
+      }
     }
+  };
 
-    const int g_first = b.group;
-    const int g_last = b.group + ((b.gpos + b.cnt - 1 >= p.ipg) ? 1 : 0);   // a batch touches at most two groups
+  int loaded_chunk = -1;
+  int slot_group0 = -1, slot_group1 = -1;   // which group each image slot holds
+  bool active = false;
+  bool first_batch = true;
+  int parity = 0;
+
+  int seq = 0;
+  int chunk = first_chunk;
+  int rbg = first_rbg;
+  while (seq < nitems) {
+    // ---- the batch: items [seq, seq + cnt) = row block groups [rbg, rbg + cnt) of `chunk` ----------------
+    const int group = rbg / p.ipg;
+    const int gpos = rbg - group * p.ipg;
+    int cnt = min(min(p.batch, nitems - seq), min(r_end - rbg, p.nslots * p.ipg - gpos));
+    const int g_first = group;
+    const int g_last = group + ((gpos + cnt - 1 >= p.ipg) ? 1 : 0);   // a batch touches at most two groups
     {
       const bool need0 = (p.nslots == 1) ? (slot_group0 != g_first)
                                          : ((((g_first & 1) == 0) && slot_group0 != g_first) ||
@@ -356,8 +417,9 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
                                              (((g_last & 1) == 1) && slot_group1 != g_last));
       if (need0 || need1) {
         if (!first_batch) __syncthreads();   // everyone is done looking up in the old images
-        if (need0) { slot_group0 = (p.nslots == 1 || (g_first & 1) == 0) ? g_first : g_last; build_image(slot_group0, 0); }
-        if (need1) { slot_group1 = ((g_first & 1) == 1) ? g_first : g_last; build_image(slot_group1, 1); }
+        if (need0) slot_group0 = (p.nslots == 1 || (g_first & 1) == 0) ? g_first : g_last;
+        if (need1) slot_group1 = ((g_first & 1) == 1) ? g_first : g_last;
+        build_images(need0 ? slot_group0 : 0, need0, need1 ? slot_group1 : 0, need1);
         __syncthreads();
         asm volatile("add.u32 %0, %0, 1;" : "+r"(epoch));
       }
@@ -367,94 +429,56 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
     // stream's order: when the launch was made with programmatic stream serialisation this kernel may have
     // started while its predecessor was still running, and waits here for it to complete.
     if (first_batch) asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (b.chunk != loaded_chunk) {
-      loaded_chunk = b.chunk;
-      active = role_ok && (b.chunk * kWarps + wsl) < p.nslices;
-      if constexpr (FORM == 1) {
-        // B fragment of column g = (batch row g/2, pair selector g%2): for each group q of 8 K values,
-        // register 0 = pair {0-1} or {2-3}, register 1 = pair {4-5} or {6-7}.  16 scattered 4-byte loads
-        // per thread are cheap enough here (M <= 4) and need no barrier.
-        const int m = g >> 1, h = g & 1;
-        const int kt = (b.chunk * kWarps + wsl) * kSliceK + t4 * 64;
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.x + static_cast<size_t>(m) * p.K + kt) + h;
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          uint32_t v0 = 0, v1 = 0;
-          if (active && m < p.M) { v0 = __ldg(src + 4 * q); v1 = __ldg(src + 4 * q + 2); }
-          xf[2 * q] = v0; xf[2 * q + 1] = v1;
-        }
-      } else {
-        load_x_fragments(b.chunk);
-      }
-    }
     first_batch = false;
-    float* rb = red + static_cast<size_t>(parity) * (kWarps * warp_stride);
+    if (chunk != loaded_chunk) {
+      // forms 2/3 pass X through the memory of the partial tiles: nobody may still be summing the last batch
+      if (FORM != 1 && loaded_chunk >= 0) __syncthreads();
+      active = role_ok && (chunk * NW + wsl) < p.nslices;
+      load_x(chunk, active);
+      if (FORM != 1) __syncthreads();   // ... and nobody writes partial tiles before every warp has its X
+      loaded_chunk = chunk;
+    }
+
+    float* pb = part + static_cast<size_t>(parity) * (p.batch * NW * item_floats);
     parity ^= 1;
-    float* mine = rb + warp * warp_stride;
-#pragma unroll
-    for (int s = 0; s < PFB; ++s) {
-      if (s < b.cnt) {
+    if (active) {
+      for (int s = 0; s < cnt; ++s) {
         // image of this item's group
-        const int grp = b.group + ((b.gpos + s >= p.ipg) ? 1 : 0);
+        const int grp = group + ((gpos + s >= p.ipg) ? 1 : 0);
         const uint32_t img_s = img_lane + ((p.nslots == 2 && (grp & 1)) ? img_bytes : 0u);
+        tc::mbar_wait(my_bars + c_stage * 8, c_parity, p.status, DS_TMA_FULL_TIMEOUT);
+        const uint32_t tile = my_ring + c_stage * STAGE;
+        float* mine = pb + static_cast<size_t>(s * NW + warp) * item_floats;
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          float acc[4] = {0.f, 0.f, 0.f, 0.f};
-          float acc2[4] = {0.f, 0.f, 0.f, 0.f};  // second, independent accumulation chain
-          if (active) {
-            const uint32_t* w = cur[s][u].w;
-            if constexpr (FORM == 1) {
-              if constexpr (V == 4) {
-                uint2 e[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) e[i] = lds64(img_s + (idx_at<IB>(w, i) << ENTRY_SHIFT), epoch);
-#pragma unroll
-                for (int q = 0; q < 8; ++q)
-                  mma_16816((q & 1) ? acc2 : acc, e[2 * q].x, e[2 * q].y, e[2 * q + 1].x, e[2 * q + 1].y, xf[2 * q], xf[2 * q + 1]);
-              } else {
-                uint4 e[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) e[i] = lds128(img_s + (idx_at<IB>(w, i) << ENTRY_SHIFT), epoch);
-#pragma unroll
-                for (int q = 0; q < 8; ++q) mma_16816((q & 1) ? acc2 : acc, e[q].x, e[q].y, e[q].z, e[q].w, xf[2 * q], xf[2 * q + 1]);
-              }
-            } else {
-              constexpr int XS = (FORM == 2) ? 2 : 4;
-              if constexpr (V == 4) {
-#pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {   // two halves of 8 lookups keep the register count down
-                  uint2 e[8];
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) e[i] = lds64(img_s + (idx_at<IB>(w, 8 * hf + i) << ENTRY_SHIFT), epoch);
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) {
-                    const int ii = 8 * hf + i;
-                    if constexpr (FORM == 2) mma_16816((i & 1) ? acc2 : acc, xf[XS * ii], 0u, xf[XS * ii + 1], 0u, e[i].x, e[i].y);
-                    else mma_16816((i & 1) ? acc2 : acc, xf[XS * ii], xf[XS * ii + 1], xf[XS * ii + 2], xf[XS * ii + 3], e[i].x, e[i].y);
-                  }
-                }
-              } else {
-                uint4 e[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) e[i] = lds128(img_s + (idx_at<IB>(w, i) << ENTRY_SHIFT), epoch);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  if constexpr (FORM == 2) {
-                    mma_16816(acc, xf[XS * 2 * i], 0u, xf[XS * 2 * i + 1], 0u, e[i].x, e[i].y);
-                    mma_16816(acc2, xf[XS * (2 * i + 1)], 0u, xf[XS * (2 * i + 1) + 1], 0u, e[i].z, e[i].w);
-                  } else {
-                    mma_16816(acc, xf[XS * 2 * i], xf[XS * 2 * i + 1], xf[XS * 2 * i + 2], xf[XS * 2 * i + 3], e[i].x, e[i].y);
-                    mma_16816(acc2, xf[XS * (2 * i + 1)], xf[XS * (2 * i + 1) + 1], xf[XS * (2 * i + 1) + 2],
-                              xf[XS * (2 * i + 1) + 3], e[i].z, e[i].w);
-                  }
-                }
-              }
-            }
+        for (int j = 0; j < SU; ++j) {
+          // this thread's TB index bytes of row r of the tile, through the tile's swizzle
+          uint32_t w[TB / 4];
+          const int r = j * 8 + g;
+          if constexpr (SLABB == 128) {
+            const uint32_t row = tile + r * 128;
+            const uint4 a = lds128_tile(row + (((2 * t4) ^ g) << 4));
+            const uint4 b = lds128_tile(row + (((2 * t4 + 1) ^ g) << 4));
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+          } else if constexpr (SLABB == 64) {
+            const uint4 a = lds128_tile(tile + r * 64 + ((t4 ^ ((g >> 1) & 3)) << 4));
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+          } else {
+            const uint2 a = lds64_tile(tile + r * 32 + (((t4 >> 1) ^ ((g >> 2) & 1)) << 4) + (t4 & 1) * 8);
+            w[0] = a.x; w[1] = a.y;
           }
+          float ch[4][4];   // four independent accumulation chains, summed in a fixed order
 #pragma unroll
-          for (int c = 0; c < 4; ++c) acc[c] += acc2[c];
+          for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) ch[a][c] = 0.f;
+#pragma unroll
+          for (int pc = 0; pc < PIECES; ++pc)
+            piece_mma<V, IB, FORM, ENTRY_SHIFT>(ch, w + pc * W64, xf + pc * (XR / PIECES), img_s, epoch);
+          float acc[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[c] = (ch[0][c] + ch[1][c]) + (ch[2][c] + ch[3][c]);
           // this warp's partial tile of the unit: [m][8 rows]
-          float* dst = mine + (s * 2 + u) * unit_floats;
+          float* dst = mine + j * p.M * 8;
           if constexpr (FORM == 1) {
             if (t4 < p.M) dst[t4 * 8 + g] = acc[0] + acc[3];
           } else {
@@ -463,80 +487,81 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
             if (FORM == 3 && g + 8 < p.M) *reinterpret_cast<float2*>(dst + (g + 8) * 8 + 2 * t4) = make_float2(acc[2], acc[3]);
           }
         }
+        // the tile has been read by every lane: its place in the ring takes the next request
+        __syncwarp();
+        --in_flight;
+        if (++c_stage == S) { c_stage = 0; c_parity ^= 1; }
+        request_tiles();
       }
+    } else {
+      // warps without a slice in this chunk (or without a row lane) still step the requester past the batch
+      request_tiles();
     }
     __syncthreads();
 
-    // fixed-order reduction over the slices of the chunk: `lpo` lanes per output, then a butterfly.
-    // Output o = ((s*rl + lr)*M + m)*16 + r; divisions by M and rl use host-made reciprocals
-    // (exact for the small ranges involved).
-    const int nsl = min(kWarps, p.nslices - b.chunk * kWarps);
-    const int outs = b.cnt * p.rl * p.M * 16;
-    const int q = tid & (p.lpo - 1);
-    const int outs_per_pass = kThreads >> p.lpo_log2;
+    // fixed-order sum over the slices of the chunk, one thread per output
+    const int nsl = min(NW, p.nslices - chunk * NW);
+    const int outs = cnt * p.rl * item_floats;
     const bool split = p.nchunks > 1 && !p.row_owned;
     const bool carry = p.nchunks > 1 && p.row_owned;   // running sums over the chunks in shared memory
-    for (int o0 = 0; o0 < outs; o0 += outs_per_pass) {
-      const int o = o0 + (tid >> p.lpo_log2);
+    for (int o = tid; o < outs; o += NT) {
+      // o = ((s * rl + lr) * SU + j) * M * 8 + m * 8 + r8, taken apart with host-made reciprocals
+      const int r8 = o & 7;
+      const int t = o >> 3;
+      const int tj = p.inv_m ? __umulhi(static_cast<unsigned>(t), p.inv_m) : t;   // t / M = (s * rl + lr) * SU + j
+      const int m = t - tj * p.M;
+      const int j = tj & (SU - 1);
+      const int tl = tj / SU;                                             // s * rl + lr
+      const int s = p.inv_rl ? __umulhi(static_cast<unsigned>(tl), p.inv_rl) : tl;
+      const int lr = tl - s * p.rl;
+      const int row = (((rbg + s) * p.rl + lr) * SU + j) * 8 + r8;
+      const float* src = pb + static_cast<size_t>(s * NW + lr * nsl_full) * item_floats + (j * p.M + m) * 8 + r8;
       float sum = 0.f;
-      int m = 0, row = 0;
-      const bool valid = o < outs;
-      if (valid) {
-        const int r = o & 15;                 // row inside the 16-row item: unit r>>3, row r&7
-        const int t = o >> 4;
-        const int t1 = (t * p.inv_m) >> 16;   // t / M
-        m = t - t1 * p.M;
-        const int s = (t1 * p.inv_rl) >> 16;  // t1 / rl
-        const int lr = t1 - s * p.rl;
-        row = ((b.rbg + s) * p.rl + lr) * 16 + r;
-        const float* src = rb + (lr * nsl_full) * warp_stride + (s * 2 + (r >> 3)) * unit_floats + m * 8 + (r & 7);
-        for (int sl = q; sl < nsl; sl += p.lpo) sum += src[sl * warp_stride];
+      if (nsl == NW) {
+#pragma unroll
+        for (int sl = 0; sl < NW; ++sl) sum += src[sl * item_floats];
+      } else {
+        for (int sl = 0; sl < nsl; ++sl) sum += src[sl * item_floats];
       }
-      for (int d = p.lpo >> 1; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
-      if (valid && q == 0 && carry) {
+      if (row >= p.N) continue;
+      if (carry) {
         // place of this output in the CTA's accumulator: the same for every chunk
-        float* a = accbuf + (static_cast<size_t>(row >> 4) - static_cast<size_t>(r_begin) * p.rl) * (p.M * 16) + m * 16 + (row & 15);
-        if (b.chunk > 0) sum += *a;
-        if (b.chunk + 1 < p.nchunks) {
-          *a = sum;
-        } else {
-          const __half h = __float2half_rn(sum);
-          const size_t o_off = static_cast<size_t>(m) * p.ld_y + row;
-          p.y[o_off] = h;
-          for (int pq = 0; pq < p.n_peers; ++pq) p.peer_y[pq][o_off] = h;
-        }
-      } else if (valid && q == 0) {
-        if (!split) {
-          const __half h = __float2half_rn(sum);
-          const size_t o_off = static_cast<size_t>(m) * p.ld_y + row;
-          p.y[o_off] = h;
-          for (int pq = 0; pq < p.n_peers; ++pq) p.peer_y[pq][o_off] = h;
-        } else {
-          __stcg(p.ws_partial + (static_cast<size_t>(b.chunk) * p.M + m) * p.N + row, sum);
-        }
+        float* a = accbuf + (static_cast<size_t>(rbg + s - off) * p.rl + lr) * item_floats + (j * p.M + m) * 8 + r8;
+        if (chunk > 0) sum += *a;
+        if (chunk + 1 < p.nchunks) { *a = sum; continue; }
+      } else if (split) {
+        __stcg(p.ws_partial + (static_cast<size_t>(chunk) * p.M + m) * p.N + row, sum);
+        continue;
       }
+      const __half h = __float2half_rn(sum);
+      const size_t o_off = static_cast<size_t>(m) * p.ld_y + row;
+      p.y[o_off] = h;
+      for (int pq = 0; pq < p.n_peers; ++pq) p.peer_y[pq][o_off] = h;
     }
     if (split) {
-      // split-K: the CTA that brings a row block's counter to nchunks sums the chunks in chunk order
+      // split-K: the CTA that brings an item's counter to nchunks sums the chunks in chunk order
       __threadfence();
       __syncthreads();
-      if (tid < b.cnt) {
-        const int old = atomicAdd(p.ws_counter + b.rbg + tid, 1);
+      if (tid < cnt) {
+        const int old = atomicAdd(p.ws_counter + rbg + tid, 1);
         const int last = (old == p.nchunks - 1);
-        if (last) p.ws_counter[b.rbg + tid] = 0;  // leave the counter zero for the next call
+        if (last) p.ws_counter[rbg + tid] = 0;  // leave the counter zero for the next call
         s_last[tid] = last;
       }
       __syncthreads();
       __threadfence();
-      for (int o = tid; o < outs; o += kThreads) {
-        const int r = o & 15;
-        const int t = o >> 4;
-        const int t1 = (t * p.inv_m) >> 16;
-        const int m = t - t1 * p.M;
-        const int s = (t1 * p.inv_rl) >> 16;
-        const int lr = t1 - s * p.rl;
+      for (int o = tid; o < outs; o += NT) {
+        const int r8 = o & 7;
+        const int t = o >> 3;
+        const int tj = p.inv_m ? __umulhi(static_cast<unsigned>(t), p.inv_m) : t;
+        const int m = t - tj * p.M;
+        const int j = tj & (SU - 1);
+        const int tl = tj / SU;
+        const int s = p.inv_rl ? __umulhi(static_cast<unsigned>(tl), p.inv_rl) : tl;
+        const int lr = tl - s * p.rl;
         if (!s_last[s]) continue;
-        const int row = ((b.rbg + s) * p.rl + lr) * 16 + r;
+        const int row = (((rbg + s) * p.rl + lr) * SU + j) * 8 + r8;
+        if (row >= p.N) continue;
         float sum = 0.f;
         for (int c = 0; c < p.nchunks; ++c)
           sum += __ldcg(p.ws_partial + (static_cast<size_t>(c) * p.M + m) * p.N + row);
@@ -547,6 +572,10 @@ __global__ void __launch_bounds__(kThreads, 1) vq_decode_kernel(const DecodePara
       }
       __syncthreads();  // s_last is rewritten by the next batch
     }
+
+    seq += cnt;
+    rbg += cnt;
+    if (rbg == r_end) { rbg = off; ++chunk; }
   }
 }
 
@@ -556,13 +585,27 @@ int pick_rep_log2(int v, int C, size_t budget) {
   return (static_cast<size_t>(C) * 2 * v << rep) <= budget ? rep : 0;
 }
 
-bool fill_params(const Problem& p, DecodeParams& d, size_t& smem_bytes) {
+int device_sms() {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms > 0 ? sms : 148;
+}
+
+struct Plan {
+  DecodeParams d;
+  int form, nw, ks, su, slabb, stage, rep_log2;
+  size_t smem;
+  int grid;
+  size_t ws_bytes;   // split-K scratch this plan needs (0 if none)
+};
+
+// Everything the launch needs except pointers into a workspace.  Returns false for shapes outside the kernel.
+bool make_plan(const Problem& p, Plan& pl) {
   if (p.M < 1 || p.M > 16) return false;
   if (!(p.v == 4 || p.v == 8)) return false;
   if (!(p.idx_bytes == 1 || (p.idx_bytes == 2 && p.v == 8))) return false;
-  if (p.K % kSliceK != 0 || p.N % 16 != 0 || p.K == 0 || p.N == 0) return false;
+  if (p.K % 256 != 0 || p.N % 8 != 0 || p.K == 0 || p.N == 0) return false;
   const bool single = p.rows_per_cb >= p.N;
-  if (!single && p.rows_per_cb % 16 != 0) return false;
   if (p.idx_bytes == 1 && p.C > 256) return false;
   if (p.C > 65536 || p.C < 1) return false;
   if (reinterpret_cast<uintptr_t>(p.x) % 16 || reinterpret_cast<uintptr_t>(p.idx) % 16 ||
@@ -570,134 +613,191 @@ bool fill_params(const Problem& p, DecodeParams& d, size_t& smem_bytes) {
     return false;
   const size_t entry = static_cast<size_t>(2) * p.v;
   if (p.C * entry > 160 * 1024) return false;
-  d.nslices = p.K / kSliceK;
-  d.nchunks = (d.nslices + kWarps - 1) / kWarps;
-  const int nsl_full = d.nslices < kWarps ? d.nslices : kWarps;
-  int rl = kWarps / nsl_full;
-  const int blocks_per_group = single ? (p.N / 16) : (p.rows_per_cb / 16);
-  while (rl > 1 && ((p.N / 16) % rl != 0 || blocks_per_group % rl != 0)) --rl;
+  DecodeParams& d = pl.d;
+  d = DecodeParams{};
+  // form 1 needs whole 512-wide slices; other K (multiples of 256) take the two-row-halves form, which holds M <= 8
+  pl.form = (p.M <= 4 && p.K % 512 == 0) ? 1 : (p.M <= 8 ? 2 : 3);
+  pl.nw = pl.form == 1 ? 8 : 16;
+  pl.ks = pl.form == 1 ? 512 : 256;
+  pl.slabb = pl.ks / p.v * p.idx_bytes;
+  pl.su = pl.slabb >= 128 ? 1 : 2;
+  pl.stage = 8 * pl.su * pl.slabb;
+  const int tile_rows = 8 * pl.su;
+  if (!single && p.rows_per_cb % tile_rows != 0) return false;
+  d.nslices = p.K / pl.ks;
+  d.nchunks = (d.nslices + pl.nw - 1) / pl.nw;
+  const int nsl_full = d.nslices < pl.nw ? d.nslices : pl.nw;
+  const int tiles = (p.N + tile_rows - 1) / tile_rows;
+  const int tiles_per_group = single ? tiles : (p.rows_per_cb / tile_rows);
+  int rl = pl.nw / nsl_full;
+  while (rl > 1 && (tiles % rl != 0 || tiles_per_group % rl != 0)) --rl;
   d.rl = rl;
-  d.nrbg = p.N / (16 * rl);
-  const int pfb = p.M <= 4 ? 6 : (p.M <= 8 ? (p.v == 8 ? 6 : 3) : (p.v == 8 ? 4 : 2));   // = PFB of the kernel
-  d.ipg = blocks_per_group / rl;
-  // lanes per output in the reduction: as many as keep all outputs of a batch in one pass
-  const int outs_max = pfb * rl * p.M * 16;
-  d.lpo = 1; d.lpo_log2 = 0;
-  while (d.lpo * 2 <= nsl_full && d.lpo < 8 && outs_max * d.lpo * 2 <= kThreads) { d.lpo *= 2; ++d.lpo_log2; }
-  d.inv_m = (65536 + p.M - 1) / p.M;
-  d.inv_rl = (65536 + rl - 1) / rl;
-  const size_t red_bytes = static_cast<size_t>(2) * kWarps * (pfb * 2 * p.M * 8 + 2) * sizeof(float);
-  const int xr = p.M <= 4 ? 16 : (p.M <= 8 ? 32 : 64);
-  const size_t stage_bytes = static_cast<size_t>(kWarps) * 32 * (xr + 4) * sizeof(uint32_t);
-  const size_t work_bytes = red_bytes > stage_bytes ? red_bytes : stage_bytes;
-  d.rep_log2 = pick_rep_log2(p.v, p.C, 64 * 1024);
-  const size_t img_bytes = static_cast<size_t>(p.C) * entry << d.rep_log2;
-  // a second resident image lets batches straddle a group boundary without a rebuild in between
-  d.nslots = (!single && 2 * img_bytes + work_bytes <= 210 * 1024) ? 2 : 1;
-  smem_bytes = d.nslots * img_bytes + work_bytes;
-  if (smem_bytes > 220 * 1024) return false;
-  d.x = p.x; d.idx = p.idx; d.cb = p.cb; d.y = p.y;
+  d.nrbg = tiles / rl;
+  d.ipg = tiles_per_group / rl;
+
+  const int sms = device_sms();
+  // what is dealt out over the CTAs: (chunk, item) pairs, or the items of one chunk in the row-owned mode.
+  // Row-owned walk of the K chunks: worth it when there are several chunks and enough items that an even split of
+  // them over the SMs is balanced (at least six per CTA), and when the running sums of a CTA's rows fit shared memory.
+  const int item_floats = pl.su * p.M * 8;
+  const size_t item_bytes = static_cast<size_t>(pl.nw) * item_floats * sizeof(float);   // partial tiles of one item
+  pl.rep_log2 = pick_rep_log2(p.v, p.C, 64 * 1024);
+  const size_t img_bytes = static_cast<size_t>(p.C) * entry << pl.rep_log2;
+  const size_t budget = pl.form == 1 ? 112 * 1024 : 220 * 1024;   // form 1: two launches side by side on an SM
+  d.nslots = (!single && 2 * img_bytes + 48 * 1024 <= budget) ? 2 : 1;
+  size_t acc_bytes = 0;
+  d.row_owned = 0;
+  if (d.nchunks > 1 && d.nrbg >= 6 * sms) {
+    const int per_cta = (d.nrbg + sms - 1) / sms;
+    const size_t need = static_cast<size_t>(per_cta) * rl * item_floats * sizeof(float);
+    if (need + d.nslots * img_bytes + 2 * item_bytes + static_cast<size_t>(pl.nw) * 2 * pl.stage + 4096 <= 220 * 1024) {
+      d.row_owned = 1;
+      acc_bytes = need;
+    }
+  }
+  const long long items = d.row_owned ? d.nrbg : static_cast<long long>(d.nchunks) * d.nrbg;
+  pl.grid = static_cast<int>(items < sms ? items : sms);
+  d.items_q = static_cast<int>(items / pl.grid);
+  d.items_r = static_cast<int>(items % pl.grid);
+  const int per_cta_items = d.items_q + (d.items_r ? 1 : 0);
+
+  // shared memory: images and running sums are fixed; the rest goes to reduction batches and tiles in flight
+  const size_t fixed = d.nslots * img_bytes + acc_bytes + static_cast<size_t>(pl.nw) * 8 * 8 + 2048;
+  if (fixed + 2 * item_bytes + static_cast<size_t>(pl.nw) * (2 * pl.stage + (pl.form != 1 ? 4096 : 0)) > 224 * 1024) return false;
+  const size_t total_budget =
+      (acc_bytes || fixed + 2 * item_bytes + static_cast<size_t>(pl.nw) * 2 * pl.stage > budget) ? 224 * 1024 : budget;
+  // batches of equal size: as few as kMaxBatch items per batch allow, within half of the memory that is left
+  int batch = per_cta_items < 1 ? 1 : per_cta_items;
+  for (int nb = 1; batch > kMaxBatch || (batch > 1 && 2 * batch * item_bytes > (total_budget - fixed) / 2); ++nb)
+    batch = (per_cta_items + nb) / (nb + 1);
+  if (batch < 1) batch = 1;
+  d.batch = batch;
+  size_t part_bytes = 2 * batch * item_bytes;
+  // forms 2/3 pass the X fragments through this memory, 4 KiB per warp
+  if (pl.form != 1 && part_bytes < static_cast<size_t>(pl.nw) * 4096) part_bytes = static_cast<size_t>(pl.nw) * 4096;
+  d.inv_m = p.M > 1 ? static_cast<unsigned>((0x100000000ULL + p.M - 1) / p.M) : 0u;
+  d.inv_rl = rl > 1 ? static_cast<unsigned>((0x100000000ULL + rl - 1) / rl) : 0u;
+  int stages = static_cast<int>((total_budget - fixed - part_bytes) / (static_cast<size_t>(pl.nw) * pl.stage));
+  if (stages > 8) stages = 8;
+  if (stages < 2) return false;
+  d.stages = stages;
+  const size_t ring = static_cast<size_t>(pl.nw) * stages * pl.stage;   // multiple of 1024 (nw*stage is)
+  d.bar_offset = static_cast<int>(ring);
+  d.img_offset = static_cast<int>((ring + static_cast<size_t>(pl.nw) * stages * 8 + 127) & ~static_cast<size_t>(127));
+  d.part_offset = static_cast<int>(d.img_offset + d.nslots * img_bytes);
+  d.acc_offset = static_cast<int>(d.part_offset + part_bytes);
+  pl.smem = d.acc_offset + acc_bytes + 1024;   // + alignment slack
+  if (pl.smem > 227 * 1024) return false;
+
+  pl.ws_bytes = 0;
+  if (d.nchunks > 1 && !d.row_owned) {
+    if (static_cast<size_t>(d.nrbg) * sizeof(int) > kCounterBytes) return false;
+    pl.ws_bytes = kCounterBytes + static_cast<size_t>(d.nchunks) * p.M * p.N * sizeof(float);
+  }
+  d.x = p.x; d.cb = p.cb; d.y = p.y;
   d.M = p.M; d.N = p.N; d.K = p.K; d.C = p.C;
-  d.rows_per_cb = single ? p.N : p.rows_per_cb;
   d.ld_y = p.ld_y;
   d.n_peers = p.n_peers;
   for (int i = 0; i < 8; ++i) d.peer_y[i] = p.peer_y[i];
   return true;
 }
 
-}  // namespace
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-bool decode_supported(const Problem& p) {
-  DecodeParams d{};
-  size_t smem;
-  return fill_params(p, d, smem);
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeFn>(f);
+  }();
+  return fn;
 }
 
-size_t decode_workspace_bytes(const Problem& p) {
-  DecodeParams d{};
-  size_t smem;
-  if (!fill_params(p, d, smem) || d.nchunks == 1) return 0;
-  return kCounterBytes + static_cast<size_t>(d.nchunks) * p.M * p.N * sizeof(float);
+// The index matrix as bytes [N][J * idx_bytes]; one box = one warp tile, swizzled over its row length.
+bool make_idx_map(CUtensorMap* map, const Problem& p, const Plan& pl) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(p.K / p.v) * p.idx_bytes;
+  const cuuint64_t dims[2] = {row_bytes, static_cast<cuuint64_t>(p.N)};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(pl.slabb), static_cast<cuuint32_t>(8 * pl.su)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle sw = pl.slabb == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                                : (pl.slabb == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(p.idx), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-namespace {
-int device_sms() {
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  return sms > 0 ? sms : 148;
-}
-// Row-owned walk of the K chunks (see DecodeParams::row_owned): worth it when there are several chunks and
-// enough row blocks that an even split of them over the SMs is balanced (at least six per CTA: measured 20 %
-// faster at 12 per CTA and K = 8192, but 12 % slower at 3.5 per CTA and K = 28672), and when the running sums of
-// a CTA's rows fit shared memory next to everything else.
-bool plan_row_owned(DecodeParams& d, size_t& smem, int M) {
-  if (d.nchunks <= 1) return false;
-  const int sms = device_sms();
-  if (d.nrbg < 6 * sms) return false;
-  const int per_cta = (d.nrbg + sms - 1) / sms;
-  const size_t acc_bytes = static_cast<size_t>(per_cta) * d.rl * M * 16 * sizeof(float);
-  const size_t off = (smem + 15) & ~static_cast<size_t>(15);
-  if (off + acc_bytes > 220 * 1024) return false;
-  d.row_owned = 1;
-  d.acc_offset = static_cast<int>(off);
-  smem = off + acc_bytes;
-  return true;
-}
-}  // namespace
+using KernelT = void (*)(const CUtensorMap, const DecodeParams);
 
-int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s) {
-  DecodeParams d{};
-  size_t smem;
-  if (!fill_params(p, d, smem)) return VQG_ERR_UNSUPPORTED;
-  const bool row_owned = plan_row_owned(d, smem, p.M);
-  if (d.nchunks > 1 && !row_owned) {
-    const size_t need = decode_workspace_bytes(p);
-    if (ws == nullptr || ws_bytes < need) return VQG_ERR_WORKSPACE;
-    if (static_cast<size_t>(d.nrbg) * sizeof(int) > kCounterBytes) return VQG_ERR_UNSUPPORTED;
-    d.ws_counter = static_cast<int*>(ws);
-    d.ws_partial = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + kCounterBytes);
-  }
-  d.status = device_status_ptr();
-
-  const int sms = device_sms();
-  // what is dealt out over the CTAs: (chunk, row block) items, or row blocks in the row-owned mode
-  const long long items = row_owned ? d.nrbg : static_cast<long long>(d.nchunks) * d.nrbg;
-  const int grid = static_cast<int>(items < sms ? items : sms);
-  d.items_q = static_cast<int>(items / grid);
-  d.items_r = static_cast<int>(items % grid);
-
-  const int form = p.M <= 4 ? 1 : (p.M <= 8 ? 2 : 3);
-  using KernelT = void (*)(const DecodeParams);
+KernelT pick_kernel(const Problem& p, const Plan& pl) {
   KernelT k = nullptr;
 #define VQG_PICK(V_, IB_)                                                                                \
   if (p.v == V_ && p.idx_bytes == IB_) {                                                                 \
-    if (d.rep_log2 > 0)                                                                                  \
-      k = form == 1 ? vq_decode_kernel<V_, IB_, 1, true>                                                 \
-                    : (form == 2 ? vq_decode_kernel<V_, IB_, 2, true> : vq_decode_kernel<V_, IB_, 3, true>); \
+    if (pl.rep_log2 > 0)                                                                                 \
+      k = pl.form == 1 ? vq_decode_kernel<V_, IB_, 1, true>                                              \
+                       : (pl.form == 2 ? vq_decode_kernel<V_, IB_, 2, true> : vq_decode_kernel<V_, IB_, 3, true>); \
     else                                                                                                 \
-      k = form == 1 ? vq_decode_kernel<V_, IB_, 1, false>                                                \
-                    : (form == 2 ? vq_decode_kernel<V_, IB_, 2, false> : vq_decode_kernel<V_, IB_, 3, false>); \
+      k = pl.form == 1 ? vq_decode_kernel<V_, IB_, 1, false>                                             \
+                       : (pl.form == 2 ? vq_decode_kernel<V_, IB_, 2, false> : vq_decode_kernel<V_, IB_, 3, false>); \
   }
   VQG_PICK(4, 1) VQG_PICK(8, 1) VQG_PICK(8, 2)
 #undef VQG_PICK
+  return k;
+}
+
+// One launch of the planned kernel; `dependent` adds programmatic stream serialisation (set-up, the codebook image
+// and the first index tiles of this launch overlap the tail of the kernel before it in the stream).
+int launch_planned(const Problem& p, Plan& pl, bool dependent, cudaStream_t s) {
+  CUtensorMap map;
+  if (!make_idx_map(&map, p, pl)) return VQG_ERR_LAUNCH;
+  KernelT k = pick_kernel(p, pl);
   if (!k) return VQG_ERR_UNSUPPORTED;
-  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pl.smem));
   if (e != cudaSuccess) return VQG_ERR_LAUNCH;
-  // Programmatic dependent launch: set-up, the codebook image and the first batch of index loads of this
-  // launch overlap the tail of the kernel before it in the stream (see the wait inside the kernel).
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(grid));
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = smem;
+  cfg.gridDim = dim3(static_cast<unsigned>(pl.grid));
+  cfg.blockDim = dim3(static_cast<unsigned>(pl.nw * 32));
+  cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, k, d);
+  cfg.numAttrs = dependent ? 1 : 0;
+  e = cudaLaunchKernelEx(&cfg, k, map, pl.d);
   count_launch();
   return cuda_status(e == cudaSuccess ? cudaGetLastError() : e);
+}
+
+}  // namespace
+
+bool decode_supported(const Problem& p) {
+  Plan pl;
+  return make_plan(p, pl);
+}
+
+size_t decode_workspace_bytes(const Problem& p) {
+  Plan pl;
+  return make_plan(p, pl) ? pl.ws_bytes : 0;
+}
+
+int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s) {
+  Plan pl;
+  if (!make_plan(p, pl)) return VQG_ERR_UNSUPPORTED;
+  if (pl.ws_bytes) {
+    if (ws == nullptr || ws_bytes < pl.ws_bytes) return VQG_ERR_WORKSPACE;
+    pl.d.ws_counter = static_cast<int*>(ws);
+    pl.d.ws_partial = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + kCounterBytes);
+  }
+  pl.d.status = device_status_ptr();
+  return launch_planned(p, pl, /*dependent=*/true, s);
 }
 
 
@@ -717,7 +817,8 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 std::mutex g_static_mu;
 unsigned char* g_static_ptr[64] = {};
 
-// Device address of the static scratch on the current device; looked up on the first call per device.
+// Device address of the static scratch on the current device; looked up on the first call per device.  That
+// first lookup is also what makes the CUDA runtime load this module onto the device, array included.
 int static_scratch_ptr(unsigned char** out) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return VQG_ERR_NO_DEVICE;
@@ -726,6 +827,10 @@ int static_scratch_ptr(unsigned char** out) {
   if (!g_static_ptr[dev]) {
     unsigned char* ptr = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
+    if (e == cudaErrorMemoryAllocation) {
+      cudaGetLastError();
+      return VQG_ERR_NO_MEMORY;
+    }
     if (e != cudaSuccess || ptr == nullptr) return VQG_ERR_LAUNCH;
     g_static_ptr[dev] = ptr;
   }
@@ -735,50 +840,21 @@ int static_scratch_ptr(unsigned char** out) {
 }  // namespace
 
 int launch_decode_static(const Problem& p, cudaStream_t s) {
-  DecodeParams d{};
-  size_t smem;
-  if (!fill_params(p, d, smem)) return VQG_ERR_UNSUPPORTED;
-  const size_t need = d.nchunks > 1 ? kCounterBytes + static_cast<size_t>(d.nchunks) * p.M * p.N * sizeof(float) : 0;
-  if (need > kStaticScratchBytes) return VQG_ERR_TOO_LARGE;
-  if (static_cast<size_t>(d.nrbg) * sizeof(int) > kCounterBytes) return VQG_ERR_TOO_LARGE;
+  Plan pl;
+  if (!make_plan(p, pl)) return VQG_ERR_UNSUPPORTED;
+  if (pl.ws_bytes > kStaticScratchBytes) return VQG_ERR_TOO_LARGE;
   unsigned char* scratch = nullptr;
   const int st = static_scratch_ptr(&scratch);
   if (st != VQG_OK) return st;
-  if (d.nchunks > 1) {
+  if (ensure_status_word() != cudaSuccess) return VQG_ERR_NO_DEVICE;
+  if (pl.ws_bytes) {
     // the array keeps whatever the previous call left: the arrival counters must start at zero
-    if (cudaMemsetAsync(scratch, 0, static_cast<size_t>(d.nrbg) * sizeof(int), s) != cudaSuccess) return VQG_ERR_LAUNCH;
-    d.ws_counter = reinterpret_cast<int*>(scratch);
-    d.ws_partial = reinterpret_cast<float*>(scratch + kCounterBytes);
+    if (cudaMemsetAsync(scratch, 0, static_cast<size_t>(pl.d.nrbg) * sizeof(int), s) != cudaSuccess) return VQG_ERR_LAUNCH;
+    pl.d.ws_counter = reinterpret_cast<int*>(scratch);
+    pl.d.ws_partial = reinterpret_cast<float*>(scratch + kCounterBytes);
   }
-  d.status = nullptr;
-
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const long long items = static_cast<long long>(d.nchunks) * d.nrbg;
-  const int grid = static_cast<int>(items < sms ? items : sms);
-  d.items_q = static_cast<int>(items / grid);
-  d.items_r = static_cast<int>(items % grid);
-  const int form = p.M <= 4 ? 1 : (p.M <= 8 ? 2 : 3);
-  using KernelT = void (*)(const DecodeParams);
-  KernelT k = nullptr;
-#define VQG_PICK(V_, IB_)                                                                                \
-  if (p.v == V_ && p.idx_bytes == IB_) {                                                                 \
-    if (d.rep_log2 > 0)                                                                                  \
-      k = form == 1 ? vq_decode_kernel<V_, IB_, 1, true>                                                 \
-                    : (form == 2 ? vq_decode_kernel<V_, IB_, 2, true> : vq_decode_kernel<V_, IB_, 3, true>); \
-    else                                                                                                 \
-      k = form == 1 ? vq_decode_kernel<V_, IB_, 1, false>                                                \
-                    : (form == 2 ? vq_decode_kernel<V_, IB_, 2, false> : vq_decode_kernel<V_, IB_, 3, false>); \
-  }
-  VQG_PICK(4, 1) VQG_PICK(8, 1) VQG_PICK(8, 2)
-#undef VQG_PICK
-  if (!k) return VQG_ERR_UNSUPPORTED;
-  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
-    return VQG_ERR_LAUNCH;
-  k<<<grid, kThreads, smem, s>>>(d);
-  count_launch();
-  return cuda_status(cudaGetLastError());
+  pl.d.status = device_status_ptr();
+  return launch_planned(p, pl, /*dependent=*/false, s);
 }
 
 }  // namespace vqg

@@ -102,6 +102,11 @@ __global__ void __launch_bounds__(256) dequant_bl_fast_kernel(const IdxT* __rest
 int launch_dequant_bl(const void* idx, const __half* cb, __half* w, int N, int K, int v, int C,
                       int idx_bytes, int rows_per_cb, cudaStream_t s) {
   if (N == 0 || K == 0) return VQG_OK;
+  // the kernels read a codebook entry (2v bytes) and write it with one access, and read indices by their own width
+  const uintptr_t entry = static_cast<uintptr_t>(2) * static_cast<uintptr_t>(v > 0 ? v : 1);
+  if (reinterpret_cast<uintptr_t>(cb) % entry || reinterpret_cast<uintptr_t>(w) % entry ||
+      reinterpret_cast<uintptr_t>(idx) % static_cast<uintptr_t>(idx_bytes > 0 ? idx_bytes : 1))
+    return VQG_ERR_BAD_ARG;
   const bool single = rows_per_cb >= N;
   int rpb = (single || rows_per_cb % 16 == 0) ? 16 : 1;
   // fewer, larger blocks for large matrices (the codebook is staged once per block)

@@ -577,7 +577,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5_mlp70b")
-    ap.add_argument("--mode", default="peer", choices=["peer", "nccl"], help="how the N-sharded output is assembled")
+    ap.add_argument("--mode", default="auto", choices=["auto", "peer", "multicast", "nccl"],
+                    help="how the N-sharded output is assembled (auto: the faster of peer stores and multimem stores)")
     ap.add_argument("--no-shapes", action="store_true", help="skip the per-configuration table")
     ap.add_argument("--no-mlp", action="store_true", help="skip the tensor-parallel MLP measurement")
     ap.add_argument("--no-baselines", action="store_true",
@@ -628,21 +629,50 @@ def main():
     x_h, idx_h, cb_h = make_inputs(shape, seed=0, n_rows=n_local if rpc > 0 else None, row0=row0)
     x_h, idx_h, cb_h = x_h.pin_memory(), idx_h.pin_memory(), cb_h.pin_memory()
     x, idx, cb = x_h.to(dev), idx_h.to(dev), cb_h.to(dev)
-    # peer mode needs symmetric memory; if it cannot be set up on this box every rank falls back to NCCL together
-    mode = args.mode
-    try:
-        op = ShardedVQGemm(shape.M, shape.N, mode=mode, device=dev)
-        failed = 0
-    except Exception as e:  # noqa: BLE001
-        op, failed = None, 1
-        print(f"rank {rank}: {mode} mode unavailable ({e!r})", file=sys.stderr)
-    if world > 1:
-        t = torch.tensor([failed], device=dev)
+    # How Y is assembled.  Every rank first finds out LOCALLY whether symmetric memory can be had at all, the
+    # ranks agree on that (a rank that fails inside a collective constructor would leave the others waiting in
+    # it), and only then build -- all in the same mode.  "auto": multimem stores through the switch where the
+    # fabric has a multicast mapping, timed against plain peer stores, the faster one kept.
+    def agree(flag_ok: bool) -> bool:
+        if world == 1:
+            return flag_ok
+        t = torch.tensor([0 if flag_ok else 1], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        failed = int(t.item())
-    if failed:
-        mode = "nccl"
-        op = ShardedVQGemm(shape.M, shape.N, mode=mode, device=dev)
+        return int(t.item()) == 0
+
+    mode = args.mode
+    gather_modes = {}
+    if world > 1 and mode != "nccl":
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            probe = symm_mem.empty(1024, dtype=torch.float16, device=dev)
+            local_ok = True
+            del probe
+        except Exception as e:  # noqa: BLE001
+            local_ok = False
+            print(f"rank {rank}: symmetric memory unavailable ({e!r})", file=sys.stderr)
+        if not agree(local_ok):
+            mode = "nccl"
+    if world > 1 and mode in ("auto", "multicast"):
+        from vq_gemm_b200.sharded import multicast_available
+        has_mc = agree(multicast_available(dev))
+        if mode == "multicast" and not has_mc:
+            mode = "peer"
+        if mode == "auto":
+            mode = "peer"
+            if has_mc:
+                # a short trial of both: 10 timed steps each after 3 warm-up steps, max over ranks
+                for cand in ("peer", "multicast"):
+                    trial = ShardedVQGemm(shape.M, shape.N, mode=cand, device=dev)
+                    tms = _time_loop(lambda: trial(x, idx, cb, rpc), 10, 3, barrier)
+                    tt = torch.tensor([tms], device=dev, dtype=torch.float64)
+                    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                    gather_modes[cand] = float(tt.item())
+                    del trial
+                mode = min(gather_modes, key=gather_modes.get)
+    if world == 1 and mode == "auto":
+        mode = "peer"
+    op = ShardedVQGemm(shape.M, shape.N, mode=mode, device=dev)
 
     # clock warm-up: the SM clock idles at a few hundred MHz
     a = torch.randn(4096, 4096, device=dev, dtype=torch.float16)
@@ -685,9 +715,15 @@ def main():
         # streams (copy-in, compute, copy-out) over double-buffered device inputs and outputs, so step i+1's
         # input copy and step i-1's output copy overlap step i's kernel.  Every step still moves all of its
         # inputs (X, indices, codebooks) from pinned host memory and its output block back to pinned memory.
+        # With G ranks on one host every rank copies only its M/G rows of X in and the ranks all-gather X over
+        # NVLink (ShardedVQGemm.gather_x), so the host link carries X once per step, not G times.
         ops = [op, ShardedVQGemm(shape.M, shape.N, mode=mode, device=dev)]
         y_h = [torch.empty((shape.M, n_local), dtype=torch.float16).pin_memory() for _ in range(2)]
         ins = [(torch.empty_like(x), torch.empty_like(idx), torch.empty_like(cb)) for _ in range(2)]
+        shard_x = world > 1 and shape.M % world == 0
+        m_rows = shape.M // world if shard_x else shape.M
+        xr_h = x_h[rank * m_rows:(rank + 1) * m_rows] if shard_x else x_h     # a view of the pinned X
+        xr = [torch.empty((m_rows, shape.K), dtype=torch.float16, device=dev) for _ in range(2)]
         s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         cur = torch.cuda.current_stream(dev)
         in_ready = [torch.cuda.Event() for _ in range(2)]
@@ -704,13 +740,15 @@ def main():
                 with torch.cuda.stream(s_in):
                     if i >= 2:
                         s_in.wait_event(comp_done[b])       # the kernel two steps back has read these buffers
-                    ins[b][0].copy_(x_h, non_blocking=True)
+                    (xr[b] if shard_x else ins[b][0]).copy_(xr_h, non_blocking=True)
                     ins[b][1].copy_(idx_h, non_blocking=True)
                     ins[b][2].copy_(cb_h, non_blocking=True)
                     in_ready[b].record(s_in)
                 cur.wait_event(in_ready[b])
                 if i >= 2:
                     cur.wait_event(out_free[b])             # its previous output has left the device
+                if shard_x:
+                    ops[b].gather_x(xr[b], out=ins[b][0])
                 y = ops[b](ins[b][0], ins[b][1], ins[b][2], rpc)
                 comp_done[b].record(cur)
                 with torch.cuda.stream(s_out):
@@ -735,6 +773,54 @@ def main():
         ems = e0.elapsed_time(e1) / e2e_steps
     status = V.device_status()
 
+    multi = None
+    if world > 1:
+        multi = {"gather_modes_trial_ms": gather_modes or None}
+        # NVLink rate of this box: every rank reads 100 MB from its right neighbour's symmetric buffer at the same
+        # time (plain copy-engine peer copy), max time over ranks
+        try:
+            hdl = op._hdl
+            nelem = 50_000_000
+            peer = hdl.get_buffer((rank + 1) % world, (nelem,), torch.float16, 0)
+            dst = torch.empty(nelem, dtype=torch.float16, device=dev)
+            for _ in range(2):
+                dst.copy_(peer)
+            torch.cuda.synchronize(); dist.barrier()
+            e0, e1 = _events()
+            e0.record()
+            for _ in range(5):
+                dst.copy_(peer)
+            e1.record()
+            torch.cuda.synchronize()
+            tt = torch.tensor([e0.elapsed_time(e1) / 5], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            multi["link_gbs"] = nelem * 2 / float(tt.item()) / 1e6
+            del dst, peer
+        except Exception as e:  # noqa: BLE001
+            multi["link_gbs"] = None
+            multi["link_error"] = repr(e)
+        # correctness of the gathered Y on every rank: bit for bit against the NCCL all-gather of the same blocks,
+        # and this rank's own columns against the CPU oracle on a seeded 64 x 1028 subset
+        try:
+            from oracle import vq_oracle as O
+            y_fused = op(x, idx, cb, rpc).clone()
+            ref_op = ShardedVQGemm(shape.M, shape.N, mode="nccl", device=dev)
+            y_nccl = ref_op(x, idx, cb, rpc)
+            torch.cuda.synchronize()
+            same = bool(torch.equal(y_fused.view(torch.int16), y_nccl.view(torch.int16)))
+            g = torch.Generator().manual_seed(1 + rank)
+            rows = torch.randperm(shape.M, generator=g)[:64].sort().values
+            cols = torch.cat([torch.randperm(n_local, generator=g)[:1024], torch.tensor([0, 127, 128, n_local - 1])]).unique()
+            sub = O.vq_gemm_bl_rows(x_h, idx_h, cb_h, rpc, rows, cols)
+            got = y_fused[:, row0:row0 + n_local].cpu()[rows][:, cols]
+            tol = O.check_tolerance(got, sub)["ok"]
+            okt = torch.tensor([1 if (same and tol) else 0], device=dev)
+            dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+            multi["gather_check"] = "bitwise+oracle ok" if int(okt.item()) == 1 else f"FAILED (rank {rank}: bitwise={same} oracle={tol})"
+            del ref_op, y_nccl, y_fused
+        except Exception as e:  # noqa: BLE001
+            multi["gather_check"] = "error: " + repr(e)
+
     def reduce_max(v):
         if world == 1:
             return v
@@ -743,7 +829,7 @@ def main():
         return float(t.item())
 
     ms, kms, ems = reduce_max(ms), reduce_max(kms), reduce_max(ems)
-    h2d = x_h.numel() * 2 + idx_h.numel() * idx_h.element_size() + cb_h.numel() * 2
+    h2d = xr_h.numel() * 2 + idx_h.numel() * idx_h.element_size() + cb_h.numel() * 2
     d2h = y_h[0].numel() * 2
     flops = shape.flops
     kflops = 2.0 * shape.M * n_local * shape.K
@@ -773,13 +859,25 @@ def main():
                    "l2": "working set (indices + X + Y = 180 MB) larger than the 126 MB L2"},
         "e2e": {"value": flops / ems / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ems, "steps": e2e_steps,
-                "pipeline": "3 streams, double-buffered; every step copies X + indices + codebooks in and its Y block out"},
+                "pipeline": "3 streams, double-buffered; every step copies X" + (" (this rank's M/G rows, then all-gathered over NVLink)" if world > 1 else "")
+                            + " + indices + codebooks in and its Y block out"},
         "gpu_launches": int(launches),
         "host_issue_ms_per_step": host_issue_ms,
         "roofline": roof,
         "clocks": clocks.summary(),
         "device_status": status,
     }
+    if multi is not None:
+        # what the link allows: every rank must RECEIVE (G-1)/G of Y while it computes its block
+        ingress = shape.M * (shape.N - n_local) * 2
+        multi["ingress_bytes_per_gpu"] = ingress
+        if multi.get("link_gbs"):
+            multi["ingress_ms_at_link"] = ingress / multi["link_gbs"] / 1e6
+            multi["step_lower_bound_ms"] = max(kms, multi["ingress_ms_at_link"])
+            multi["step_over_bound"] = ms / multi["step_lower_bound_ms"]
+        multi["kernel_alone_ms"] = kms
+        multi["exposed_gather_ms"] = ms - kms
+        line["multi_gpu"] = multi
     if not args.no_mlp:
         try:
             mlp = _mlp(V, world, rank, dev, args.steps, args.warmup, barrier, reduce_max)

@@ -134,6 +134,30 @@ VQG_API int vqg_gemm_sharded(const void* x, const void* idx, const void* codeboo
                      int M, int N_local, int K, int v, int C, int idx_bytes, int rows_per_codebook,
                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same product with the gather done by the NVLink switch: y_multicast is the multicast (NVLS) address of
+ * the ranks' Y buffers -- a mapping through which one store lands in every rank's buffer at the same offset,
+ * this rank's included (cuMulticast* objects; torch's symmetric memory exposes it as `multicast_ptr`).  For
+ * shapes that run the prefill kernel the epilogue then issues ONE 16-byte multimem store per 16 bytes of
+ * output instead of one store per rank: a rank's block leaves over NVLink once and the switch replicates it.
+ * Other shapes, y_multicast == NULL and nranks == 1 behave exactly like vqg_gemm_sharded.  No reference
+ * counterpart.  Every rank of the multicast group must stay alive while the mapping is bound. */
+VQG_API int vqg_gemm_sharded_mc(const void* x, const void* idx, const void* codebook,
+                        void* const* y_peers, void* y_multicast, int rank, int nranks,
+                        int M, int N_local, int K, int v, int C, int idx_bytes, int rows_per_codebook,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* Barrier across the ranks of a sharded product, to be enqueued after vqg_gemm_sharded* (or
+ * vqg_gemm_rowparallel) on the same stream: when it completes on a rank, every rank's stores into this rank's
+ * buffers have landed.  flag_ptrs[r] (HOST array of nranks DEVICE pointers) is rank r's flag array: nranks
+ * 32-bit words in peer-mapped memory, zero when first used, never reset; flag_ptrs[rank] is local.  `epoch`
+ * is the number of this barrier: 1 for the first, one more for each following barrier on these flags, the
+ * same on every rank.  The wait is bounded: if a rank has not arrived after limit_cycles SM cycles
+ * (1e3 .. 2e10) the kernel records code 11 in the device status word and returns -- vqg_device_status() then
+ * reports VQG_ERR_DEVICE_TIMEOUT and the device stays usable.  Plain system-scope stores and loads over
+ * NVLink; no multicast.  No reference counterpart (the reference is single-GPU, strategy_1/src.cu:343). */
+VQG_API int vqg_rank_barrier(void* const* flag_ptrs, int rank, int nranks, unsigned epoch,
+                     long long limit_cycles, void* stream);
+
 /* Small-batch product (M <= 16) for callers that must not allocate device memory.  (This entry
  * point has no counterpart in the reference.)
  *

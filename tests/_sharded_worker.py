@@ -45,6 +45,13 @@ def main():
     if os.environ.get("VQG_WORKER_MODE") == "rowparallel":
         ok = rowparallel(rank, world, dev)
         cases = []
+    modes = ["peer", "nccl"]
+    if cases and os.environ.get("VQG_WORKER_MULTICAST") == "1":
+        from vq_gemm_b200.sharded import multicast_available
+        if multicast_available(dev):
+            modes.append("multicast")
+            if rank == 0:
+                print("MULTICAST_TESTED", flush=True)
     for (M, K, N, v, C, rpc) in cases:
         x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=5)
         # the single-GPU result, block by block: a block computed alone has the same shape, hence the same
@@ -56,7 +63,7 @@ def main():
             blocks.append(V.vq_gemm(x.to(dev), idx_r.to(dev), cb_r.to(dev), rows_per_codebook=rpc, layout="bl"))
         single = torch.cat(blocks, dim=1)
         idx_l, cb_l = shard_weights(idx, cb, world, rank, rpc)
-        for mode in ("peer", "nccl"):
+        for mode in modes:
             op = ShardedVQGemm(M, N, mode=mode, device=dev)
             for _ in range(3):
                 y = op(x.to(dev), idx_l.to(dev), cb_l.to(dev), rpc)

@@ -57,6 +57,19 @@ def test_column_block_with_leading_dimension():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_ranks_gather_through_the_switch_equals_single_gpu():
+    # the multimem-store epilogue (NVLS multicast mapping of the symmetric buffers), where the fabric offers it;
+    # both ranks run to the end (a rank must not leave while its memory is bound to the multicast object)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", VQG_WORKER_MULTICAST="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29513", os.path.join(ROOT, "tests", "_sharded_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert p.returncode == 0 and "SHARDED_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+    if "MULTICAST_TESTED" not in p.stdout:
+        pytest.skip("no multicast mapping on this machine: only the peer-store and NCCL modes ran")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_two_ranks_equal_single_gpu():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",

@@ -127,3 +127,54 @@ def test_two_rank_row_parallel_reduce_scatter():
     for p in procs:
         p.join(timeout=60)
     assert res == [(0, True), (1, True)]
+
+
+def _barrier_protocol_worker(rank, world, port, leave_after, q):
+    """The epoch-flag protocol of vqg_rank_barrier restated on the host with the process group's store standing in
+    for the peer-mapped flag words: arrive = write my epoch into slot `rank` of every other rank's array, wait =
+    until every slot of my own array has reached the epoch, bounded in time.  Rank 1 leaves between two steps
+    (none of its work in flight); rank 0's next wait runs out, turns into a status code and rank 0 carries on."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    store = dist.distributed_c10d._get_default_store()
+    x, idx, cb = O.make_bl_inputs(3, 64, 256, 4, 256, 128, seed=19)
+    idx_l, cb_l = shard_weights(idx, cb, world, rank, 128)
+    status, log = 0, []
+    for epoch in range(1, 5):
+        if rank != 0 and epoch > leave_after:
+            break                                                   # this rank is gone before step `epoch` starts
+        block = O.vq_gemm_bl(x, idx_l, cb_l, 128)                   # the step's work (stand-in for the kernel)
+        for r in range(world):
+            if r != rank:
+                store.set(f"flag/{r}/{rank}/{epoch}", "1")          # arrival at barrier `epoch` in r's array, slot `rank`
+        ok = True
+        for r in range(world):
+            if r != rank:
+                try:
+                    store.wait([f"flag/{rank}/{r}/{epoch}"], datetime.timedelta(seconds=1.0))
+                except Exception:                                   # the bounded wait ran out
+                    ok = False
+                    status = 11                                     # DS_RANK_BARRIER_TIMEOUT
+        log.append((epoch, ok, tuple(block.shape)))
+    q.put((rank, status, log))
+    # no collective at the end: a rank that left cannot take part in one
+    dist.destroy_process_group()
+
+
+def test_barrier_protocol_when_a_rank_leaves_between_steps():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_barrier_protocol_worker, args=(r, 2, port, 2, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {r: (st, log) for r, st, log in (q.get(timeout=120) for _ in procs)}
+    for p in procs:
+        p.join(timeout=60)
+    st0, log0 = res[0]
+    st1, log1 = res[1]
+    assert [e for e, ok, _ in log1] == [1, 2] and all(ok for _, ok, _ in log1) and st1 == 0
+    assert [ok for _, ok, _ in log0] == [True, True, False, False]   # steps 3 and 4: the other rank never arrives
+    assert st0 == 11 and len(log0) == 4                              # rank 0 noticed and still finished every step

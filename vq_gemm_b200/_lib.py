@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_int, c_longlong, c_size_t, c_ulonglong, c_void_p, POINTER
+from ctypes import c_char_p, c_int, c_longlong, c_size_t, c_uint, c_ulonglong, c_void_p, POINTER
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libvqg_b200.so")
@@ -30,6 +30,9 @@ SIGNATURES = {
     "vqg_dense_workspace_bytes": (c_size_t, [c_int] * 4),
     "vqg_gemm_sharded": (c_int, [c_void_p] * 3 + [POINTER(c_void_p), c_int, c_int] + [c_int] * 7
                          + [c_void_p, c_size_t, c_void_p]),
+    "vqg_gemm_sharded_mc": (c_int, [c_void_p] * 3 + [POINTER(c_void_p), c_void_p, c_int, c_int] + [c_int] * 7
+                            + [c_void_p, c_size_t, c_void_p]),
+    "vqg_rank_barrier": (c_int, [POINTER(c_void_p), c_int, c_int, c_uint, c_longlong, c_void_p]),
     "vqg_swiglu_workspace_bytes": (c_size_t, [c_int] * 7),
     "vqg_gemm_swiglu": (c_int, [c_void_p] * 4 + [c_int] * 7 + [c_void_p, c_size_t, c_void_p]),
     "vqg_rowparallel_workspace_bytes": (c_size_t, [c_int] * 7),

@@ -263,7 +263,28 @@ int vqg_dense_gemm(const void* x, const void* w, void* y, int M, int N, int K, i
 int vqg_gemm_sharded(const void* x, const void* idx, const void* codebook, void* const* y_peers, int rank,
                      int nranks, int M, int N_local, int K, int v, int C, int idx_bytes, int rows_per_codebook,
                      void* workspace, size_t workspace_bytes, void* stream) {
+  return vqg_gemm_sharded_mc(x, idx, codebook, y_peers, nullptr, rank, nranks, M, N_local, K, v, C, idx_bytes,
+                             rows_per_codebook, workspace, workspace_bytes, stream);
+}
+
+int vqg_rank_barrier(void* const* flag_ptrs, int rank, int nranks, unsigned epoch, long long limit_cycles, void* stream) {
+  if (nranks < 1 || nranks > 8 || rank < 0 || rank >= nranks || !flag_ptrs) return VQG_ERR_BAD_ARG;
+  if (limit_cycles < 1000 || limit_cycles > 20000000000LL) return VQG_ERR_BAD_ARG;   // at most about ten seconds
+  unsigned* f[8] = {};
+  for (int r = 0; r < nranks; ++r) {
+    if (!flag_ptrs[r] || !aligned(flag_ptrs[r], 4)) return VQG_ERR_BAD_ARG;
+    f[r] = static_cast<unsigned*>(flag_ptrs[r]);
+  }
+  if (nranks == 1) return VQG_OK;
+  if (ensure_status_word() != cudaSuccess) return VQG_ERR_NO_DEVICE;
+  return launch_rank_barrier(f, rank, nranks, epoch, limit_cycles, static_cast<cudaStream_t>(stream));
+}
+
+int vqg_gemm_sharded_mc(const void* x, const void* idx, const void* codebook, void* const* y_peers, void* y_multicast,
+                        int rank, int nranks, int M, int N_local, int K, int v, int C, int idx_bytes,
+                        int rows_per_codebook, void* workspace, size_t workspace_bytes, void* stream) {
   if (nranks < 1 || nranks > 8 || rank < 0 || rank >= nranks || !y_peers) return VQG_ERR_BAD_ARG;
+  if (y_multicast && !aligned(y_multicast, 16)) return VQG_ERR_BAD_ARG;
   for (int r = 0; r < nranks; ++r)
     if (!y_peers[r]) return VQG_ERR_BAD_ARG;
   const long long ld = static_cast<long long>(nranks) * N_local;
@@ -274,6 +295,10 @@ int vqg_gemm_sharded(const void* x, const void* idx, const void* codebook, void*
   Problem p = make_problem(x, idx, codebook, y_local, M, N_local, K, v, C, idx_bytes, rows_per_codebook, ld);
   for (int r = 0; r < nranks; ++r)
     if (r != rank) p.peer_y[p.n_peers++] = static_cast<__half*>(y_peers[r]) + col0;
+  // through the switch only where the kernel that will run has the multimem epilogue (the prefill kernel);
+  // every other kernel keeps its per-rank stores
+  if (y_multicast && nranks > 1 && auto_path(p, VQG_LAYOUT_BL) == VQG_PATH_TENSOR_TS)
+    p.mc_y = static_cast<__half*>(y_multicast) + col0;
   return run(p, VQG_LAYOUT_BL, VQG_PATH_AUTO, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 

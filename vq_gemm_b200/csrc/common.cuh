@@ -24,6 +24,10 @@ struct Problem {
   // multi-GPU epilogue: additional copies of the output block (peer-mapped), may be 0
   int n_peers;
   __half* peer_y[8];
+  // multi-GPU epilogue through the switch: the multicast address of the output block (NVLS mapping of the ranks'
+  // symmetric Y buffers); one multimem store then lands in every rank's copy, this rank's included, and y /
+  // peer_y are not written.  Null = off.  Only the prefill kernel (weights through tensor memory) uses it.
+  __half* mc_y;
   // row-parallel (K-sharded) mode: the output columns are cut into n_owners blocks of owner_cols columns and
   // block o is written, as this rank's partial sum, to owner_part[o] ([M, owner_cols] fp16, possibly peer
   // memory) instead of y.  0 = off.
@@ -45,6 +49,7 @@ enum DeviceStatus : int {
   DS_PEER_READY_TIMEOUT = 8, // pair leader waited for the second CTA's operands
   DS_EPILOGUE_SYNC_TIMEOUT = 9,
   DS_SELFTEST_TIMEOUT = 10,  // the self-test kernel's wait on a barrier nobody signals
+  DS_RANK_BARRIER_TIMEOUT = 11,  // the cross-GPU barrier waited for a rank that did not arrive
 };
 int* device_status_ptr();          // device address of the status word of the current device
 cudaError_t ensure_status_word();  // looks its address up on first use (per device); allocates nothing
@@ -94,6 +99,8 @@ int launch_quantize_update(const __half* w, const void* idx, __half* cb, void* w
                            int C, int idx_bytes, int rows_per_cb, cudaStream_t s);
 int launch_pack12(const void* in, void* out, long long values, bool pack, cudaStream_t s);
 int launch_selftest_wait(long long limit_cycles, cudaStream_t s);   // see vqg_selftest_bounded_wait
+// cross-GPU barrier on epoch flags in peer-mapped memory, bounded wait (see vqg_rank_barrier)
+int launch_rank_barrier(unsigned* const* flags, int rank, int nranks, unsigned epoch, long long limit_cycles, cudaStream_t s);
 int launch_transpose(const __half* in, __half* out, int rows, int cols, cudaStream_t s);
 
 constexpr size_t kCounterBytes = 64 * 1024;  // arrival counters at the head of a workspace

@@ -77,6 +77,7 @@ struct TsParams {
   int* ws_counter;           // [tile][rank] arrivals of contributors; zero between calls
   int n_peers;
   __half* peer_y[8];
+  __half* mc_y;              // multicast address of the output block (gather through the switch), or null
   // row-parallel mode: the tile goes, as this rank's partial sum, to the buffer of the rank that owns its
   // columns (tensor map `owner` of PeerMaps, local or peer memory) and nowhere else
   int n_owners, owner_cols;
@@ -218,6 +219,9 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   const uint32_t to_peer = map_to_cta(base, rank ^ 1u) - base;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kTmemSlot);
 
+  // a kernel launched behind this one with programmatic stream serialisation (the cross-GPU barrier that ends a
+  // sharded step) may take its place on an SM now; it waits for this grid to complete before it does anything
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full(s), 1 + kDequantThreads / 32 + (rank == 0 ? 1 : 0));
@@ -483,6 +487,15 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           if (m0 + m < p.M && ncol < n_out) {
             const uint4 v = *reinterpret_cast<const uint4*>(stg + m * ROW_BYTES + chunk * 16);
             const size_t off = static_cast<size_t>(m0 + m) * p.ld_y + ncol;
+            if (p.mc_y) {
+              // gather through the switch: ONE 16-byte multimem store to the multicast mapping of the ranks'
+              // Y buffers; NVSwitch writes it into every rank's copy (this rank's too), so the SM issues one
+              // store per 16 bytes instead of one per rank and the link carries the block out once
+              asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.mc_y + off),
+                           "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+                           "f"(__uint_as_float(v.w)) : "memory");
+              continue;
+            }
             *reinterpret_cast<uint4*>(p.y + off) = v;
             // gather mode: the same 16 bytes to every peer's copy of Y.  (One TMA tensor store per peer from
             // the staging tile was measured slower: 265 against 219 us per step on 8 GPUs, 223 against 217 on
@@ -728,6 +741,7 @@ int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s
   tp.n_tiles = (p.N + BN - 1) / BN;
   tp.n_peers = p.n_peers;
   for (int i = 0; i < 8; ++i) tp.peer_y[i] = p.peer_y[i];
+  tp.mc_y = p.mc_y;
   tp.n_owners = p.n_owners;
   tp.owner_cols = p.owner_cols;
   const int max_pairs = sm_count() / 2;

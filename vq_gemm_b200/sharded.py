@@ -2,18 +2,27 @@
 matrix and the codebooks of those rows), X is replicated, and every rank ends up with the whole
 Y[M, N].  One process per GPU, ``torch.distributed`` for the plumbing.
 
-Two ways of assembling Y:
+Three ways of assembling Y:
 
-``mode="peer"``   Y lives in symmetric memory (two [M, N] buffers per rank, used in turn, peer-mapped
-                  over NVLink).  The GEMM epilogue stores each finished tile into every rank's buffer
-                  with ordinary global stores (``vqg_gemm_sharded``), so the exchange overlaps the
-                  main loop; one device-side barrier across ranks ends the step.  A step writes the
-                  buffer that was last written two steps ago: every rank passed the previous step's
-                  barrier after reading it, so no barrier is needed before the stores.  The returned
-                  tensor is therefore valid until the second call after it.  No TMA and no multicast
-                  touch peer memory.
-``mode="nccl"``   each rank computes its [M, N/G] block, NCCL all-gathers the blocks into
-                  [G, M, N/G] and a re-layout copy interleaves them into [M, N].
+``mode="peer"``       Y lives in symmetric memory (two [M, N] buffers per rank, used in turn, peer-mapped
+                      over NVLink).  The GEMM epilogue stores each finished tile into every rank's buffer
+                      with ordinary global stores (``vqg_gemm_sharded``), so the exchange overlaps the
+                      main loop; one bounded barrier across the ranks ends the step (``vqg_rank_barrier``:
+                      epoch flags in the same symmetric allocation, a rank that does not arrive within
+                      ``barrier_timeout_s`` turns into a status code, not a hang).
+``mode="multicast"``  the same, but the epilogue of the prefill kernel issues ONE multimem store per 16
+                      bytes to the NVLS multicast mapping of the buffers and the switch replicates it to
+                      every rank (``vqg_gemm_sharded_mc``): the SM issues 1/G of the stores and a rank's
+                      block leaves its GPU once.  Needs a multicast-capable fabric; ``multicast_available``
+                      tells.  Every rank must stay alive while the mapping exists.
+``mode="nccl"``       each rank computes its [M, N/G] block, NCCL all-gathers the blocks into
+                      [G, M, N/G] and a re-layout copy interleaves them into [M, N].
+
+Lifetime of the returned tensor (peer / multicast): a step writes the buffer that was last written two
+steps ago and no barrier precedes the stores, so the tensor returned by a call may be read only by work
+that is enqueued ON THE CALLING STREAM BEFORE THE NEXT CALL of the same object.  A reader on another
+stream must be waited for (event) before that next call; a reader enqueued after it races with the stores of
+ranks that are already one step ahead.  Copy the result if it has to live longer.
 
 ``RowParallelVQGemm`` is the K-sharded counterpart for the second half of a tensor-parallel MLP:
 each rank multiplies its slice of the input features by its K slice of the weights, the partial
@@ -65,15 +74,52 @@ def interleave_blocks(gathered: torch.Tensor) -> torch.Tensor:
     return gathered.permute(1, 0, 2).reshape(M, G * n_local)
 
 
+_FLAG_HALFS = 64          # 128 bytes of epoch flags behind the payload of a symmetric allocation
+_SM_HZ = 2.0e9            # cycles per second used to turn a timeout into a cycle limit (upper bound of the SM clock)
+
+
+class _RankBarrier:
+    """Epoch flags of ``vqg_rank_barrier`` inside a symmetric allocation: the last 128 bytes of ``flat``."""
+
+    def __init__(self, flat: torch.Tensor, hdl, world: int, rank: int, timeout_s: float):
+        self.world, self.rank = world, rank
+        self.flags = flat[-_FLAG_HALFS:].view(torch.int32)
+        self.flags.zero_()
+        off = (flat.numel() - _FLAG_HALFS) * 2
+        self._arr = (ctypes.c_void_p * world)(*[int(p) + off for p in hdl.buffer_ptrs])
+        self._limit = int(max(1e3, min(2e10, timeout_s * _SM_HZ)))
+        self._epoch = 0
+        torch.cuda.current_stream(flat.device).synchronize()
+        hdl.barrier()                      # once, at construction: every rank's flags are zero before anyone signals
+        torch.cuda.current_stream(flat.device).synchronize()
+
+    def __call__(self, stream: int) -> None:
+        self._epoch = (self._epoch + 1) & 0xFFFFFFFF          # flags are compared by signed difference: wrap-around is fine
+        st = _lib.load().vqg_rank_barrier(self._arr, self.rank, self.world, self._epoch, self._limit, stream)
+        _lib.check(st, "vqg_rank_barrier")
+
+
+def multicast_available(device: Optional[torch.device] = None, group: Optional[dist.ProcessGroup] = None) -> bool:
+    """Whether symmetric memory on this box comes with an NVLS multicast mapping (collective: every rank of
+    ``group`` must call it)."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) < 2:
+        return False
+    import torch.distributed._symmetric_memory as symm_mem
+    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    t = symm_mem.empty(1024, dtype=torch.float16, device=dev)
+    hdl = symm_mem.rendezvous(t, group if group is not None else dist.group.WORLD)
+    return int(getattr(hdl, "multicast_ptr", 0) or 0) != 0
+
+
 class ShardedVQGemm:
     """Holds the per-rank output buffers and runs the sharded product.
 
-    Collective construction: every rank of ``group`` must create it with the same M and N."""
+    Collective construction: every rank of ``group`` must create it with the same M, N and mode."""
 
     def __init__(self, M: int, N: int, *, group: Optional[dist.ProcessGroup] = None, mode: str = "peer",
-                 device: Optional[torch.device] = None):
-        if mode not in ("peer", "nccl"):
-            raise ValueError("mode must be 'peer' or 'nccl'")
+                 device: Optional[torch.device] = None, barrier_timeout_s: float = 2.0):
+        if mode not in ("peer", "multicast", "nccl"):
+            raise ValueError("mode must be 'peer', 'multicast' or 'nccl'")
         if dist.is_available() and dist.is_initialized():
             self.group = group if group is not None else dist.group.WORLD
             self.world = dist.get_world_size(self.group)
@@ -86,16 +132,23 @@ class ShardedVQGemm:
             raise ValueError("N must be a multiple of the world size")
         self.n_local = N // self.world
         self._hdl = None
+        self._mc = 0
         if self.world == 1:
             self.y = torch.empty((M, N), dtype=torch.float16, device=self.device)
             self._ptrs = [self.y.data_ptr()]
-        elif mode == "peer":
+        elif mode in ("peer", "multicast"):
             import torch.distributed._symmetric_memory as symm_mem
-            self._ybuf = symm_mem.empty((2, M, N), dtype=torch.float16, device=self.device)
-            self._hdl = symm_mem.rendezvous(self._ybuf, self.group)
+            self._flat = symm_mem.empty(2 * M * N + _FLAG_HALFS, dtype=torch.float16, device=self.device)
+            self._hdl = symm_mem.rendezvous(self._flat, self.group)
+            self._ybuf = self._flat[:2 * M * N].view(2, M, N)
             self._ptrs = [int(p) for p in self._hdl.buffer_ptrs]
-            if self._ptrs[self.rank] != self._ybuf.data_ptr():
+            if self._ptrs[self.rank] != self._flat.data_ptr():
                 raise RuntimeError("symmetric memory: local buffer pointer mismatch")
+            if mode == "multicast":
+                self._mc = int(getattr(self._hdl, "multicast_ptr", 0) or 0)
+                if self._mc == 0:
+                    raise RuntimeError("symmetric memory has no multicast mapping on this machine (mode='peer' works without)")
+            self._barrier = _RankBarrier(self._flat, self._hdl, self.world, self.rank, barrier_timeout_s)
             self._step = 0
             self.y = self._ybuf[0]
         else:
@@ -115,9 +168,20 @@ class ShardedVQGemm:
             self._ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         return self._ws.data_ptr(), self._ws.numel()
 
+    def gather_x(self, x_rows: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """All-gather of a row-sharded activation: every rank passes its [M/G, K] block of X (rank r holds rows
+        [r*M/G, (r+1)*M/G)) and gets the whole [M, K] back.  Lets a host feed each GPU 1/G of X instead of all of it."""
+        if self.world == 1:
+            return x_rows
+        if out is None:
+            out = torch.empty((x_rows.shape[0] * self.world, x_rows.shape[1]), dtype=x_rows.dtype, device=x_rows.device)
+        dist.all_gather_into_tensor(out, x_rows.contiguous(), group=self.group)
+        return out
+
     def __call__(self, x: torch.Tensor, idx_local: torch.Tensor, cb_local: torch.Tensor, rows_per_codebook: int = 0):
-        """x [M, K] (replicated), idx_local [N/G, K/v], cb_local: the block's codebooks.  Returns
-        the rank's full Y[M, N]; valid after the call on the current stream."""
+        """x [M, K] (replicated), idx_local [N/G, K/v], cb_local: the block's codebooks.  Returns the rank's full
+        Y[M, N]: valid for work enqueued on the current stream before the next call of this object (see the
+        module text)."""
         lib = _lib.load()
         M, K = x.shape
         if M != self.M or idx_local.shape[0] != self.n_local:
@@ -126,7 +190,7 @@ class ShardedVQGemm:
         _, C, v = cb3.shape
         ib = 1 if idx_local.dtype == torch.uint8 else 2
         stream = torch.cuda.current_stream(self.device).cuda_stream
-        if self.mode == "peer" or self.world == 1:
+        if self.mode != "nccl" or self.world == 1:
             # per-shape constants are looked up once: at 8 ranks a step is ~0.2 ms and host time counts
             key = (K, v, C, ib, rows_per_codebook)
             plan = self._plans.get(key)
@@ -137,17 +201,19 @@ class ShardedVQGemm:
                 plan = self._plans[key] = (nbytes, arrs)
             nbytes, arrs = plan
             ws_ptr, ws_n = self._workspace(nbytes)   # looked up every call: the buffer may have been regrown
-            arr = arrs[0]
+            arr, mc = arrs[0], None
             if self._hdl is not None:
                 par = self._step & 1
                 self.y = self._ybuf[par]
                 arr = arrs[par]
+                if self._mc:
+                    mc = self._mc + par * self.M * self.N * 2
                 self._step += 1
-            st = lib.vqg_gemm_sharded(x.data_ptr(), idx_local.data_ptr(), cb_local.data_ptr(), arr, self.rank,
-                                      self.world, M, self.n_local, K, v, C, ib, rows_per_codebook, ws_ptr, ws_n, stream)
+            st = lib.vqg_gemm_sharded_mc(x.data_ptr(), idx_local.data_ptr(), cb_local.data_ptr(), arr, mc, self.rank,
+                                         self.world, M, self.n_local, K, v, C, ib, rows_per_codebook, ws_ptr, ws_n, stream)
             _lib.check(st, "vqg_gemm_sharded")
             if self._hdl is not None:
-                self._hdl.barrier()  # every rank's stores into this rank's buffer have landed
+                self._barrier(stream)   # every rank's stores into this rank's buffer have landed
             return self.y
         from .ops import vq_gemm
         vq_gemm(x, idx_local, cb_local, rows_per_codebook=rows_per_codebook, layout="bl", out=self._block)
@@ -175,7 +241,8 @@ class RowParallelVQGemm:
     live in symmetric memory as two sets of G slots used in turn, so that one barrier per step (after
     the stores, before the sum) is enough."""
 
-    def __init__(self, M: int, N: int, *, group: Optional[dist.ProcessGroup] = None, device: Optional[torch.device] = None):
+    def __init__(self, M: int, N: int, *, group: Optional[dist.ProcessGroup] = None, device: Optional[torch.device] = None,
+                 barrier_timeout_s: float = 2.0):
         if dist.is_available() and dist.is_initialized():
             self.group = group if group is not None else dist.group.WORLD
             self.world = dist.get_world_size(self.group)
@@ -193,11 +260,13 @@ class RowParallelVQGemm:
             self._bases = [self._part.data_ptr()]
         else:
             import torch.distributed._symmetric_memory as symm_mem
-            self._part = symm_mem.empty((2, G, M, self.n_local), dtype=torch.float16, device=self.device)
-            self._hdl = symm_mem.rendezvous(self._part, self.group)
+            self._flat = symm_mem.empty(2 * G * M * self.n_local + _FLAG_HALFS, dtype=torch.float16, device=self.device)
+            self._hdl = symm_mem.rendezvous(self._flat, self.group)
+            self._part = self._flat[:2 * G * M * self.n_local].view(2, G, M, self.n_local)
             self._bases = [int(p) for p in self._hdl.buffer_ptrs]
-            if self._bases[self.rank] != self._part.data_ptr():
+            if self._bases[self.rank] != self._flat.data_ptr():
                 raise RuntimeError("symmetric memory: local buffer pointer mismatch")
+            self._barrier = _RankBarrier(self._flat, self._hdl, G, self.rank, barrier_timeout_s)
         self.y = torch.empty((M, self.n_local), dtype=torch.float16, device=self.device)
         self._step = 0
         self._ws = None
@@ -229,7 +298,7 @@ class RowParallelVQGemm:
                                       self._ws.data_ptr() if nbytes else None, self._ws.numel() if nbytes else 0, stream)
         _lib.check(st, "vqg_gemm_rowparallel")
         if self._hdl is not None:
-            self._hdl.barrier()   # every rank's partial of my block has landed in my slots
+            self._barrier(stream)   # every rank's partial of my block has landed in my slots
         st = lib.vqg_reduce_slots(self._part[par].data_ptr(), self.y.data_ptr(), self.world, M, self.n_local, self.n_local, stream)
         _lib.check(st, "vqg_reduce_slots")
         return self.y

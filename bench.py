@@ -334,6 +334,31 @@ def _sustained(V, shape, x, idx, cb, peaks, device_index, seconds=2.5):
             "frac_of_burst_peak": round(tf / peaks["tflops"], 4)}
 
 
+def _residual(V, peaks):
+    """Residual (two-codebook) weights on the headline shape: 2 x 1 bit per weight, both stages looked up and added
+    inside the prefill kernel."""
+    import torch
+    M, K, N, v, C, rpc, S = 2048, 8192, 28672, 8, 256, 128, 2
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(M, K, device="cuda", generator=g).half()
+    idx = torch.randint(0, C, (S, N, K // v), device="cuda", generator=g, dtype=torch.int32).to(torch.uint8)
+    cb = torch.stack([(torch.randn(N // rpc, C, v, device="cuda", generator=g) * (0.02 / 2 ** s)).half() for s in range(S)])
+    out = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    e0, e1 = _events()
+    for _ in range(3):
+        V.vq_gemm_residual(x, idx, cb, rows_per_codebook=rpc, out=out)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(10):
+        V.vq_gemm_residual(x, idx, cb, rows_per_codebook=rpc, out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 10
+    tf = 2.0 * M * N * K / ms / 1e9
+    return {"workload": "c5 shape, residual weights (2 stages x 1 bit/weight)", "M": M, "K": K, "N": N, "v": v, "C": C,
+            "stages": S, "us": round(ms * 1e3, 1), "tflops": round(tf, 1), "frac": round(tf / peaks["tflops"], 4)}
+
+
 def _quantizer(peaks, clocks_mhz):
     """Quantiser kernels on a layer of C4's size (N=14336, K=4096, v=4, 256 entries per 128 rows)."""
     from vq_gemm_b200 import quantize as VQ
@@ -896,6 +921,10 @@ def main():
             detail["gated_mlp_up"] = _gated(V, peaks)
         except Exception as e:
             detail["gated_mlp_up"] = {"error": repr(e)}
+        try:
+            detail["residual"] = _residual(V, peaks)
+        except Exception as e:
+            detail["residual"] = {"error": repr(e)}
         try:
             detail["quantizer"] = _quantizer(peaks, line["clocks"].get("sm_max_mhz") or 1965.0)
         except Exception as e:

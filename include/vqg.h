@@ -230,6 +230,28 @@ VQG_API int vqg_gemm_swiglu(const void* x, const void* idx, const void* codebook
                             int v, int C, int idx_bytes, int rows_per_codebook, void* workspace,
                             size_t workspace_bytes, void* stream);
 
+/* ---- Residual (multi-codebook) weights ---------------------------------------------------------
+ * The reference only hints at this format: `#define RESIDUAL 1` (strategy_1/src.cu:18) is defined and never
+ * used.  Here: n_stages index matrices idx [S][N][K/v] and codebook sets codebook [S][G][C][v], each stage
+ * laid out like the BL format and stored one after the other; the weight is the running fp16 sum of the
+ * stages' entries,
+ *     W_0 = codebook_0[g(n)][idx_0[n,j]],   W_s = fp16(W_{s-1} + codebook_s[g(n)][idx_s[n,j]])   (round to nearest even),
+ * so S stages of b bits give S*b bits per sub-vector.  vqg_dequant_residual writes exactly that W [N, K].
+ * vqg_gemm_residual computes Y = X * W^T: for M > 16 and two stages the prefill kernel holds both stages'
+ * codebook images and adds the two entries (HADD2) on their way into tensor memory -- the tensor core sees
+ * W bit for bit; for M <= 16 the decode kernel walks the stages like further chunks of K (the products of
+ * the stages are summed in fp32, which differs from the product with the rounded W by less than the fp16
+ * rounding of W); other shapes dequantise into the workspace and run the dense kernel, or use the generic
+ * kernel.  n_stages == 1 is the plain product.  Workspace: vqg_residual_workspace_bytes(), 1024-byte
+ * aligned, zeroed once. */
+VQG_API size_t vqg_residual_workspace_bytes(int M, int N, int K, int v, int C, int idx_bytes, int rows_per_codebook,
+                                            int n_stages);
+VQG_API int vqg_gemm_residual(const void* x, const void* idx, const void* codebook, void* y, int M, int N, int K,
+                              int v, int C, int idx_bytes, int rows_per_codebook, int n_stages, void* workspace,
+                              size_t workspace_bytes, void* stream);
+VQG_API int vqg_dequant_residual(const void* idx, const void* codebook, void* w_out, int N, int K, int v, int C,
+                                 int idx_bytes, int rows_per_codebook, int n_stages, void* stream);
+
 /* ---- Quantiser: the step before the product ------------------------------------------------
  * The reference has no quantiser (bench.py:83-85 fills `w` with random bytes); these entry points
  * turn a dense fp16 weight W[N, K] into the BL format on the GPU.  All pointers are device

@@ -117,6 +117,62 @@ def dequant_ref_scalar(w, codebook):
     return out
 
 
+def dequant_bl_residual(idx: torch.Tensor, codebook: torch.Tensor, rows_per_codebook: int = 0) -> torch.Tensor:
+    """Residual (multi-codebook) BL gather.  idx [S, N, K/v]; codebook [S, G, C, v] -> W [N, K] fp16 with
+
+        W_0 = codebook_0[g(n)][idx_0[n, j]],   W_s = fp16(W_{s-1} + codebook_s[g(n)][idx_s[n, j]])
+
+    i.e. the stages' entries added one after the other, every addition rounded to fp16 (round to nearest even;
+    torch adds two fp16 tensors on the CPU by adding in fp32 and rounding, which is the same value).  The
+    reference only names the idea (`#define RESIDUAL 1`, strategy_1/src.cu:18, never used), so the rule is
+    this build's: parity unpinned against the reference."""
+    S = idx.shape[0]
+    w = dequant_bl_layout(idx[0], codebook[0], rows_per_codebook)
+    for s in range(1, S):
+        w = (w.float() + dequant_bl_layout(idx[s], codebook[s], rows_per_codebook).float()).half()
+    return w
+
+
+def dequant_bl_residual_scalar(idx, codebook, rows_per_codebook: int = 0):
+    """The residual rule as plain Python loops over numpy float16 scalars (small cases only)."""
+    import numpy as np
+    S, N, J = idx.shape
+    _, G, C, v = codebook.shape
+    if rows_per_codebook <= 0:
+        rows_per_codebook = N if G == 1 else N // G
+    cbn = codebook.numpy()
+    ii = [_as_index(idx[s]).tolist() for s in range(S)]
+    out = np.empty((N, J * v), dtype=np.float16)
+    for n in range(N):
+        g = n // rows_per_codebook
+        for j in range(J):
+            for r in range(v):
+                acc = cbn[0, g, ii[0][n][j], r]
+                for s in range(1, S):
+                    acc = np.float16(np.float32(acc) + np.float32(cbn[s, g, ii[s][n][j], r]))
+                out[n, v * j + r] = acc
+    return torch.from_numpy(out)
+
+
+def vq_gemm_bl_residual(x, idx, codebook, rows_per_codebook: int = 0) -> torch.Tensor:
+    return matmul_fp32acc(x, dequant_bl_residual(idx, codebook, rows_per_codebook))
+
+
+def make_residual_inputs(M, K, N, v, C, rows_per_codebook=0, stages=2, seed=0, idx_dtype: Optional[torch.dtype] = None,
+                         cb_sigma: float = 0.02):
+    """Seeded inputs of the residual format: stage s has its own indices and codebooks, later stages smaller
+    (sigma / 2^s) as a residual quantiser would leave them."""
+    g = torch.Generator().manual_seed(seed)
+    G = 1 if rows_per_codebook <= 0 else (N + rows_per_codebook - 1) // rows_per_codebook
+    x = torch.randn(M, K, generator=g).half()
+    cb = torch.stack([(torch.randn(G, C, v, generator=g) * (cb_sigma / 2 ** s)).half() for s in range(stages)])
+    if idx_dtype is None:
+        idx_dtype = torch.uint8 if C <= 256 else torch.int16
+    idx = torch.randint(0, C, (stages, N, K // v), generator=g, dtype=torch.int32)
+    idx = idx.to(torch.uint8) if idx_dtype == torch.uint8 else idx.to(torch.int16)
+    return x, idx.contiguous(), cb.contiguous()
+
+
 def matmul_fp32acc(x: torch.Tensor, w_nk: torch.Tensor) -> torch.Tensor:
     """Y = X @ W^T with fp32 accumulation and one rounding to fp16.  x [M,K], w_nk [N,K]."""
     return (x.float() @ w_nk.float().t()).half()

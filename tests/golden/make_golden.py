@@ -103,5 +103,15 @@ def main():
         print(tag, "written", tuple(y.shape))
 
 
+    # residual (two-codebook) case, written by the scalar-loop statement of the rule: (M, K, N, v, C, rpc, stages, seed)
+    for tag, (M, K, N, v, C, rpc, stages, seed) in {"bl_residual_v8_c256_s2": (20, 128, 256, 8, 256, 128, 2, 3)}.items():
+        x, idx, cb = O.make_residual_inputs(M, K, N, v, C, rpc, stages=stages, seed=seed)
+        wdec = O.dequant_bl_residual_scalar(idx, cb, rpc)
+        y = O.matmul_fp32acc(x, wdec)
+        np.savez_compressed(os.path.join(HERE, f"{tag}.npz"), x=x.numpy(), idx=idx.numpy(), codebook=cb.numpy(),
+                            w_decoded=wdec.numpy(), y=y.numpy(), meta=np.array([M, K, N, v, C, rpc, stages, seed]))
+        print(tag, "written", tuple(y.shape))
+
+
 if __name__ == "__main__":
     main()

@@ -51,8 +51,8 @@ def test_bl_gather_matches_bytes_gathered_by_the_reference(golden_dir):
 
 def test_golden_files_all_covered(golden_dir):
     tags = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(golden_dir, "*.npz")))
-    assert tags == ["bl_v4_c256_groups", "bl_v8_c256_groups", "bl_v8_c4096_single", "ref_nq4_bridge", "ref_ragged",
-                    "ref_small", "ref_two_tiles"]
+    assert tags == ["bl_residual_v8_c256_s2", "bl_v4_c256_groups", "bl_v8_c256_groups", "bl_v8_c4096_single",
+                    "ref_nq4_bridge", "ref_ragged", "ref_small", "ref_two_tiles"]
 
 
 @pytest.mark.parametrize("N,K,v,C,rpc,dtype", [
@@ -106,3 +106,18 @@ def test_empty_shapes():
     x, idx, cb = O.make_bl_inputs(4, 0, 8, 4, 256, 0, seed=0)
     y = O.vq_gemm_bl(x, idx, cb, 0)
     assert y.shape == (4, 8) and float(y.abs().max()) == 0.0
+
+
+def test_residual_rule_vectorised_equals_scalar_and_fixture(golden_dir):
+    g = _load(os.path.join(golden_dir, "bl_residual_v8_c256_s2.npz"))
+    M, K, N, v, C, rpc, stages, seed = [int(t) for t in g["meta"]]
+    w = O.dequant_bl_residual(g["idx"], g["codebook"], rpc)
+    assert torch.equal(w.view(torch.int16), g["w_decoded"].view(torch.int16))
+    # one stage is the plain format; two equal stages double every weight exactly
+    assert torch.equal(O.dequant_bl_residual(g["idx"][:1], g["codebook"][:1], rpc).view(torch.int16),
+                       O.dequant_bl_layout(g["idx"][0], g["codebook"][0], rpc).view(torch.int16))
+    _, idx, cb = O.make_residual_inputs(1, 32, 24, 4, 37, 8, stages=3, seed=2)
+    assert torch.equal(O.dequant_bl_residual(idx, cb, 8).view(torch.int16),
+                       O.dequant_bl_residual_scalar(idx, cb, 8).view(torch.int16))
+    y = O.vq_gemm_bl_residual(g["x"], g["idx"], g["codebook"], rpc)
+    assert O.check_tolerance(y, g["y"])["ok"]

@@ -402,6 +402,81 @@ int vqg_gemm_small_batch_noalloc(const void* x, const void* idx, const void* cod
   return launch_decode_static(p, static_cast<cudaStream_t>(stream));
 }
 
+// ---- residual (multi-codebook) weights -------------------------------------------------------------
+namespace {
+// which kernel serves a residual problem: 2 decode, 6 prefill (two resident images), 4 dequantise + dense, 1 generic
+int residual_route(const vqg::Problem& p) {
+  if (p.K == 0) return VQG_PATH_GENERIC;
+  if (p.M <= 16 && vqg::decode_supported(p)) return VQG_PATH_DECODE;
+  const int groups = (p.N + p.rows_per_cb - 1) / p.rows_per_cb;
+  if (p.n_stages == 2 && p.M > 16 && vqg::tensor_ts_supported(p) &&
+      (static_cast<size_t>(groups) * p.C * p.v * 2) % 16 == 0)
+    return VQG_PATH_TENSOR_TS;
+  if (vqg::dense_supported(p.M, p.N, p.K) && (p.v == 2 || p.v == 4 || p.v == 8)) return VQG_PATH_TWO_PHASE;
+  return VQG_PATH_GENERIC;
+}
+}  // namespace
+
+size_t vqg_residual_workspace_bytes(int M, int N, int K, int v, int C, int idx_bytes, int rows_per_codebook, int n_stages) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (n_stages <= 1) return vqg_workspace_bytes(M, N, K, v, C, idx_bytes, rows_per_codebook, VQG_LAYOUT_BL, VQG_PATH_AUTO);
+  void* dummy = reinterpret_cast<void*>(static_cast<uintptr_t>(1024));
+  Problem p = make_problem(dummy, dummy, dummy, dummy, M, N, K, v, C, idx_bytes, rows_per_codebook, N);
+  p.n_stages = n_stages;
+  switch (residual_route(p)) {
+    case VQG_PATH_DECODE: return decode_workspace_bytes(p);
+    case VQG_PATH_TENSOR_TS: return tensor_ts_workspace_bytes(p);
+    case VQG_PATH_TWO_PHASE: return two_phase_bytes(N, K);
+    default: return 0;
+  }
+}
+
+int vqg_gemm_residual(const void* x, const void* idx, const void* codebook, void* y, int M, int N, int K, int v, int C,
+                      int idx_bytes, int rows_per_codebook, int n_stages, void* workspace, size_t workspace_bytes,
+                      void* stream) {
+  if (n_stages < 1 || n_stages > 8) return VQG_ERR_BAD_ARG;
+  if (n_stages == 1)
+    return vqg_gemm(x, idx, codebook, y, M, N, K, v, C, idx_bytes, rows_per_codebook, VQG_LAYOUT_BL, workspace,
+                    workspace_bytes, stream);
+  const int st = check_common(x, idx, codebook, y, M, N, K, v, C, idx_bytes, VQG_LAYOUT_BL);
+  if (st != VQG_OK) return st;
+  if (M == 0 || N == 0) return VQG_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Problem p = make_problem(x, idx, codebook, y, M, N, K, v, C, idx_bytes, rows_per_codebook, N);
+  p.n_stages = n_stages;
+  if (ensure_status_word() != cudaSuccess) return VQG_ERR_NO_DEVICE;
+  switch (residual_route(p)) {
+    case VQG_PATH_DECODE:
+      return launch_decode(p, workspace, workspace_bytes, s);
+    case VQG_PATH_TENSOR_TS:
+      return launch_tensor_ts(p, workspace, workspace_bytes, s);
+    case VQG_PATH_TWO_PHASE: {
+      const size_t need = two_phase_bytes(N, K);
+      if (!workspace || workspace_bytes < need || !aligned(workspace, 1024)) return VQG_ERR_WORKSPACE;
+      __half* w = reinterpret_cast<__half*>(static_cast<unsigned char*>(workspace) + kCounterBytes);
+      const int st2 = launch_dequant_bl_residual(idx, p.cb, w, N, K, v, C, idx_bytes, p.rows_per_cb, n_stages, s);
+      if (st2 != VQG_OK) return st2;
+      if (M > 128) return launch_dense_pair(p.x, w, p.y, M, N, K, N, 0, nullptr, s);
+      return launch_dense(p.x, w, p.y, M, N, K, N, 0, nullptr, s);
+    }
+    default:
+      return launch_generic(p, VQG_LAYOUT_BL, s);
+  }
+}
+
+int vqg_dequant_residual(const void* idx, const void* codebook, void* w_out, int N, int K, int v, int C, int idx_bytes,
+                         int rows_per_codebook, int n_stages, void* stream) {
+  if (N < 0 || K < 0 || n_stages < 1 || n_stages > 8) return VQG_ERR_BAD_ARG;
+  if (N == 0 || K == 0) return VQG_OK;
+  if (!idx || !codebook || !w_out) return VQG_ERR_BAD_ARG;
+  if (v < 1 || C < 1 || K % v != 0) return VQG_ERR_BAD_ARG;
+  if (idx_bytes != 1 && idx_bytes != 2) return VQG_ERR_UNSUPPORTED;
+  if (idx_bytes == 1 && C > 256) return VQG_ERR_BAD_ARG;
+  const int rpc = (rows_per_codebook <= 0 || rows_per_codebook > N) ? N : rows_per_codebook;
+  return launch_dequant_bl_residual(idx, static_cast<const __half*>(codebook), static_cast<__half*>(w_out), N, K, v, C,
+                                    idx_bytes, rpc, n_stages, static_cast<cudaStream_t>(stream));
+}
+
 int vqg_quantize_assign(const void* w, const void* codebook, void* idx_out, int N, int K, int v, int C, int idx_bytes,
                         int rows_per_codebook, void* stream) {
   if (!w || !codebook || !idx_out || N < 0 || K < 0) return VQG_ERR_BAD_ARG;

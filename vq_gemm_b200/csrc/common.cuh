@@ -34,6 +34,9 @@ struct Problem {
   int n_owners;
   int owner_cols;
   __half* owner_part[8];
+  // residual (multi-codebook) weights: n_stages index matrices [S][N][K/v] and codebook sets [S][G][C][v], one
+  // after the other in memory; W = the running fp16 sum over the stages of the looked-up entries.  0 or 1 = plain.
+  int n_stages;
 };
 
 // Device status word: 0 = fine; otherwise the code of the first bounded wait that ran out.
@@ -61,6 +64,9 @@ int launch_dequant_bl(const void* idx, const __half* cb, __half* w, int N, int K
                       int idx_bytes, int rows_per_cb, cudaStream_t s);
 int launch_dequant_ref(const uint8_t* w, const __half* cb, __half* out, int Nq, int K, bool transposed,
                        cudaStream_t s);
+// residual weights: w[n, k] = fp16 running sum over `stages` of codebook_s[g(n)][idx_s[n, k/v]][k%v]
+int launch_dequant_bl_residual(const void* idx, const __half* cb, __half* w, int N, int K, int v, int C, int idx_bytes,
+                               int rows_per_cb, int stages, cudaStream_t s);
 int launch_generic(const Problem& p, int layout, cudaStream_t s);
 
 bool decode_supported(const Problem& p);

@@ -54,7 +54,10 @@ struct DecodeParams {
   int M, N, K, C;
   long long ld_y;
   int nslices;         // K / KS
-  int nchunks;         // ceil(nslices / warps)
+  int nchunks;         // K chunks a row block is summed over: kchunks * stages
+  int kchunks;         // ceil(nslices / warps): chunks of K
+  int ngroups;         // codebook groups of one stage
+  int stage_rows;      // rows between the index matrices of consecutive residual stages (N)
   int rl;              // row lanes: super-units processed side by side by one CTA (warps / slices when K is short)
   int nrbg;            // items per chunk: ceil(N / (8 * SU * rl))
   int nslots;          // resident codebook images (1 or 2)
@@ -254,21 +257,29 @@ vq_decode_kernel(const __grid_constant__ CUtensorMap idx_map, const DecodeParams
     p_rbg = it0 - p_chunk * div;
   }
   const int first_chunk = p_chunk, first_rbg = p_rbg;
+  // a chunk is (residual stage, chunk of K): chunk = stage * kchunks + kchunk
+  int p_stg = (p.kchunks > 0 && p_chunk >= p.kchunks) ? p_chunk / p.kchunks : 0;
+  int p_kchunk = p_chunk - p_stg * p.kchunks;
   int p_stage = 0, in_flight = 0;
   auto request_tiles = [&]() {
     while (p_left > 0 && in_flight < S) {
-      const int slice = p_chunk * NW + wsl;
+      const int slice = p_kchunk * NW + wsl;
       if (role_ok && slice < p.nslices) {
         if (lane == 0) {
           const uint32_t bar = my_bars + p_stage * 8;
           tc::mbar_expect_tx(bar, STAGE);
-          tc::tma_load_2d(my_ring + p_stage * STAGE, &idx_map, slice * SLABB, (p_rbg * p.rl + wrl) * (8 * SU), bar);
+          tc::tma_load_2d(my_ring + p_stage * STAGE, &idx_map, slice * SLABB,
+                          p_stg * p.stage_rows + (p_rbg * p.rl + wrl) * (8 * SU), bar);
         }
         p_stage = (p_stage + 1 == S) ? 0 : p_stage + 1;
         ++in_flight;
       }
       --p_left;
-      if (++p_rbg == r_end) { p_rbg = off; ++p_chunk; }
+      if (++p_rbg == r_end) {
+        p_rbg = off;
+        ++p_chunk;
+        if (++p_kchunk == p.kchunks) { p_kchunk = 0; ++p_stg; }
+      }
     }
   };
   if (lane == 0) {
@@ -393,7 +404,7 @@ vq_decode_kernel(const __grid_constant__ CUtensorMap idx_map, const DecodeParams
     }
   };
 
-  int loaded_chunk = -1;
+  int loaded_kchunk = -1;
   int slot_group0 = -1, slot_group1 = -1;   // which group each image slot holds
   bool active = false;
   bool first_batch = true;
@@ -402,10 +413,13 @@ vq_decode_kernel(const __grid_constant__ CUtensorMap idx_map, const DecodeParams
   int seq = 0;
   int chunk = first_chunk;
   int rbg = first_rbg;
+  int stg = (chunk >= p.kchunks) ? chunk / p.kchunks : 0;   // residual stage and K chunk of `chunk`
+  int kchunk = chunk - stg * p.kchunks;
   while (seq < nitems) {
     // ---- the batch: items [seq, seq + cnt) = row block groups [rbg, rbg + cnt) of `chunk` ----------------
-    const int group = rbg / p.ipg;
-    const int gpos = rbg - group * p.ipg;
+    const int group_in_stage = rbg / p.ipg;
+    const int gpos = rbg - group_in_stage * p.ipg;
+    const int group = stg * p.ngroups + group_in_stage;    // codebooks of all stages, stage-major
     int cnt = min(min(p.batch, nitems - seq), min(r_end - rbg, p.nslots * p.ipg - gpos));
     const int g_first = group;
     const int g_last = group + ((gpos + cnt - 1 >= p.ipg) ? 1 : 0);   // a batch touches at most two groups
@@ -430,13 +444,13 @@ vq_decode_kernel(const __grid_constant__ CUtensorMap idx_map, const DecodeParams
     // started while its predecessor was still running, and waits here for it to complete.
     if (first_batch) asm volatile("griddepcontrol.wait;" ::: "memory");
     first_batch = false;
-    if (chunk != loaded_chunk) {
+    if (kchunk != loaded_kchunk) {
       // forms 2/3 pass X through the memory of the partial tiles: nobody may still be summing the last batch
-      if (FORM != 1 && loaded_chunk >= 0) __syncthreads();
-      active = role_ok && (chunk * NW + wsl) < p.nslices;
-      load_x(chunk, active);
+      if (FORM != 1 && loaded_kchunk >= 0) __syncthreads();
+      active = role_ok && (kchunk * NW + wsl) < p.nslices;
+      load_x(kchunk, active);
       if (FORM != 1) __syncthreads();   // ... and nobody writes partial tiles before every warp has its X
-      loaded_chunk = chunk;
+      loaded_kchunk = kchunk;
     }
 
     float* pb = part + static_cast<size_t>(parity) * (p.batch * NW * item_floats);
@@ -500,7 +514,7 @@ vq_decode_kernel(const __grid_constant__ CUtensorMap idx_map, const DecodeParams
     __syncthreads();
 
     // fixed-order sum over the slices of the chunk, one thread per output
-    const int nsl = min(NW, p.nslices - chunk * NW);
+    const int nsl = min(NW, p.nslices - kchunk * NW);
     const int outs = cnt * p.rl * item_floats;
     const bool split = p.nchunks > 1 && !p.row_owned;
     const bool carry = p.nchunks > 1 && p.row_owned;   // running sums over the chunks in shared memory
@@ -575,7 +589,11 @@ vq_decode_kernel(const __grid_constant__ CUtensorMap idx_map, const DecodeParams
 
     seq += cnt;
     rbg += cnt;
-    if (rbg == r_end) { rbg = off; ++chunk; }
+    if (rbg == r_end) {
+      rbg = off;
+      ++chunk;
+      if (++kchunk == p.kchunks) { kchunk = 0; ++stg; }
+    }
   }
 }
 
@@ -625,7 +643,11 @@ bool make_plan(const Problem& p, Plan& pl) {
   const int tile_rows = 8 * pl.su;
   if (!single && p.rows_per_cb % tile_rows != 0) return false;
   d.nslices = p.K / pl.ks;
-  d.nchunks = (d.nslices + pl.nw - 1) / pl.nw;
+  const int wstages = p.n_stages > 1 ? p.n_stages : 1;   // residual stages of the weights
+  if (wstages > 8) return false;
+  d.kchunks = (d.nslices + pl.nw - 1) / pl.nw;
+  d.nchunks = d.kchunks * wstages;
+  d.stage_rows = p.N;
   const int nsl_full = d.nslices < pl.nw ? d.nslices : pl.nw;
   const int tiles = (p.N + tile_rows - 1) / tile_rows;
   const int tiles_per_group = single ? tiles : (p.rows_per_cb / tile_rows);
@@ -634,6 +656,9 @@ bool make_plan(const Problem& p, Plan& pl) {
   d.rl = rl;
   d.nrbg = tiles / rl;
   d.ipg = tiles_per_group / rl;
+  d.ngroups = single ? 1 : (p.N + p.rows_per_cb - 1) / p.rows_per_cb;
+  // residual stages: the tiles of stage s are found s * N rows further down, so N must hold whole tiles
+  if (wstages > 1 && p.N % tile_rows != 0) return false;
 
   const int sms = device_sms();
   // what is dealt out over the CTAs: (chunk, item) pairs, or the items of one chunk in the row-owned mode.
@@ -723,7 +748,7 @@ bool make_idx_map(CUtensorMap* map, const Problem& p, const Plan& pl) {
   EncodeFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t row_bytes = static_cast<cuuint64_t>(p.K / p.v) * p.idx_bytes;
-  const cuuint64_t dims[2] = {row_bytes, static_cast<cuuint64_t>(p.N)};
+  const cuuint64_t dims[2] = {row_bytes, static_cast<cuuint64_t>(p.N) * (p.n_stages > 1 ? p.n_stages : 1)};
   const cuuint64_t strides[1] = {row_bytes};
   const cuuint32_t box[2] = {static_cast<cuuint32_t>(pl.slabb), static_cast<cuuint32_t>(8 * pl.su)};
   const cuuint32_t estr[2] = {1, 1};

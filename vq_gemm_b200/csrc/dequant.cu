@@ -235,6 +235,53 @@ int launch_transpose(const __half* in, __half* out, int rows, int cols, cudaStre
   return cuda_status(cudaGetLastError());
 }
 
+// Residual weights: one thread per index position; the stages' entries are added one after the other in fp16
+// (HADD2, round to nearest even), which is the format's rule, so the result is bit-exact by construction.
+template <int V, typename IdxT>
+__global__ void __launch_bounds__(256) dequant_bl_residual_kernel(const IdxT* __restrict__ idx, const __half* __restrict__ cb,
+                                                                  __half* __restrict__ w, int N, int K, int C, int rows_per_cb,
+                                                                  int stages) {
+  const int J = K / V;
+  const long long total = static_cast<long long>(N) * J;
+  const int groups = (N + rows_per_cb - 1) / rows_per_cb;
+  for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+       e += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int n = static_cast<int>(e / J);
+    const int g = n / rows_per_cb;
+    __half2 acc[V / 2];
+#pragma unroll
+    for (int r = 0; r < V / 2; ++r)
+      acc[r] = reinterpret_cast<const __half2*>(cb + (static_cast<size_t>(g) * C + idx[e]) * V)[r];
+    for (int st = 1; st < stages; ++st) {
+      const __half2* ent = reinterpret_cast<const __half2*>(cb + ((static_cast<size_t>(st) * groups + g) * C + idx[static_cast<size_t>(st) * total + e]) * V);
+#pragma unroll
+      for (int r = 0; r < V / 2; ++r) acc[r] = __hadd2(acc[r], ent[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < V / 2; ++r) reinterpret_cast<__half2*>(w + e * V)[r] = acc[r];
+  }
+}
+
+int launch_dequant_bl_residual(const void* idx, const __half* cb, __half* w, int N, int K, int v, int C, int idx_bytes,
+                               int rows_per_cb, int stages, cudaStream_t s) {
+  if (N == 0 || K == 0) return VQG_OK;
+  if (stages < 1 || stages > 8) return VQG_ERR_BAD_ARG;
+  if (!(v == 2 || v == 4 || v == 8)) return VQG_ERR_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(cb) % 4 || reinterpret_cast<uintptr_t>(w) % 4 ||
+      reinterpret_cast<uintptr_t>(idx) % static_cast<uintptr_t>(idx_bytes > 0 ? idx_bytes : 1))
+    return VQG_ERR_BAD_ARG;
+  const long long total = static_cast<long long>(N) * (K / v);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+#define VQG_DQR(V_, T_) dequant_bl_residual_kernel<V_, T_><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const T_*>(idx), cb, w, N, K, C, rows_per_cb, stages)
+  if (idx_bytes == 1) { if (v == 2) VQG_DQR(2, uint8_t); else if (v == 4) VQG_DQR(4, uint8_t); else VQG_DQR(8, uint8_t); }
+  else if (idx_bytes == 2) { if (v == 2) VQG_DQR(2, uint16_t); else if (v == 4) VQG_DQR(4, uint16_t); else VQG_DQR(8, uint16_t); }
+  else return VQG_ERR_UNSUPPORTED;
+#undef VQG_DQR
+  count_launch();
+  return cuda_status(cudaGetLastError());
+}
+
 // ---------------------------------------------------------------------------------------------
 // Shape-agnostic VQ-GEMM on CUDA cores: 64x64 output tile, 32-wide K steps, 4x4 per thread.
 // Accepts any M, N, K (K % v == 0), any C, both layouts.  Not a performance path.
@@ -262,7 +309,15 @@ __global__ void __launch_bounds__(256) generic_vq_gemm_kernel(Problem p) {
             const size_t ii = static_cast<size_t>(n) * J + k / p.v;
             const int c = p.idx_bytes == 1 ? idx8[ii] : idx16[ii];
             const int g = n / p.rows_per_cb;
-            wv = __half2float(p.cb[(static_cast<size_t>(g) * p.C + c) * p.v + (k % p.v)]);
+            __half w = p.cb[(static_cast<size_t>(g) * p.C + c) * p.v + (k % p.v)];
+            // residual stages: the fp16 running sum of the stages' entries (each addition rounded to fp16)
+            const int groups = (p.N + p.rows_per_cb - 1) / p.rows_per_cb;
+            for (int st = 1; st < p.n_stages; ++st) {
+              const size_t is = static_cast<size_t>(st) * p.N * J + ii;
+              const int cs = p.idx_bytes == 1 ? idx8[is] : idx16[is];
+              w = __hadd(w, p.cb[((static_cast<size_t>(st) * groups + g) * p.C + cs) * p.v + (k % p.v)]);
+            }
+            wv = __half2float(w);
           } else {
             const int nq = n >> 1, Nq = p.N >> 1;
             const int c = idx8[static_cast<size_t>(k) * Nq + nq];

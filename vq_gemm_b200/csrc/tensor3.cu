@@ -63,6 +63,8 @@ constexpr uint32_t kAColsPerStage = BK / 2;         // 32 columns: two fp16 per 
 struct TsParams {
   const unsigned char* idx;  // [N, K/v] uint8
   const __half* cb;          // [G, C, v]
+  const unsigned char* idx2; // residual weights: indices and codebooks of the second stage (RESID kernels)
+  const __half* cb2;
   __half* y;
   int* status;
   int M, N, K, C;
@@ -145,10 +147,10 @@ __device__ __forceinline__ Segment take_segment(int& lo, int& hi, bool& from_bac
 // kind::f16, A = B = fp16, D = fp32, both K-major, M = 256 weight rows (pair), N = 256 batch rows
 constexpr uint32_t kIdescTs = (1u << 4) | (static_cast<uint32_t>(BM >> 3) << 17) | (static_cast<uint32_t>(BN >> 4) << 24);
 
-template <int STAGES, int KS>
+template <int STAGES, int KS, int IMAGES = 1>
 struct TsSmem {
   static constexpr uint32_t kImage = STAGES * KS * kXBytes;
-  static constexpr uint32_t kStaging = kImage + kImageBytes;
+  static constexpr uint32_t kStaging = kImage + IMAGES * kImageBytes;
   static constexpr uint32_t kBars = kStaging + kStagingBytes;
   // full[S], empty[S], acc_full, acc_empty, dequant rendezvous, epilogue rendezvous
   static constexpr uint32_t kTmemSlot = kBars + (2 * STAGES + 4) * 8;
@@ -184,14 +186,24 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 // fp32 SiLU(g) * u of one (gate, up) pair of accumulators
 __device__ __forceinline__ float swiglu(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
 
+// fp16 addition of two packed pairs, round to nearest even, subnormals kept: the rule of the residual format
+__device__ __forceinline__ uint32_t hadd2_bits(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
 // GATED: weight rows come in (gate, up) pairs -- row 2i is gate row i, row 2i+1 is up row i -- and the
 // epilogue writes SiLU(X g_i) * (X u_i) into output column i, so Y is [M, N/2] and the two products of a
 // gated MLP's first half never reach memory.
-template <int V, int STAGES, int KS, bool GATED = false>
+// RESID: residual (two-codebook) weights, W = fp16(cb0[idx0] + cb1[idx1]): a dequant thread looks both entries
+// up (two resident images, two index streams) and adds them with HADD2 before the tcgen05.st, so the tensor
+// core sees ordinary fp16 weights.  One X stage less than the plain kernel makes room for the second image.
+template <int V, int STAGES, int KS, bool GATED = false, bool RESID = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ PeerMaps peer_maps,
                     const TsParams p) {
-  using L = TsSmem<STAGES, KS>;
+  using L = TsSmem<STAGES, KS, RESID ? 2 : 1>;
   constexpr uint32_t kStageCols = KS * kAColsPerStage;
   constexpr uint32_t kStageXBytes = KS * kXBytes;
   static_assert(kAccCols + STAGES * kStageCols <= kTmemCols, "A stages do not fit tensor memory");
@@ -553,19 +565,41 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           for (int u = tix; u < p.C * REPS; u += kDequantThreads)
             reinterpret_cast<uint4*>(image)[u] = __ldg(reinterpret_cast<const uint4*>(src) + u / REPS);
         }
+        if constexpr (RESID) {   // the second stage's codebook of the same group, behind the first image
+          const unsigned char* src2 = reinterpret_cast<const unsigned char*>(p.cb2) + (static_cast<size_t>(group) * p.C << ENTRY_LOG2);
+          unsigned char* image2 = image + kImageBytes;
+          if (V == 4) {
+            for (int u = tix; u < p.C * (REPS / 2); u += kDequantThreads) {
+              const uint2 e = __ldg(reinterpret_cast<const uint2*>(src2) + u / (REPS / 2));
+              reinterpret_cast<uint4*>(image2)[u] = make_uint4(e.x, e.y, e.x, e.y);
+            }
+          } else {
+            for (int u = tix; u < p.C * REPS; u += kDequantThreads)
+              reinterpret_cast<uint4*>(image2)[u] = __ldg(reinterpret_cast<const uint4*>(src2) + u / REPS);
+          }
+        }
         if (!(ok = dq_sync())) break;
       }
 
       const unsigned char* row_ptr = p.idx + static_cast<size_t>(row_valid ? n : 0) * J;
       uint32_t cur[16], nxt[16];
-      auto load_granule = [&](int gi, uint32_t (&dst)[16]) {
+      // second index stream of the residual format (one 16-register buffer: its loads are issued a granule
+      // ahead like the first stream's, straight into the buffer the next granule reads)
+      constexpr int R2 = RESID ? 16 : 1;
+      uint32_t cur2[R2], nxt2[R2];
+      auto load_granule_from = [&](const unsigned char* rp, int gi, uint32_t* dst) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint4 t = make_uint4(0, 0, 0, 0);
           const int byte0 = gi * 64 + q * 16;
-          if (row_valid && byte0 + 16 <= J) t = __ldg(reinterpret_cast<const uint4*>(row_ptr + byte0));
+          if (row_valid && byte0 + 16 <= J) t = __ldg(reinterpret_cast<const uint4*>(rp + byte0));
           dst[4 * q] = t.x; dst[4 * q + 1] = t.y; dst[4 * q + 2] = t.z; dst[4 * q + 3] = t.w;
         }
+      };
+      const unsigned char* row_ptr2 = RESID ? p.idx2 + static_cast<size_t>(row_valid ? n : 0) * J : nullptr;
+      auto load_granule = [&](int gi, uint32_t (&dst)[16]) {
+        load_granule_from(row_ptr, gi, dst);
+        if constexpr (RESID) load_granule_from(row_ptr2, gi, nxt2);
       };
       // a unit is a whole number of 64-byte index granules unless it is the whole tile
       const int ks_begin = g.kt_begin * KS, ks_end = g.kt_end * KS;    // 64-wide sub-steps of the piece
@@ -574,6 +608,10 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       for (int gi = gi_begin; ok && gi < ngran; ++gi) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) cur[i] = nxt[i];
+        if constexpr (RESID) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) cur2[i] = nxt2[i];
+        }
         if (gi + 1 < ngran) load_granule(gi + 1, nxt);
 #pragma unroll
         for (int st = 0; st < GSTEPS; ++st) {
@@ -589,6 +627,13 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
               for (int b = 0; b < 4; ++b) {
                 const uint32_t c0 = (word >> (8 * b)) & 0xffu;
                 asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(a[8 * w + 2 * b]), "=r"(a[8 * w + 2 * b + 1]) : "r"(img + (c0 << 7)));
+                if constexpr (RESID) {
+                  const uint32_t c1 = (cur2[st * WPS + w] >> (8 * b)) & 0xffu;
+                  uint32_t e0, e1;
+                  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(e0), "=r"(e1) : "r"(img + kImageBytes + (c1 << 7)));
+                  a[8 * w + 2 * b] = hadd2_bits(a[8 * w + 2 * b], e0);
+                  a[8 * w + 2 * b + 1] = hadd2_bits(a[8 * w + 2 * b + 1], e1);
+                }
               }
             }
           } else {
@@ -601,6 +646,16 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                              : "=r"(a[16 * w + 4 * b]), "=r"(a[16 * w + 4 * b + 1]), "=r"(a[16 * w + 4 * b + 2]), "=r"(a[16 * w + 4 * b + 3])
                              : "r"(img + (c0 << 7)));
+                if constexpr (RESID) {
+                  const uint32_t c1 = (cur2[st * WPS + w] >> (8 * b)) & 0xffu;
+                  uint32_t e0, e1, e2, e3;
+                  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(e0), "=r"(e1), "=r"(e2), "=r"(e3)
+                               : "r"(img + kImageBytes + (c1 << 7)));
+                  a[16 * w + 4 * b] = hadd2_bits(a[16 * w + 4 * b], e0);
+                  a[16 * w + 4 * b + 1] = hadd2_bits(a[16 * w + 4 * b + 1], e1);
+                  a[16 * w + 4 * b + 2] = hadd2_bits(a[16 * w + 4 * b + 2], e2);
+                  a[16 * w + 4 * b + 3] = hadd2_bits(a[16 * w + 4 * b + 3], e3);
+                }
               }
             }
           }
@@ -762,7 +817,15 @@ int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s
   tp.ws_counter = split ? static_cast<int*>(ws) : nullptr;
   tp.ws_partial = split ? reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + kCounterBytes) : nullptr;
   constexpr int S = 4, KS = 2;   // 4 stages of 128 K values: 128 KiB of X tiles, 4 x 64 TMEM columns of A
-  const size_t smem = TsSmem<S, KS>::kTotal + 1024;
+  constexpr int SR = 3;          // residual weights: 3 stages, the fourth's 32 KiB hold the second codebook image
+  const bool resid = p.n_stages == 2;
+  if (p.n_stages > 2 || (resid && gated)) return VQG_ERR_UNSUPPORTED;
+  if (resid) {
+    const int groups = (p.N + tp.rows_per_cb - 1) / tp.rows_per_cb;
+    tp.idx2 = tp.idx + static_cast<size_t>(p.N) * (p.K / p.v);
+    tp.cb2 = tp.cb + static_cast<size_t>(groups) * p.C * p.v;
+  }
+  const size_t smem = (resid ? TsSmem<SR, KS, 2>::kTotal : TsSmem<S, KS>::kTotal) + 1024;
   auto launch = [&](auto kernel) -> int {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return VQG_ERR_LAUNCH;
@@ -770,6 +833,7 @@ int launch_tensor_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s
     count_launch();
     return cuda_status(cudaGetLastError());
   };
+  if (resid) return p.v == 4 ? launch(vq_tensor_ts_kernel<4, SR, KS, false, true>) : launch(vq_tensor_ts_kernel<8, SR, KS, false, true>);
   if (gated) return p.v == 4 ? launch(vq_tensor_ts_kernel<4, S, KS, true>) : launch(vq_tensor_ts_kernel<8, S, KS, true>);
   if (p.v == 4) return launch(vq_tensor_ts_kernel<4, S, KS>);
   return launch(vq_tensor_ts_kernel<8, S, KS>);

@@ -4,6 +4,7 @@
     gemm(input, w) -> o                    dense fp16 product, w given as [K, N]
     vq_gemm(x, indices, codebook, ...)     generalised entry point (both weight formats)
     vq_gemm_swiglu(x, indices, codebook)   gated product SiLU(X g) * (X u) over (gate, up) row pairs
+    vq_gemm_residual(x, indices, codebook) residual (multi-codebook) weights: indices [S, N, K/v], codebook [S, G, C, v]
     dequant(indices, codebook, ...)        bit-exact dequantised weights
 
 All tensors must be CUDA tensors on one device; the output is allocated by the callee on that
@@ -115,6 +116,60 @@ def vq_gemm(x: torch.Tensor, indices: torch.Tensor, codebook: torch.Tensor, *, r
                                rows_per_codebook, lay, pth, ws.data_ptr() if ws is not None else None,
                                ws.numel() if ws is not None else 0, _stream_ptr(dev))
     _lib.check(st, "vq_gemm")
+    return out
+
+
+def _residual_dims(indices: torch.Tensor, codebook: torch.Tensor, rows_per_codebook: Optional[int]):
+    if indices.dim() != 3 or codebook.dim() != 4 or indices.shape[0] != codebook.shape[0]:
+        raise RuntimeError("residual weights need indices [S, N, K/v] and codebook [S, G, C, v] with the same S")
+    S, N, J = indices.shape
+    _, G, C, v = codebook.shape
+    if rows_per_codebook is None:
+        rows_per_codebook = 0 if G == 1 else N // G
+    need_groups = 1 if rows_per_codebook <= 0 else -(-N // rows_per_codebook)
+    if G != need_groups:
+        raise RuntimeError(f"{G} codebooks per stage given, {need_groups} needed (stages are stored back to back)")
+    return S, N, J, G, C, v, rows_per_codebook
+
+
+def vq_gemm_residual(x: torch.Tensor, indices: torch.Tensor, codebook: torch.Tensor, *,
+                     rows_per_codebook: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Y = X @ W^T for residual (multi-codebook) weights: indices [S, N, K/v], codebook [S, G, C, v],
+    W = the running fp16 sum over the stages of the looked-up entries (see include/vqg.h)."""
+    lib = _lib.load()
+    dev = _require_cuda(x, indices, codebook)
+    if x.dtype != torch.float16 or codebook.dtype != torch.float16:
+        raise RuntimeError("x and codebook must be float16")
+    S, N, J, G, C, v, rpc = _residual_dims(indices, codebook, rows_per_codebook)
+    M, K = x.shape
+    if J * v != K:
+        raise RuntimeError(f"indices [S, N, K/v] = {tuple(indices.shape)} do not match K={K}, v={v}")
+    ib = _idx_bytes(indices)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=dev)
+    elif tuple(out.shape) != (M, N) or out.dtype != torch.float16 or not out.is_contiguous() or out.device != dev:
+        raise RuntimeError("out must be a contiguous float16 [M, N] tensor on the inputs' device")
+    with torch.cuda.device(dev):
+        ws = _ws(dev, lib.vqg_residual_workspace_bytes(M, N, K, v, C, ib, rpc, S))
+        st = lib.vqg_gemm_residual(x.data_ptr(), indices.data_ptr(), codebook.data_ptr(), out.data_ptr(), M, N, K, v, C, ib,
+                                   rpc, S, ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                                   _stream_ptr(dev))
+    _lib.check(st, "vq_gemm_residual")
+    return out
+
+
+def dequant_residual(indices: torch.Tensor, codebook: torch.Tensor, *, rows_per_codebook: Optional[int] = None) -> torch.Tensor:
+    """Dequantised residual weights [N, K], bit-exact by the format's rule."""
+    lib = _lib.load()
+    dev = _require_cuda(indices, codebook)
+    if codebook.dtype != torch.float16:
+        raise RuntimeError("codebook must be float16")
+    S, N, J, G, C, v, rpc = _residual_dims(indices, codebook, rows_per_codebook)
+    out = torch.empty((N, J * v), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        st = lib.vqg_dequant_residual(indices.data_ptr(), codebook.data_ptr(), out.data_ptr(), N, J * v, v, C,
+                                      _idx_bytes(indices), rpc, S, _stream_ptr(dev))
+    _lib.check(st, "dequant_residual")
     return out
 
 

@@ -669,7 +669,9 @@ bool make_plan(const Problem& p, Plan& pl) {
   pl.rep_log2 = pick_rep_log2(p.v, p.C, 64 * 1024);
   const size_t img_bytes = static_cast<size_t>(p.C) * entry << pl.rep_log2;
   const size_t budget = pl.form == 1 ? 112 * 1024 : 220 * 1024;   // form 1: two launches side by side on an SM
-  d.nslots = (!single && 2 * img_bytes + 48 * 1024 <= budget) ? 2 : 1;
+  // a second resident image lets a batch straddle a group boundary; only where it leaves room for the rest
+  const size_t rest_min = 2 * item_bytes + static_cast<size_t>(pl.nw) * (4 * pl.stage + (pl.form != 1 ? 4096 : 0)) + 8192;
+  d.nslots = (!single && 2 * img_bytes + (rest_min > 48 * 1024 ? rest_min : 48 * 1024) <= budget) ? 2 : 1;
   size_t acc_bytes = 0;
   d.row_owned = 0;
   if (d.nchunks > 1 && d.nrbg >= 6 * sms) {

@@ -52,6 +52,14 @@ def main():
             modes.append("multicast")
             if rank == 0:
                 print("MULTICAST_TESTED", flush=True)
+    if cases:
+        # a row-sharded activation all-gathered over NVLink equals the whole
+        xs = torch.arange(64 * 96, dtype=torch.float16).reshape(64, 96)
+        m_rows = 64 // world
+        got = ShardedVQGemm(64, 256 * world, mode="nccl", device=dev).gather_x(xs[rank * m_rows:(rank + 1) * m_rows].to(dev))
+        if not torch.equal(got.cpu(), xs):
+            ok = False
+            print(f"rank {rank}: gather_x MISMATCH", flush=True)
     for (M, K, N, v, C, rpc) in cases:
         x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=5)
         # the single-GPU result, block by block: a block computed alone has the same shape, hence the same

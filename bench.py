@@ -164,7 +164,7 @@ def _lookup_floor_us(shape, sm_mhz=1965.0, sms=148):
     return lookups * 2.0 * shape.v / 128.0 / sms / sm_mhz
 
 
-def _single_shape(V, shape, peaks, steps, warmup):
+def _single_shape(V, shape, peaks, steps, warmup, alternatives=True):
     """One single-GPU configuration: kernel time over a ring of index buffers larger than L2.  Returns the
     compact entry for the table at the end of the line and the per-path detail."""
     from vq_gemm_b200.formats import make_inputs
@@ -216,7 +216,7 @@ def _single_shape(V, shape, peaks, steps, warmup):
                         "frac_of_8000": round(a / 8000.0, 4), "bytes": shape.bytes_algorithmic,
                         "lookup_floor_us": round(_lookup_floor_us(shape), 2)})
         # both small-batch kernels, whichever the library picks by itself for this shape
-        for alt in ("decode", "small_ts"):
+        for alt in (("decode", "small_ts") if alternatives else ()):
             try:
                 V.vq_gemm(x, idx, cb, rows_per_codebook=shape.rows_per_codebook, layout="bl", path=alt, out=out)
             except RuntimeError:
@@ -228,7 +228,7 @@ def _single_shape(V, shape, peaks, steps, warmup):
         compact.update({"tflops": round(a, 1), "bound": "tensor", "frac": round(a / peaks["tflops"], 4),
                         "frac_of_2250": round(a / 2250.0, 4)})
         # the other routes through the library: single-CTA fused kernel, and dequantise-then-dense
-        for alt in ("tensor", "tensor_pair", "two_phase"):
+        for alt in (("tensor", "tensor_pair", "two_phase") if alternatives else ()):
             for _ in range(3):
                 V.vq_gemm(x, idx, cb, rows_per_codebook=shape.rows_per_codebook, layout="bl", path=alt, out=out)
             torch.cuda.synchronize()
@@ -720,6 +720,12 @@ def main():
                 detail["shapes"].append(det)
             except Exception as e:  # keep the headline line even if a side measurement fails
                 shapes.append({"workload": name, "error": repr(e)})
+        # C4 in a short burst as well (25 launches); its alternative routes are timed with the long extras below
+        try:
+            compact, _ = _single_shape(V, CONFIGS["c4_prefill"], peaks, 20, args.warmup, alternatives=False)
+            shapes.append(compact)
+        except Exception as e:
+            shapes.append({"workload": "c4_prefill", "error": repr(e)})
 
     def step():
         op(x, idx, cb, rpc)
@@ -910,13 +916,11 @@ def main():
             mlp = {"error": repr(e)}
         line["mlp70b"] = mlp
     if solo and not args.no_shapes:
-        for name in ("c4_prefill",):
-            try:
-                compact, det = _single_shape(V, CONFIGS[name], peaks, max(args.steps, 200), args.warmup)
-                shapes.append(compact)
-                detail["shapes"].append(det)
-            except Exception as e:  # keep the headline line even if a side measurement fails
-                shapes.append({"workload": name, "error": repr(e)})
+        try:
+            _, det = _single_shape(V, CONFIGS["c4_prefill"], peaks, max(args.steps, 200), args.warmup)
+            detail["shapes"].append(det)
+        except Exception as e:
+            detail["shapes"].append({"workload": "c4_prefill", "error": repr(e)})
         try:
             detail["gated_mlp_up"] = _gated(V, peaks)
         except Exception as e:

@@ -97,9 +97,11 @@ VQG_API int vqg_auto_path(int M, int N, int K, int v, int C, int idx_bytes, int 
  * Ordering: X, Y and the workspace follow the stream's order.  The WEIGHTS (idx, codebook) are
  * taken to be constant: for M <= 128 the kernels are launched with programmatic stream
  * serialisation and read indices and codebooks while the kernel ahead of them on the stream may
- * still be finishing (they wait for it before touching X, Y or the workspace).  If another KERNEL
- * on the same stream has just written the weights, put a synchronisation (event, host wait)
- * between it and this call; copies (cudaMemcpyAsync) need nothing. */
+ * still be finishing (they wait for it before touching X, Y or the workspace).  Weights written by
+ * this library's own entry points (vqg_quantize_*, vqg_pack12 / vqg_unpack12) are taken care of: the
+ * first product enqueued on that stream afterwards is launched in plain stream order.  If another
+ * KERNEL of the caller's has just written the weights on the same stream, put a synchronisation
+ * (event, host wait) between it and this call; copies (cudaMemcpyAsync) need nothing. */
 VQG_API int vqg_gemm(const void* x, const void* idx, const void* codebook, void* y,
              int M, int N, int K, int v, int C, int idx_bytes, int rows_per_codebook,
              int layout, void* workspace, size_t workspace_bytes, void* stream);

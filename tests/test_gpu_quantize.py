@@ -87,3 +87,24 @@ def test_pack12_round_trip_and_layout():
     assert torch.equal(VQ.unpack12(packed).cpu(), idx)
     with pytest.raises(RuntimeError):
         VQ.pack12(idx[:, :3].contiguous().cuda())
+
+
+def test_product_enqueued_right_behind_the_quantiser_sees_the_new_weights():
+    """The small-batch kernels read indices and codebooks before they wait for the kernel ahead of them on the
+    stream; behind the library's own quantiser kernels they are launched in plain stream order instead.  Ten
+    rounds of (new assignment, product) with no host synchronisation in between, each checked afterwards."""
+    N, K, v, C, rpc, M = 2048, 4096, 4, 256, 128, 2
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(3)).half().cuda()
+    outs, idxs = [], []
+    cbs = [VQ.initial_codebook(_weights(N, K, seed=20 + i).cuda(), v, C, rpc, seed=i) for i in range(10)]
+    ws = [_weights(N, K, seed=40 + i).cuda() for i in range(10)]
+    idx = torch.empty((N, K // v), dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    for i in range(10):
+        VQ.assign(ws[i], cbs[i], rpc, out=idx)                                  # writes the indices ...
+        outs.append(V.vq_gemm(x, idx, cbs[i], rows_per_codebook=rpc, layout="bl"))   # ... the product reads them at once
+        idxs.append(idx.clone())
+    torch.cuda.synchronize()
+    for i in range(10):
+        want = V.vq_gemm(x, idxs[i], cbs[i], rows_per_codebook=rpc, layout="bl")
+        assert torch.equal(outs[i].view(torch.int16), want.view(torch.int16)), i

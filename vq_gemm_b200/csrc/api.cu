@@ -18,6 +18,30 @@ __device__ int g_status_word[64];
 
 void count_launch(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
 
+namespace {
+std::mutex g_dirty_mu;
+cudaStream_t g_dirty[16];
+int g_ndirty = 0;
+}  // namespace
+
+void note_weights_written(cudaStream_t s) {
+  std::lock_guard<std::mutex> lk(g_dirty_mu);
+  for (int i = 0; i < g_ndirty; ++i)
+    if (g_dirty[i] == s) return;
+  if (g_ndirty < 16) g_dirty[g_ndirty++] = s;
+  else g_dirty[0] = s;   // table full: streams may then be reported late; the documented contract still holds
+}
+
+bool take_weights_written(cudaStream_t s) {
+  std::lock_guard<std::mutex> lk(g_dirty_mu);
+  for (int i = 0; i < g_ndirty; ++i)
+    if (g_dirty[i] == s) {
+      g_dirty[i] = g_dirty[--g_ndirty];
+      return true;
+    }
+  return false;
+}
+
 cudaError_t ensure_status_word() {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);

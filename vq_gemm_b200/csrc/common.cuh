@@ -59,6 +59,13 @@ cudaError_t ensure_status_word();  // looks its address up on first use (per dev
 
 void count_launch(int n = 1);
 
+// Weights written by this library on a stream (the quantiser, the index packer): the small-batch kernels read
+// indices and codebooks BEFORE they wait for the kernel ahead of them when launched with programmatic stream
+// serialisation, so the first product enqueued on that stream afterwards is launched without that attribute
+// (ordinary stream order).  note_weights_written marks the stream; take_weights_written reports and clears it.
+void note_weights_written(cudaStream_t s);
+bool take_weights_written(cudaStream_t s);
+
 // ---- launchers (each returns a VQG_* status) -------------------------------------------
 int launch_dequant_bl(const void* idx, const __half* cb, __half* w, int N, int K, int v, int C,
                       int idx_bytes, int rows_per_cb, cudaStream_t s);

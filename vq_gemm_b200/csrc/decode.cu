@@ -824,7 +824,8 @@ int launch_decode(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s) {
     pl.d.ws_partial = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + kCounterBytes);
   }
   pl.d.status = device_status_ptr();
-  return launch_planned(p, pl, /*dependent=*/true, s);
+  // the weight-only prologue may run beside the kernel ahead on the stream -- unless that kernel wrote the weights
+  return launch_planned(p, pl, /*dependent=*/!take_weights_written(s), s);
 }
 
 

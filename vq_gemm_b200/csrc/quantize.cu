@@ -246,6 +246,7 @@ int launch_quantize_assign(const __half* w, const __half* cb, void* idx, int N, 
   }
 #undef VQG_ASSIGN
   count_launch();
+  note_weights_written(s);
   return cuda_status(cudaGetLastError());
 }
 
@@ -292,6 +293,7 @@ int launch_quantize_update(const __half* w, const void* idx, __half* cb, void* w
   const long long n_entries = static_cast<long long>(entries);
   finalize_kernel<<<static_cast<unsigned>((n_entries + 255) / 256), 256, 0, s>>>(cb, sums, counts, n_entries, v);
   count_launch();
+  note_weights_written(s);
   return cuda_status(cudaGetLastError());
 }
 
@@ -309,6 +311,7 @@ int launch_pack12(const void* in, void* out, long long values, bool pack, cudaSt
   else
     unpack12_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const unsigned char*>(in), static_cast<uint16_t*>(out), pairs);
   count_launch();
+  note_weights_written(s);
   return cuda_status(cudaGetLastError());
 }
 

@@ -563,6 +563,7 @@ int launch_small_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s)
 
   const size_t entry = static_cast<size_t>(2) * p.v;
   const size_t img = pl.repl ? static_cast<size_t>(p.C) * 128 : static_cast<size_t>(p.C) * entry;
+  const bool dependent = !take_weights_written(s);   // not beside a kernel of this library that wrote the weights
   auto launch = [&](auto kernel, size_t x_bytes, int n_bars) -> int {
     const size_t smem = x_bytes + ((img + 15) & ~static_cast<size_t>(15)) + (n_bars + 1) * 8 + 16 + 1024;
     if (smem > 227 * 1024) return VQG_ERR_UNSUPPORTED;
@@ -579,7 +580,7 @@ int launch_small_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s)
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = dependent ? 1 : 0;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mx, sp);
     count_launch();
     return cuda_status(e == cudaSuccess ? cudaGetLastError() : e);

@@ -100,9 +100,8 @@ def kmeans_quantize(weight: torch.Tensor, *, v: int = 8, entries: int = 256, row
         kmeans_update(weight, idx, cb, rows_per_codebook)
         assign(weight, cb, rows_per_codebook, out=idx)
     # The small-batch product kernels read their weights before they wait for the kernel ahead of them on the
-    # stream (programmatic dependent launch): weights must be complete before such a launch is made.  This
-    # is an offline step, so one host-side wait here makes the returned tensors safe to use immediately.
-    torch.cuda.current_stream(weight.device).synchronize()
+    # stream (programmatic dependent launch).  The library orders its own quantiser kernels against the next
+    # product on the same stream, so the returned tensors can be used at once on this stream.
     return idx, cb
 
 

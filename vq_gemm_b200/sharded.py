@@ -178,10 +178,15 @@ class ShardedVQGemm:
         dist.all_gather_into_tensor(out, x_rows.contiguous(), group=self.group)
         return out
 
-    def __call__(self, x: torch.Tensor, idx_local: torch.Tensor, cb_local: torch.Tensor, rows_per_codebook: int = 0):
+    def __call__(self, x: torch.Tensor, idx_local: torch.Tensor, cb_local: torch.Tensor, rows_per_codebook: int = 0,
+                 copy: bool = False):
         """x [M, K] (replicated), idx_local [N/G, K/v], cb_local: the block's codebooks.  Returns the rank's full
         Y[M, N]: valid for work enqueued on the current stream before the next call of this object (see the
-        module text)."""
+        module text); with ``copy=True`` a private copy that stays valid."""
+        y = self._run(x, idx_local, cb_local, rows_per_codebook)
+        return y.clone() if copy else y
+
+    def _run(self, x: torch.Tensor, idx_local: torch.Tensor, cb_local: torch.Tensor, rows_per_codebook: int = 0):
         lib = _lib.load()
         M, K = x.shape
         if M != self.M or idx_local.shape[0] != self.n_local:

@@ -144,6 +144,31 @@ __device__ __forceinline__ Segment take_segment(int& lo, int& hi, bool& from_bac
   return g;
 }
 
+// The pieces of a pair's range in the order they are worked on; every role of the kernel walks them the same way.
+// Both partial pieces come first, then the whole tiles.  Even pairs take the piece at the END of their range
+// first, odd pairs the piece at the START: the tile shared by an even pair b and the odd pair b+1 then gets both of
+// its pieces at the very start of the kernel and is complete after max(l, 1 - l) of a tile time (l = the even pair's
+// share of it) instead of after both pairs have done both of their pieces -- in gather mode the first output crosses
+// the link that much earlier.  (The other half of the shared tiles is complete when the pieces are, as before.)
+struct Walk {
+  int lo, hi;
+  bool back_pending, front_first;
+  __device__ __forceinline__ Walk(int pair_id, const TsParams& p) {
+    lo = pair_begin(pair_id, p.q, p.r);
+    hi = pair_begin(pair_id + 1, p.q, p.r);
+    back_pending = (hi % p.units_per_tile) != 0;
+    front_first = (pair_id & 1) != 0 && (lo % p.units_per_tile) != 0;
+  }
+  __device__ __forceinline__ bool next(Segment& g, const TsParams& p) {
+    if (lo >= hi) return false;
+    bool rev = false;
+    if (front_first) front_first = false;           // the piece at the start of the range
+    else if (back_pending) { rev = true; back_pending = false; }
+    g = take_segment(lo, hi, rev, p);
+    return true;
+  }
+};
+
 // kind::f16, A = B = fp16, D = fp32, both K-major, M = 256 weight rows (pair), N = 256 batch rows
 constexpr uint32_t kIdescTs = (1u << 4) | (static_cast<uint32_t>(BM >> 3) << 17) | (static_cast<uint32_t>(BN >> 4) << 24);
 
@@ -215,8 +240,6 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();         // 0 = pair leader
   const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int u_begin = pair_begin(pair_id, p.q, p.r), u_end = pair_begin(pair_id + 1, p.q, p.r);
-  const bool ends_inside_tile = (u_end % p.units_per_tile) != 0;
 
   auto x_addr = [&](int s) { return base + s * kStageXBytes; };
   // full[s]: this CTA's X half has landed (TMA, 1 arrival + bytes) and its 4 dequant warps have written
@@ -265,9 +288,9 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      bool from_back = ends_inside_tile;
-      for (int lo = u_begin, hi = u_end; ok && lo < hi;) {
-        const Segment g = take_segment(lo, hi, from_back, p);
+      Walk walk(pair_id, p);
+      Segment g;
+      while (ok && walk.next(g, p)) {
         const int m0 = (g.tile % p.m_tiles) * BM + static_cast<int>(rank) * BMH;
         for (int kt = g.kt_begin; kt < g.kt_end; ++kt) {
           if (!(ok = mbar_wait_cluster(bar_empty(stage), phase ^ 1, p.status, DS_STAGE_EMPTY_TIMEOUT))) break;
@@ -287,9 +310,9 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       if (rank == 0) {
         // ------------------------------- MMA issuer (pair leader) ---------------------------
         uint32_t acc_phase = 0;
-        bool from_back = ends_inside_tile;
-        for (int lo = u_begin, hi = u_end; ok && lo < hi;) {
-          const Segment g = take_segment(lo, hi, from_back, p);
+        Walk walk(pair_id, p);
+        Segment g;
+        while (ok && walk.next(g, p)) {
           if (!(ok = mbar_wait_cluster(bar_acc_empty, acc_phase ^ 1, p.status, DS_ACC_EMPTY_TIMEOUT))) break;
           tc_fence_after();
           for (int kt = g.kt_begin; kt < g.kt_end; ++kt) {
@@ -316,9 +339,9 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
       } else {
         // ------------------------------- forwarder (second CTA) -----------------------------
-        bool from_back = ends_inside_tile;
-        for (int lo = u_begin, hi = u_end; ok && lo < hi;) {
-          const Segment g = take_segment(lo, hi, from_back, p);
+        Walk walk(pair_id, p);
+        Segment g;
+        while (ok && walk.next(g, p)) {
           for (int kt = g.kt_begin; kt < g.kt_end; ++kt) {
             if (!(ok = mbar_wait(bar_full(stage), phase, p.status, DS_TMA_FULL_TIMEOUT))) break;
             mbar_arrive_remote(bar_full(stage) + to_peer);
@@ -347,9 +370,9 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     constexpr int OUT_COLS = GATED ? BNH / 2 : BNH;      // output columns of this CTA's half tile
     constexpr int ROW_BYTES = OUT_COLS * 2;              // one staged row of the tile
     constexpr size_t kPartialFloats = static_cast<size_t>(BM) * BNH;   // one CTA's share of a pair tile
-    bool from_back = ends_inside_tile;
-    for (int lo = u_begin, hi = u_end; ok && lo < hi;) {
-      const Segment g = take_segment(lo, hi, from_back, p);
+    Walk walk(pair_id, p);
+    Segment g;
+    while (ok && walk.next(g, p)) {
       const int tile = g.tile;
       const int m0 = (tile % p.m_tiles) * BM;
       const int n0 = ((tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH) / (GATED ? 2 : 1);   // first output column
@@ -545,9 +568,9 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       dq_phase ^= 1;
       return done;
     };
-    bool from_back = ends_inside_tile;
-    for (int lo = u_begin, hi = u_end; ok && lo < hi;) {
-      const Segment g = take_segment(lo, hi, from_back, p);
+    Walk walk(pair_id, p);
+    Segment g;
+    while (ok && walk.next(g, p)) {
       const int n_half0 = (g.tile / p.m_tiles) * BN + static_cast<int>(rank) * BNH;
       const int n = n_half0 + r;
       const bool row_valid = n < p.N;

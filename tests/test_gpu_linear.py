@@ -81,6 +81,40 @@ def test_from_weight_quantises_and_runs():
     assert rel_q <= 2e-2 * (float(dense.abs().max()) + 1)
 
 
+def test_residual_module_equals_the_functional_call_and_the_oracle():
+    x, idx, cb = O.make_residual_inputs(24, 512, 256, 8, 256, 128, 2, seed=9)
+    layer = VQLinear(idx, cb, 128).cuda()
+    assert layer.residual and (layer.in_features, layer.out_features, layer.v) == (512, 256, 8)
+    y = layer(x.reshape(2, 12, 512).cuda())
+    assert y.shape == (2, 12, 256)
+    assert torch.equal(bits(y.reshape(24, 256)), bits(V.vq_gemm_residual(x.cuda(), idx.cuda(), cb.cuda(), rows_per_codebook=128)))
+    assert_within_tolerance(y.reshape(24, 256).cpu(), O.vq_gemm_bl_residual(x, idx, cb, 128))
+    assert torch.equal(bits(layer.dequantized_weight()).cpu(), bits(O.dequant_bl_residual(idx, cb, 128)))
+    torch.library.opcheck(torch.ops.vq_gemm_b200.vq_linear_residual.default, (x.cuda(), idx.cuda(), cb.cuda(), 128),
+                          test_utils=("test_schema", "test_faketensor"))
+    assert "stages=2" in repr(layer)
+    assert V.device_status() == 0
+
+
+def test_residual_quantiser_lowers_the_error_stage_by_stage():
+    w = (torch.randn(256, 512, generator=torch.Generator().manual_seed(5)) * 0.05).half().cuda()
+    errs = []
+    for stages in (1, 2, 3):
+        layer = VQLinear.from_weight(w, v=8, entries=256, rows_per_codebook=128, iters=4, stages=stages)
+        assert layer.indices.shape == ((stages, 256, 64) if stages > 1 else (256, 64))
+        errs.append(float((layer.dequantized_weight().float() - w.float()).norm() / w.float().norm()))
+    assert errs[1] < 0.9 * errs[0] and errs[2] < 0.9 * errs[1]
+    x = torch.randn(16, 512, generator=torch.Generator().manual_seed(6)).half().cuda()
+    dense = x.float() @ w.float().t()
+    y = layer(x)
+    assert float((y.float() - dense).norm() / dense.norm()) < 1.3 * errs[2] + 1e-2
+    # stage 0 of the residual quantiser is the plain quantiser with the same seed
+    from vq_gemm_b200.quantize import kmeans_quantize, kmeans_quantize_residual
+    i1, c1 = kmeans_quantize(w, v=8, entries=256, rows_per_codebook=128, iters=4, seed=0)
+    i2, c2 = kmeans_quantize_residual(w, stages=2, v=8, entries=256, rows_per_codebook=128, iters=4, seed=0)
+    assert torch.equal(i1, i2[0]) and torch.equal(bits(c1), bits(c2[0]))
+
+
 def test_gated_module_and_operator():
     from vq_gemm_b200.linear import VQGatedUp
     x, idx, cb = O.make_bl_inputs(160, 512, 512, 8, 256, 128, seed=7, cb_sigma=0.05)

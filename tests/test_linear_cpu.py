@@ -17,6 +17,31 @@ def test_fake_tensor_rule_gives_shape_and_dtype():
             torch.ops.vq_gemm_b200.vq_linear(x, idx, torch.empty(1, 256, 8, dtype=torch.float16, device="cuda"), 0)
 
 
+def test_fake_tensor_rule_of_the_residual_operator():
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        x = torch.empty(5, 64, dtype=torch.float16, device="cuda")
+        idx = torch.empty(2, 32, 16, dtype=torch.uint8, device="cuda")
+        cb = torch.empty(2, 1, 256, 4, dtype=torch.float16, device="cuda")
+        y = torch.ops.vq_gemm_b200.vq_linear_residual(x, idx, cb, 0)
+        assert y.shape == (5, 32) and y.dtype == torch.float16
+        with pytest.raises(RuntimeError):
+            torch.ops.vq_gemm_b200.vq_linear_residual(x, idx, cb[:1], 0)
+
+
+def test_residual_module_bookkeeping():
+    idx = torch.zeros(2, 256, 64, dtype=torch.uint8)
+    cb = torch.zeros(2, 2, 256, 8, dtype=torch.float16)
+    layer = VQLinear(idx, cb, 128)
+    assert layer.residual and (layer.in_features, layer.out_features, layer.v) == (512, 256, 8)
+    with pytest.raises(ValueError):
+        VQLinear(idx, cb[:1], 128)                 # one codebook array per stage
+    with pytest.raises(ValueError):
+        VQLinear(idx, cb[:, :1], 128)              # two groups of rows need two codebooks per stage
+    with pytest.raises(ValueError):
+        VQLinear(idx, cb[0], 128)
+
+
 def test_module_bookkeeping_and_checks():
     idx = torch.zeros(256, 64, dtype=torch.uint8)
     cb = torch.zeros(2, 256, 8, dtype=torch.float16)

@@ -33,6 +33,21 @@ def _(x, indices, codebook, rows_per_codebook):
     return x.new_empty((x.shape[0], indices.shape[0]))
 
 
+@torch.library.custom_op("vq_gemm_b200::vq_linear_residual", mutates_args=(), device_types="cuda")
+def vq_linear_residual(x: torch.Tensor, indices: torch.Tensor, codebook: torch.Tensor, rows_per_codebook: int) -> torch.Tensor:
+    """Residual weights: x [M, K] fp16, indices [S, N, K/v], codebook [S, G, C, v] fp16 -> [M, N] fp16."""
+    return ops.vq_gemm_residual(x, indices, codebook, rows_per_codebook=rows_per_codebook)
+
+
+@vq_linear_residual.register_fake
+def _(x, indices, codebook, rows_per_codebook):
+    if x.dim() != 2 or indices.dim() != 3 or codebook.dim() != 4 or indices.shape[0] != codebook.shape[0]:
+        raise RuntimeError("vq_linear_residual expects x [M, K], indices [S, N, K/v], codebook [S, G, C, v]")
+    if indices.shape[2] * codebook.shape[3] != x.shape[1]:
+        raise RuntimeError("indices [S, N, K/v] and codebook [S, G, C, v] do not match x [M, K]")
+    return x.new_empty((x.shape[0], indices.shape[1]))
+
+
 @torch.library.custom_op("vq_gemm_b200::vq_swiglu", mutates_args=(), device_types="cuda")
 def vq_swiglu(x: torch.Tensor, indices: torch.Tensor, codebook: torch.Tensor, rows_per_codebook: int) -> torch.Tensor:
     """x [M, K]; indices [2*N_out, K/v] with (gate, up) row pairs -> SiLU(x g^T) * (x u^T), [M, N_out] fp16."""
@@ -55,23 +70,30 @@ class VQLinear(nn.Module):
     entries), ``codebook`` [groups, C, v] fp16 with one codebook per ``rows_per_codebook``
     consecutive output features (0: a single codebook).  Both are buffers, so ``state_dict`` /
     ``load_state_dict`` / ``.to(device)`` carry them.  Accepts inputs of any leading shape.
+
+    Residual (multi-codebook) weights: ``indices`` [S, out_features, in_features / v] and ``codebook``
+    [S, groups, C, v]; the weight is the running fp16 sum of the S stages' entries (``from_weight(stages=2)``).
     """
 
     def __init__(self, indices: torch.Tensor, codebook: torch.Tensor, rows_per_codebook: int = 0,
                  bias: Optional[torch.Tensor] = None):
         super().__init__()
-        if indices.dim() != 2 or codebook.dim() not in (2, 3):
+        self.residual = indices.dim() == 3
+        if self.residual:
+            if codebook.dim() != 4 or codebook.shape[0] != indices.shape[0]:
+                raise ValueError("residual weights need indices [S, N, K/v] and codebook [S, G, C, v]")
+        elif indices.dim() != 2 or codebook.dim() not in (2, 3):
             raise ValueError("indices must be [N, K/v] and codebook [G, C, v] (or [C, v])")
         if indices.dtype not in (torch.uint8, torch.int16, torch.uint16):
             raise ValueError("indices must be uint8 or (u)int16")
-        cb = codebook if codebook.dim() == 3 else codebook.unsqueeze(0)
-        N = indices.shape[0]
+        cb = codebook if codebook.dim() >= 3 else codebook.unsqueeze(0)
+        N = indices.shape[-2]
         groups = 1 if rows_per_codebook <= 0 else -(-N // rows_per_codebook)
-        if cb.shape[0] < groups:
-            raise ValueError(f"{cb.shape[0]} codebooks given, {groups} needed")
+        if cb.shape[-3] < groups or (self.residual and cb.shape[-3] != groups):
+            raise ValueError(f"{cb.shape[-3]} codebooks given, {groups} needed")
         self.out_features = N
-        self.v = cb.shape[2]
-        self.in_features = indices.shape[1] * self.v
+        self.v = cb.shape[-1]
+        self.in_features = indices.shape[-1] * self.v
         self.rows_per_codebook = int(rows_per_codebook)
         self.register_buffer("indices", indices.contiguous())
         self.register_buffer("codebook", cb.to(torch.float16).contiguous())
@@ -84,10 +106,15 @@ class VQLinear(nn.Module):
 
     @classmethod
     def from_weight(cls, weight: torch.Tensor, *, v: int = 8, entries: int = 256, rows_per_codebook: int = 128,
-                    iters: int = 10, seed: int = 0, bias: Optional[torch.Tensor] = None) -> "VQLinear":
-        """Quantises a dense [out_features, in_features] weight (on its CUDA device) with k-means."""
-        from .quantize import kmeans_quantize
-        idx, cb = kmeans_quantize(weight, v=v, entries=entries, rows_per_codebook=rows_per_codebook, iters=iters, seed=seed)
+                    iters: int = 10, seed: int = 0, bias: Optional[torch.Tensor] = None, stages: int = 1) -> "VQLinear":
+        """Quantises a dense [out_features, in_features] weight (on its CUDA device) with k-means; ``stages`` > 1
+        gives residual weights (every further stage quantises what the stages before it left over)."""
+        from .quantize import kmeans_quantize, kmeans_quantize_residual
+        if stages > 1:
+            idx, cb = kmeans_quantize_residual(weight, stages=stages, v=v, entries=entries, rows_per_codebook=rows_per_codebook,
+                                               iters=iters, seed=seed)
+        else:
+            idx, cb = kmeans_quantize(weight, v=v, entries=entries, rows_per_codebook=rows_per_codebook, iters=iters, seed=seed)
         return cls(idx, cb, rows_per_codebook, bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -97,18 +124,22 @@ class VQLinear(nn.Module):
         x2 = x.reshape(-1, self.in_features)
         if x2.dtype != torch.float16:
             x2 = x2.to(torch.float16)
-        y = torch.ops.vq_gemm_b200.vq_linear(x2.contiguous(), self.indices, self.codebook, self.rows_per_codebook)
+        op = torch.ops.vq_gemm_b200.vq_linear_residual if self.residual else torch.ops.vq_gemm_b200.vq_linear
+        y = op(x2.contiguous(), self.indices, self.codebook, self.rows_per_codebook)
         if self.bias is not None:
             y = y + self.bias
         return y.reshape(*lead, self.out_features)
 
     def dequantized_weight(self) -> torch.Tensor:
         """The dense fp16 [out_features, in_features] weight this layer stands for (bit-exact gather)."""
+        if self.residual:
+            return ops.dequant_residual(self.indices, self.codebook, rows_per_codebook=self.rows_per_codebook)
         return ops.dequant(self.indices, self.codebook, rows_per_codebook=self.rows_per_codebook)
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, v={self.v}, "
-                f"entries={self.codebook.shape[1]}, rows_per_codebook={self.rows_per_codebook}, bias={self.bias is not None}")
+                f"entries={self.codebook.shape[-2]}, rows_per_codebook={self.rows_per_codebook}, "
+                f"stages={self.indices.shape[0] if self.residual else 1}, bias={self.bias is not None}")
 
 
 class VQGatedUp(nn.Module):

@@ -105,6 +105,32 @@ def kmeans_quantize(weight: torch.Tensor, *, v: int = 8, entries: int = 256, row
     return idx, cb
 
 
+def kmeans_quantize_residual(weight: torch.Tensor, *, stages: int = 2, v: int = 8, entries: int = 256,
+                             rows_per_codebook: int = 128, iters: int = 10, seed: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Residual (multi-codebook) quantisation: stage 0 quantises the weight, every further stage quantises what the
+    stages before it left over, so that ``W ~ fp16(... fp16(cb_0[idx_0] + cb_1[idx_1]) ...)`` -- the running fp16 sum
+    the residual format is defined by.  Returns (indices [S, N, K/v], codebook [S, G, entries, v])."""
+    from .ops import dequant_residual
+    if stages < 1 or stages > 8:
+        raise RuntimeError("stages must be between 1 and 8")
+    weight = weight.contiguous()
+    idx_all = cb_all = None
+    target = weight
+    for s in range(stages):
+        idx, cb = kmeans_quantize(target, v=v, entries=entries, rows_per_codebook=rows_per_codebook, iters=iters, seed=seed + s)
+        if idx_all is None:
+            idx_all = torch.empty((stages,) + tuple(idx.shape), dtype=idx.dtype, device=idx.device)
+            cb_all = torch.empty((stages,) + tuple(cb.shape), dtype=cb.dtype, device=cb.device)
+        # contiguous same-type device copies are plain stream-ordered memory copies, which the product kernels'
+        # early weight reads are ordered against (unlike a kernel's writes)
+        idx_all[s].copy_(idx)
+        cb_all[s].copy_(cb)
+        if s + 1 < stages:
+            so_far = dequant_residual(idx_all[:s + 1], cb_all[:s + 1], rows_per_codebook=rows_per_codebook)
+            target = (weight.float() - so_far.float()).half()
+    return idx_all, cb_all
+
+
 def pack12(indices: torch.Tensor) -> torch.Tensor:
     """int16/uint16 indices < 4096, even count per row -> uint8 [..., 3/2 * last]."""
     lib = _lib.load()

@@ -359,6 +359,59 @@ def _residual(V, peaks):
             "stages": S, "us": round(ms * 1e3, 1), "tflops": round(tf, 1), "frac": round(tf / peaks["tflops"], 4)}
 
 
+def _dequant_rates(V, peaks):
+    """The bit-exact dequantisation kernels against the HBM roofline: algorithmic bytes (indices + codebooks + the
+    fp16 weights written) per second, launches back to back over a ring of outputs larger than L2 (so that every
+    launch also pays for the write-back of the one before it)."""
+    rows = []
+
+    def timed(call, ring):
+        for i in range(2 * ring):
+            call(i)
+        e0, e1 = _events()
+        torch.cuda.synchronize()
+        n = 4 * ring
+        e0.record()
+        for i in range(n):
+            call(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for name, (N, K, v, C, rpc, S, dt) in {
+            "c5 weights": (28672, 8192, 8, 256, 128, 1, torch.uint8),
+            "c4 weights": (14336, 4096, 4, 256, 128, 1, torch.uint8),
+            "c3 weights": (8192, 8192, 8, 4096, 0, 1, torch.int16),
+            "c5 weights, 2 residual stages": (28672, 8192, 8, 256, 128, 2, torch.uint8)}.items():
+        G = 1 if rpc == 0 else N // rpc
+        idx = torch.randint(0, C, (S, N, K // v), device="cuda", generator=g, dtype=torch.int32).to(dt)
+        cb = (torch.randn(S, G, C, v, device="cuda", generator=g) * 0.02).half()
+        ring = max(2, int(600e6 // (N * K * 2)) + 1)
+        outs = [torch.empty(N, K, dtype=torch.float16, device="cuda") for _ in range(ring)]
+        idxs = [idx.clone() for _ in range(ring)]
+        if S == 1:
+            ms = timed(lambda i: V.dequant(idxs[i % ring][0], cb[0], rows_per_codebook=rpc, out=outs[i % ring]), ring)
+        else:
+            ms = timed(lambda i: V.dequant_residual(idxs[i % ring], cb, rows_per_codebook=rpc, out=outs[i % ring]), ring)
+        b = idx.numel() * idx.element_size() + cb.numel() * 2 + N * K * 2
+        rows.append({"what": name, "layout": "bl", "us": round(ms * 1e3, 1), "mb": round(b / 1e6, 1),
+                     "gbs": round(b / ms / 1e6), "frac_of_hbm": round(b / ms / 1e6 / peaks["hbm_gbs"], 3)})
+        del outs, idxs
+    for K, Nq in ((4096, 7168), (8192, 14336)):
+        w = torch.randint(0, 256, (K, Nq), device="cuda", generator=g, dtype=torch.int32).to(torch.uint8)
+        cb = (torch.randn(Nq // 4, 256, 2, device="cuda", generator=g) * 0.02).half()
+        ring = max(2, int(600e6 // (K * Nq * 4)) + 1)
+        outs = [torch.empty(K, 2 * Nq, dtype=torch.float16, device="cuda") for _ in range(ring)]
+        ws = [w.clone() for _ in range(ring)]
+        ms = timed(lambda i: V.dequant(ws[i % ring], cb, layout="ref", out=outs[i % ring]), ring)
+        b = w.numel() + cb.numel() * 2 + K * Nq * 4
+        rows.append({"what": f"reference format K={K} Nq={Nq}", "layout": "ref", "us": round(ms * 1e3, 1), "mb": round(b / 1e6, 1),
+                     "gbs": round(b / ms / 1e6), "frac_of_hbm": round(b / ms / 1e6 / peaks["hbm_gbs"], 3)})
+        del outs, ws
+    return rows
+
+
 def _quantizer(peaks, clocks_mhz):
     """Quantiser kernels on a layer of C4's size (N=14336, K=4096, v=4, 256 entries per 128 rows)."""
     from vq_gemm_b200 import quantize as VQ
@@ -731,6 +784,11 @@ def main():
                 detail["shapes"].append(det)
             except Exception as e:  # keep the headline line even if a side measurement fails
                 shapes.append({"workload": name, "error": repr(e)})
+        # the dequantisation kernels, HBM-bound, before anything heats the part up
+        try:
+            detail["dequant"] = _dequant_rates(V, peaks)
+        except Exception as e:
+            detail["dequant"] = {"error": repr(e)}
         # C4 in a short burst as well (25 launches); its alternative routes are timed with the long extras below
         try:
             compact, _ = _single_shape(V, CONFIGS["c4_prefill"], peaks, 20, args.warmup, alternatives=False)

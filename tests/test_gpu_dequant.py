@@ -51,11 +51,58 @@ def test_bl_random(N, K, v, C, rpc, dt):
     assert torch.equal(bits(w), bits(O.dequant_bl_layout(idx, cb, rpc)))
 
 
-@pytest.mark.parametrize("K,Nq", [(64, 64), (100, 12), (4096, 640)])
+@pytest.mark.parametrize("K,Nq", [(64, 64), (100, 12), (4096, 640), (72, 132), (8192, 8), (130, 260), (1, 4), (200, 1028)])
 def test_ref_random(K, Nq):
     _, w, cb = O.make_ref_inputs(1, K, Nq, seed=K + Nq)
     out = V.dequant(w.cuda(), cb.cuda(), layout="ref")
     assert torch.equal(bits(out), bits(O.dequant_ref_layout(w, cb)))
+
+
+def test_ref_misaligned_pointers_take_the_plain_kernel():
+    # index matrix starting on an odd byte: the streaming form (4-byte index words) must not be chosen
+    _, w, cb = O.make_ref_inputs(1, 96, 136, seed=5)
+    buf = torch.empty(w.numel() + 1, dtype=torch.uint8, device="cuda")
+    wd = buf[1:].view(96, 136)
+    wd.copy_(w)
+    assert wd.data_ptr() % 4 != 0
+    out = V.dequant(wd, cb.cuda(), layout="ref")
+    assert torch.equal(bits(out), bits(O.dequant_ref_layout(w, cb)))
+
+
+@pytest.mark.parametrize("K,Nq", [(64, 16), (256, 144), (512, 640), (192, 272), (4096, 128)])
+def test_ref_transposed_weights_through_an_identity_product(K, Nq):
+    # the K-major form of the dequantised reference weights only exists as the operand of the dense kernel:
+    # with X = I the product returns it element for element (one non-zero term per sum, exact in fp32)
+    _, w, cb = O.make_ref_inputs(1, K, Nq, seed=3 * K + Nq)
+    x = torch.eye(K, dtype=torch.float16)
+    y = V.vq_gemm(x.cuda(), w.cuda(), cb.cuda(), layout="ref")
+    assert torch.equal(y.cpu(), O.dequant_ref_layout(w, cb))
+
+
+@pytest.mark.parametrize("N,K,v,C,rpc,dt,S", [
+    (512, 1024, 8, 4096, 0, torch.int16, 1),      # streaming form, one 64 KiB image
+    (300, 512, 8, 1024, 100, torch.int16, 1),     # groups of 100 rows: block ranges cross group boundaries
+    (1000, 256, 4, 512, 0, torch.int16, 1),
+    (777, 64, 2, 2048, 77, torch.int16, 1),
+    (2048, 2048, 8, 256, 128, torch.uint8, 2),    # residual, replicated images
+    (640, 512, 4, 256, 128, torch.uint8, 3),
+    (200, 128, 2, 256, 0, torch.uint8, 2),
+    (256, 512, 8, 4096, 0, torch.int16, 2),       # residual with large codebooks: unreplicated images
+    (96, 256, 8, 8192, 0, torch.int16, 2),        # images do not fit: plain kernel
+    (64, 24, 8, 256, 0, torch.uint8, 2),
+    (512, 256, 4, 256, 128, torch.uint8, 4),
+    (256, 128, 8, 256, 64, torch.uint8, 5),       # more than four stages: plain kernel
+    (130, 64, 2, 300, 0, torch.int16, 8),
+])
+def test_bl_streaming_form(N, K, v, C, rpc, dt, S):
+    if S == 1:
+        _, idx, cb = O.make_bl_inputs(1, K, N, v, C, rpc, seed=N + K, idx_dtype=dt)
+        w = V.dequant(idx.cuda(), cb.cuda(), rows_per_codebook=rpc)
+        assert torch.equal(bits(w), bits(O.dequant_bl_layout(idx, cb, rpc)))
+    else:
+        _, idx, cb = O.make_residual_inputs(1, K, N, v, C, rpc, S, seed=N + K, idx_dtype=dt)
+        w = V.dequant_residual(idx.cuda(), cb.cuda(), rows_per_codebook=rpc)
+        assert torch.equal(bits(w), bits(O.dequant_bl_residual(idx, cb, rpc)))
 
 
 def test_empty():

@@ -9,6 +9,12 @@
 
 namespace vqg {
 
+__device__ __forceinline__ uint32_t hadd2_u32(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
 template <int V> struct Entry;
 template <> struct Entry<2> { using T = uint32_t; };
 template <> struct Entry<4> { using T = uint2; };
@@ -43,60 +49,145 @@ __global__ void __launch_bounds__(256) dequant_bl_kernel(const IdxT* __restrict_
   }
 }
 
-// Fast path: every thread produces 16 output bytes (8/V indices) so that a warp's stores are one
-// contiguous 512-byte run; the codebook sits in shared memory replicated to fill 128-byte lines
-// (entry c, replica r at byte c*128 + r*2V, lane uses replica lane % (64/V)), so lookups are
-// bank-conflict free.  Needs C*128 bytes of shared memory (C <= 256 here) and K/V a multiple of 8/V.
-template <int V, typename IdxT>
-__global__ void __launch_bounds__(256) dequant_bl_fast_kernel(const IdxT* __restrict__ idx,
-                                                              const __half* __restrict__ cb,
-                                                              __half* __restrict__ w, int N, int K, int C,
-                                                              int rows_per_cb, int rows_per_block) {
-  using E = typename Entry<V>::T;
-  constexpr int IPT = 8 / V;                 // indices per thread (16 output bytes)
-  constexpr int REPS = 64 / V;               // replicas per 128-byte line
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int J = K / V;
-  const int row0 = blockIdx.x * rows_per_block;
-  const int group = row0 / rows_per_cb;
-  const E* cbg = reinterpret_cast<const E*>(cb) + static_cast<size_t>(group) * C;
-  E* img = reinterpret_cast<E*>(smem_raw);
-  for (int i = threadIdx.x; i < C * REPS; i += blockDim.x) img[i] = __ldg(cbg + i / REPS);
-  __syncthreads();
-  const E* mine = img + (threadIdx.x & (REPS - 1));
-  const int rows = min(rows_per_block, N - row0);
-  const long long total = static_cast<long long>(rows) * (J / IPT);   // 16-byte outputs
-  const IdxT* ip = idx + static_cast<size_t>(row0) * J;
-  uint4* op = reinterpret_cast<uint4*>(w + static_cast<size_t>(row0) * K);
-#pragma unroll 4
-  for (long long i = threadIdx.x; i < total; i += blockDim.x) {
-    uint4 out;
-    if constexpr (V == 8) {
-      out = *reinterpret_cast<const uint4*>(mine + static_cast<uint32_t>(ip[i]) * REPS);
-    } else if constexpr (V == 4) {
-      uint32_t c0, c1;
-      if constexpr (sizeof(IdxT) == 1) {
-        const uint16_t two = __ldg(reinterpret_cast<const uint16_t*>(ip) + i);
-        c0 = two & 0xffu; c1 = two >> 8;
-      } else {
-        const uint32_t two = __ldg(reinterpret_cast<const uint32_t*>(ip) + i);
-        c0 = two & 0xffffu; c1 = two >> 16;
-      }
-      const uint2 e0 = mine[c0 * REPS], e1 = mine[c1 * REPS];
-      out = make_uint4(e0.x, e0.y, e1.x, e1.y);
+// Streaming form, the one normally taken: plain weights (STAGES = 1) and residual weights (STAGES codebook arrays
+// and index planes, entries added one after the other in fp16 -- HADD2, round to nearest even, which is the
+// residual format's rule).  A block owns a contiguous range of rows, so it rebuilds its
+// shared-memory images only when the range crosses into the next codebook group; an image holds every entry
+// `reps` times side by side (entry c, replica r at (c * reps + r) * 2V bytes; a lane uses replica lane % reps),
+// which makes the lookups conflict-free when reps * 2V = 128 and merely less conflicted when the codebook is too
+// large for that.  16 output bytes per thread and step; a warp's stores are one contiguous 512-byte run.
+template <int V, typename IdxT> struct IdxWord;                 // the 8/V indices behind 16 output bytes, as one load
+template <> struct IdxWord<8, uint8_t> { using T = uint8_t; };
+template <> struct IdxWord<8, uint16_t> { using T = uint16_t; };
+template <> struct IdxWord<4, uint8_t> { using T = uint16_t; };
+template <> struct IdxWord<4, uint16_t> { using T = uint32_t; };
+template <> struct IdxWord<2, uint8_t> { using T = uint32_t; };
+template <> struct IdxWord<2, uint16_t> { using T = uint2; };
+
+template <int V, typename IdxT, typename W>
+__device__ __forceinline__ uint4 lookup16(const typename Entry<V>::T* tab, W word, int reps) {
+  if constexpr (V == 8) {
+    return tab[static_cast<uint32_t>(word) * reps];
+  } else if constexpr (V == 4) {
+    uint32_t c0, c1;
+    if constexpr (sizeof(IdxT) == 1) { c0 = word & 0xffu; c1 = word >> 8; }
+    else { c0 = word & 0xffffu; c1 = word >> 16; }
+    const uint2 e0 = tab[c0 * reps], e1 = tab[c1 * reps];
+    return make_uint4(e0.x, e0.y, e1.x, e1.y);
+  } else {
+    uint32_t c[4];
+    if constexpr (sizeof(IdxT) == 1) {
+      c[0] = word & 0xffu; c[1] = (word >> 8) & 0xffu; c[2] = (word >> 16) & 0xffu; c[3] = word >> 24;
     } else {
-      uint32_t c[4];
-      if constexpr (sizeof(IdxT) == 1) {
-        const uint32_t four = __ldg(reinterpret_cast<const uint32_t*>(ip) + i);
-        c[0] = four & 0xffu; c[1] = (four >> 8) & 0xffu; c[2] = (four >> 16) & 0xffu; c[3] = four >> 24;
-      } else {
-        const uint2 four = __ldg(reinterpret_cast<const uint2*>(ip) + i);
-        c[0] = four.x & 0xffffu; c[1] = four.x >> 16; c[2] = four.y & 0xffffu; c[3] = four.y >> 16;
-      }
-      out = make_uint4(mine[c[0] * REPS], mine[c[1] * REPS], mine[c[2] * REPS], mine[c[3] * REPS]);
+      c[0] = word.x & 0xffffu; c[1] = word.x >> 16; c[2] = word.y & 0xffffu; c[3] = word.y >> 16;
     }
-    __stcs(op + i, out);
+    return make_uint4(tab[c[0] * reps], tab[c[1] * reps], tab[c[2] * reps], tab[c[3] * reps]);
   }
+}
+
+// STAGES is a template parameter so that the index loads of a step's four outputs and all their stages are issued
+// before the first lookup (with a run-time stage count the loads of one output wait for the lookups of the last).
+template <int V, typename IdxT, int STAGES>
+__global__ void __launch_bounds__(512) dequant_bl_stream_kernel(const IdxT* __restrict__ idx, const __half* __restrict__ cb,
+                                                                __half* __restrict__ w, int N, int K, int C, int rows_per_cb,
+                                                                int reps) {
+  using E = typename Entry<V>::T;
+  using W = typename IdxWord<V, IdxT>::T;
+  constexpr int IPT = 8 / V;                   // indices per 16 output bytes
+  constexpr int U = 4;                         // outputs per thread and step
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  E* img = reinterpret_cast<E*>(smem_raw);
+  const int J = K / V;
+  const int JO = J / IPT;                      // 16-byte outputs per row
+  const int groups = (N + rows_per_cb - 1) / rows_per_cb;
+  const size_t plane = static_cast<size_t>(N) * JO;          // index words per stage
+  const int img_entries = C * reps;                          // entries of one stage's image
+  const int row_lo = static_cast<int>(static_cast<long long>(N) * blockIdx.x / gridDim.x);
+  const int row_hi = static_cast<int>(static_cast<long long>(N) * (blockIdx.x + 1) / gridDim.x);
+  const E* mine = img + (threadIdx.x & (reps - 1));
+  const int nt = blockDim.x;
+  for (int r0 = row_lo; r0 < row_hi;) {
+    const int g = r0 / rows_per_cb;
+    const int r1 = min(row_hi, (g + 1) * rows_per_cb);
+    __syncthreads();                           // everybody is done with the previous group's images
+#pragma unroll
+    for (int st = 0; st < STAGES; ++st) {
+      const E* src = reinterpret_cast<const E*>(cb) + (static_cast<size_t>(st) * groups + g) * C;
+      E* dst = img + static_cast<size_t>(st) * img_entries;
+      for (int e = threadIdx.x; e < img_entries; e += nt) dst[e] = __ldg(src + e / reps);
+    }
+    __syncthreads();
+    const long long total = static_cast<long long>(r1 - r0) * JO;
+    const W* ip = reinterpret_cast<const W*>(idx) + static_cast<size_t>(r0) * JO;
+    uint4* op = reinterpret_cast<uint4*>(w + static_cast<size_t>(r0) * K);
+    for (long long i0 = threadIdx.x; i0 < total; i0 += static_cast<long long>(U) * nt) {
+      W word[U][STAGES];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + static_cast<long long>(u) * nt;
+#pragma unroll
+        for (int st = 0; st < STAGES; ++st)
+          if (i < total) word[u][st] = __ldg(ip + static_cast<size_t>(st) * plane + i);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + static_cast<long long>(u) * nt;
+        if (i < total) {
+          uint4 out = lookup16<V, IdxT, W>(mine, word[u][0], reps);
+#pragma unroll
+          for (int st = 1; st < STAGES; ++st) {
+            const uint4 e = lookup16<V, IdxT, W>(mine + static_cast<size_t>(st) * img_entries, word[u][st], reps);
+            out.x = hadd2_u32(out.x, e.x); out.y = hadd2_u32(out.y, e.y);
+            out.z = hadd2_u32(out.z, e.z); out.w = hadd2_u32(out.w, e.w);
+          }
+          __stcs(op + i, out);
+        }
+      }
+    }
+    r0 = r1;
+  }
+}
+
+// Launches the streaming kernel when its conditions hold (returns false otherwise, nothing launched):
+// v in {2,4,8}, whole 16-byte outputs per row, pointers aligned to what the kernel reads and writes at once,
+// and the stages' images fit the shared memory of a block.
+static bool launch_stream(const void* idx, const __half* cb, __half* w, int N, int K, int v, int C, int idx_bytes,
+                          int rows_per_cb, int stages, cudaStream_t s) {
+  if (!(v == 2 || v == 4 || v == 8) || (idx_bytes != 1 && idx_bytes != 2) || stages < 1 || stages > 4) return false;
+  const int ipt = 8 / v;
+  if ((K / v) % ipt != 0) return false;
+  if (reinterpret_cast<uintptr_t>(w) % 16 || reinterpret_cast<uintptr_t>(cb) % (2 * v) ||
+      reinterpret_cast<uintptr_t>(idx) % static_cast<uintptr_t>(ipt * idx_bytes))
+    return false;
+  // a plane of indices must keep that alignment too
+  if ((static_cast<size_t>(N) * (K / v) * idx_bytes) % static_cast<size_t>(ipt * idx_bytes) != 0) return false;
+  const size_t one = static_cast<size_t>(stages) * C * v * 2;      // unreplicated images
+  if (one > 200 * 1024) return false;
+  int reps = 64 / v;
+  while (reps > 1 && one * reps > 72 * 1024) reps >>= 1;
+  const size_t smem = one * reps;
+  // two blocks of 512 threads per SM measured best (89 us for 470 MB of weights; three blocks 95, four 102, one 119):
+  // enough loads in flight, few enough write streams for the memory's open pages
+  int per_sm = static_cast<int>((220 * 1024) / (smem + 1024));
+  per_sm = per_sm > 2 ? 2 : (per_sm < 1 ? 1 : per_sm);
+  int blocks = 148 * per_sm;
+  if (blocks > N) blocks = N;
+#define VQG_DQS2(V_, T_, S_)                                                                                  \
+  do {                                                                                                        \
+    auto k = dequant_bl_stream_kernel<V_, T_, S_>;                                                            \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    k<<<blocks, 512, smem, s>>>(static_cast<const T_*>(idx), cb, w, N, K, C, rows_per_cb, reps);              \
+  } while (0)
+#define VQG_DQS(V_, T_)                                                                                       \
+  do {                                                                                                        \
+    if (stages == 1) VQG_DQS2(V_, T_, 1); else if (stages == 2) VQG_DQS2(V_, T_, 2);                          \
+    else if (stages == 3) VQG_DQS2(V_, T_, 3); else VQG_DQS2(V_, T_, 4);                                      \
+  } while (0)
+  if (idx_bytes == 1) { if (v == 2) VQG_DQS(2, uint8_t); else if (v == 4) VQG_DQS(4, uint8_t); else VQG_DQS(8, uint8_t); }
+  else { if (v == 2) VQG_DQS(2, uint16_t); else if (v == 4) VQG_DQS(4, uint16_t); else VQG_DQS(8, uint16_t); }
+#undef VQG_DQS2
+#undef VQG_DQS
+  return true;
 }
 
 int launch_dequant_bl(const void* idx, const __half* cb, __half* w, int N, int K, int v, int C,
@@ -113,17 +204,7 @@ int launch_dequant_bl(const void* idx, const __half* cb, __half* w, int N, int K
   while (rpb >= 16 && (single || rows_per_cb % (rpb * 2) == 0) && (N / (rpb * 2)) >= 148 * 16) rpb *= 2;
   const int blocks = (N + rpb - 1) / rpb;
   const size_t cb_bytes = static_cast<size_t>(C) * v * 2;
-  // fast path: replicated image (C * 128 bytes), 16 output bytes per thread
-  if ((v == 2 || v == 4 || v == 8) && C <= 256 && (K / v) % (8 / v) == 0 && (single || rows_per_cb % 16 == 0) &&
-      reinterpret_cast<uintptr_t>(idx) % 8 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
-    int rows = 16;
-    while ((single || rows_per_cb % (rows * 2) == 0) && (N / (rows * 2)) >= 148 * 8) rows *= 2;
-    const int nblocks = (N + rows - 1) / rows;
-    const size_t sm = static_cast<size_t>(C) * 128;
-#define VQG_DQF(V_, T_) dequant_bl_fast_kernel<V_, T_><<<nblocks, 256, sm, s>>>(static_cast<const T_*>(idx), cb, w, N, K, C, rows_per_cb, rows)
-    if (idx_bytes == 1) { if (v == 2) VQG_DQF(2, uint8_t); else if (v == 4) VQG_DQF(4, uint8_t); else VQG_DQF(8, uint8_t); }
-    else { if (v == 2) VQG_DQF(2, uint16_t); else if (v == 4) VQG_DQF(4, uint16_t); else VQG_DQF(8, uint16_t); }
-#undef VQG_DQF
+  if (launch_stream(idx, cb, w, N, K, v, C, idx_bytes, rows_per_cb, 1, s)) {
     count_launch();
     return cuda_status(cudaGetLastError());
   }
@@ -195,9 +276,141 @@ __global__ void __launch_bounds__(256) dequant_ref_t_kernel(const uint8_t* __res
   }
 }
 
+// REF layout, streaming form of both orientations.  The reference's format has one 256-entry codebook of 4-byte
+// entries per 4 index columns, so a lane that owns ONE codebook (4 consecutive index columns = one 32-bit word of
+// an index row) finds its entries in the image [entry c][codebook q] at word c * 32 + q: lane q always reads bank
+// q, whatever the indices are, and a warp covers a strip of 32 codebooks = 128 index columns = 256 output columns.
+// The image is the strip's 32 KiB of codebooks transposed, nothing is replicated.
+//   natural    Wdec [K, 2 Nq]: a lane turns one index word into 16 output bytes; a warp writes 512 contiguous bytes.
+//   transposed WdecT [2 Nq, K]: tiles of 64 k.  A lane looks up two k rows (4 columns each), pairs the halves into
+//              the 32-bit words (k, k+1) of its 8 output rows and parks them in a [256 rows][32 words] tile; at step s
+//              lane l works on k pair (s + l) % 32, which keeps the index reads (bank l), the lookups (bank l) and
+//              the tile writes (bank (s + l) % 32) conflict-free.  The tile then leaves in 16-byte stores, 128
+//              contiguous bytes per output row.
+// A block walks a contiguous range of (strip, 64-k tile) units and rebuilds the image when the strip changes.
+constexpr int kRefStripCols = 128;             // index columns per strip
+constexpr int kRefTileK = 64;
+
+__device__ __forceinline__ void ref_build_image(const uint32_t* __restrict__ table, uint32_t* image, uint32_t* stage,
+                                                int q0, int qs) {
+  // codebooks q0 .. q0+qs-1 (1 KiB each, contiguous) -> stage[q][c], then stage -> image[c][q] along diagonals
+  const uint4* src = reinterpret_cast<const uint4*>(table + (static_cast<size_t>(q0) << 8));
+  uint4* dst = reinterpret_cast<uint4*>(stage);
+  for (int e = threadIdx.x; e < qs * 64; e += blockDim.x) dst[e] = __ldg(src + e);
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int cb0 = warp * 32; cb0 < 256; cb0 += nwarps * 32) {
+    const int c = cb0 + lane;
+#pragma unroll 8
+    for (int st = 0; st < 32; ++st) {
+      const int q = (lane + st) & 31;
+      image[c * 32 + q] = q < qs ? stage[q * 256 + c] : 0u;
+    }
+  }
+  __syncthreads();
+}
+
+template <bool TRANSPOSED, int NT>
+__global__ void __launch_bounds__(NT) dequant_ref_strip_kernel(const uint8_t* __restrict__ w, const __half* __restrict__ cb,
+                                                                __half* __restrict__ out, int Nq, int K, int strips,
+                                                                int tiles_per_strip) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint32_t* image = reinterpret_cast<uint32_t*>(smem_raw);                 // [256][32] words
+  uint32_t* otile = image + 256 * 32;                                      // [256 rows][32 words]; staging of the build
+  uint32_t* itile = otile + 256 * 32;                                      // [64 k][32 words] (transposed form only)
+  const uint32_t* table = reinterpret_cast<const uint32_t*>(cb);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const long long units = static_cast<long long>(strips) * tiles_per_strip;
+  const long long u_lo = units * blockIdx.x / gridDim.x, u_hi = units * (blockIdx.x + 1) / gridDim.x;
+  int have = -1;
+  for (long long u = u_lo; u < u_hi; ++u) {
+    const int strip = static_cast<int>(u / tiles_per_strip);
+    const int k0 = static_cast<int>(u % tiles_per_strip) * kRefTileK;
+    const int k1 = min(K, k0 + kRefTileK);
+    const int nq0 = strip * kRefStripCols;
+    const int nqs = min(kRefStripCols, Nq - nq0);                          // a multiple of 4
+    if (strip != have) {
+      __syncthreads();                                                     // the tile is free (previous unit's stores read it)
+      ref_build_image(table, image, otile, nq0 >> 2, nqs >> 2);
+      have = strip;
+    }
+    if constexpr (!TRANSPOSED) {
+      if (4 * lane < nqs) {
+#pragma unroll 4
+        for (int k = k0 + warp; k < k1; k += nwarps) {
+          const size_t at = static_cast<size_t>(k) * Nq + nq0 + 4 * lane;  // index byte = output word
+          const uint32_t four = __ldg(reinterpret_cast<const uint32_t*>(w + at));
+          uint4 o;
+          o.x = image[(four & 0xffu) * 32 + lane];
+          o.y = image[((four >> 8) & 0xffu) * 32 + lane];
+          o.z = image[((four >> 16) & 0xffu) * 32 + lane];
+          o.w = image[(four >> 24) * 32 + lane];
+          __stcs(reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + at), o);
+        }
+      }
+    } else {
+      // (1) index tile, coalesced rows of up to 128 bytes
+      constexpr int NW = NT / 32;
+#pragma unroll
+      for (int i = 0; i < kRefTileK / NW; ++i) {
+        const int r = warp + NW * i, k = k0 + r;
+        uint32_t v = 0;
+        if (k < k1 && 4 * lane < nqs) v = __ldg(reinterpret_cast<const uint32_t*>(w + static_cast<size_t>(k) * Nq + nq0 + 4 * lane));
+        itile[r * 32 + lane] = v;
+      }
+      __syncthreads();
+      // (2) lookups along diagonals
+#pragma unroll
+      for (int i = 0; i < 32 / NW; ++i) {
+        const int kp = ((32 / NW) * warp + i + lane) & 31;
+        const uint32_t a = itile[(2 * kp) * 32 + lane], b = itile[(2 * kp + 1) * 32 + lane];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t ea = image[((a >> (8 * j)) & 0xffu) * 32 + lane];
+          const uint32_t eb = image[((b >> (8 * j)) & 0xffu) * 32 + lane];
+          otile[(8 * lane + 2 * j) * 32 + kp] = __byte_perm(ea, eb, 0x5410);       // output row 2n  : halves r = 0 of k, k+1
+          otile[(8 * lane + 2 * j + 1) * 32 + kp] = __byte_perm(ea, eb, 0x7632);   // output row 2n+1: halves r = 1
+        }
+      }
+      __syncthreads();
+      // (3) the tile leaves: 8 lanes write the 128 bytes of one output row
+#pragma unroll
+      for (int i = 0; i < 2048 / NT; ++i) {
+        const int id = threadIdx.x + NT * i;
+        const int row = id >> 3, c16 = id & 7;
+        const int k = k0 + 8 * c16;
+        if (row < 2 * nqs && k < k1) {
+          const uint4 v = *reinterpret_cast<const uint4*>(otile + row * 32 + 4 * c16);
+          __stcs(reinterpret_cast<uint4*>(out + static_cast<size_t>(2 * nq0 + row) * K + k), v);
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
 int launch_dequant_ref(const uint8_t* w, const __half* cb, __half* out, int Nq, int K, bool transposed,
                        cudaStream_t s) {
   if (Nq == 0 || K == 0) return VQG_OK;
+  // streaming form: index rows start on 4-byte boundaries (Nq % 4 == 0 holds for the format), 16-byte stores
+  if (Nq % 4 == 0 && reinterpret_cast<uintptr_t>(w) % 4 == 0 && reinterpret_cast<uintptr_t>(cb) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(out) % 16 == 0 && (!transposed || K % 8 == 0)) {
+    const int strips = (Nq + kRefStripCols - 1) / kRefStripCols;
+    const int tiles = (K + kRefTileK - 1) / kRefTileK;
+    const long long units = static_cast<long long>(strips) * tiles;
+    const int blocks = static_cast<int>(units < 148 * 3 ? units : 148 * 3);   // three blocks of 512 threads per SM
+    const size_t smem = transposed ? (32 + 32 + 8) * 1024 : (32 + 32) * 1024;
+#define VQG_DQREF(T_, NT_)                                                                              \
+  do {                                                                                                  \
+    auto k = dequant_ref_strip_kernel<T_, NT_>;                                                         \
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));       \
+    k<<<blocks, NT_, smem, s>>>(w, cb, out, Nq, K, strips, tiles);                                      \
+  } while (0)
+    if (transposed) VQG_DQREF(true, 512); else VQG_DQREF(false, 512);
+#undef VQG_DQREF
+    count_launch();
+    return cuda_status(cudaGetLastError());
+  }
   if (transposed) {
     dim3 grid((Nq + 63) / 64, (K + 63) / 64);
     dequant_ref_t_kernel<<<grid, 256, 0, s>>>(w, cb, out, Nq, K);
@@ -270,6 +483,10 @@ int launch_dequant_bl_residual(const void* idx, const __half* cb, __half* w, int
   if (reinterpret_cast<uintptr_t>(cb) % 4 || reinterpret_cast<uintptr_t>(w) % 4 ||
       reinterpret_cast<uintptr_t>(idx) % static_cast<uintptr_t>(idx_bytes > 0 ? idx_bytes : 1))
     return VQG_ERR_BAD_ARG;
+  if (launch_stream(idx, cb, w, N, K, v, C, idx_bytes, rows_per_cb, stages, s)) {
+    count_launch();
+    return cuda_status(cudaGetLastError());
+  }
   const long long total = static_cast<long long>(N) * (K / v);
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;

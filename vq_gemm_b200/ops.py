@@ -158,14 +158,23 @@ def vq_gemm_residual(x: torch.Tensor, indices: torch.Tensor, codebook: torch.Ten
     return out
 
 
-def dequant_residual(indices: torch.Tensor, codebook: torch.Tensor, *, rows_per_codebook: Optional[int] = None) -> torch.Tensor:
+def _weights_out(out: Optional[torch.Tensor], shape, dev) -> torch.Tensor:
+    if out is None:
+        return torch.empty(shape, dtype=torch.float16, device=dev)
+    if tuple(out.shape) != tuple(shape) or out.dtype != torch.float16 or out.device != dev or not out.is_contiguous():
+        raise RuntimeError(f"out must be a contiguous float16 tensor of shape {tuple(shape)} on {dev}")
+    return out
+
+
+def dequant_residual(indices: torch.Tensor, codebook: torch.Tensor, *, rows_per_codebook: Optional[int] = None,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Dequantised residual weights [N, K], bit-exact by the format's rule."""
     lib = _lib.load()
     dev = _require_cuda(indices, codebook)
     if codebook.dtype != torch.float16:
         raise RuntimeError("codebook must be float16")
     S, N, J, G, C, v, rpc = _residual_dims(indices, codebook, rows_per_codebook)
-    out = torch.empty((N, J * v), dtype=torch.float16, device=dev)
+    out = _weights_out(out, (N, J * v), dev)
     with torch.cuda.device(dev):
         st = lib.vqg_dequant_residual(indices.data_ptr(), codebook.data_ptr(), out.data_ptr(), N, J * v, v, C,
                                       _idx_bytes(indices), rpc, S, _stream_ptr(dev))
@@ -245,7 +254,7 @@ def gemm(input: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 
 def dequant(indices: torch.Tensor, codebook: torch.Tensor, *, rows_per_codebook: Optional[int] = None,
-            layout: str = "bl") -> torch.Tensor:
+            layout: str = "bl", out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Dequantised weights: ``[N, K]`` for the generalised format, ``[K, 2*Nq]`` for the reference's."""
     lib = _lib.load()
     dev = _require_cuda(indices, codebook)
@@ -259,11 +268,11 @@ def dequant(indices: torch.Tensor, codebook: torch.Tensor, *, rows_per_codebook:
         K = J * v
         if rows_per_codebook is None:
             rows_per_codebook = 0 if G == 1 else N // G
-        out = torch.empty((N, K), dtype=torch.float16, device=dev)
+        out = _weights_out(out, (N, K), dev)
         args = (N, K, v, C, ib, rows_per_codebook, _lib.LAYOUT_BL)
     elif layout == "ref":
         K, Nq = indices.shape
-        out = torch.empty((K, 2 * Nq), dtype=torch.float16, device=dev)
+        out = _weights_out(out, (K, 2 * Nq), dev)
         args = (2 * Nq, K, 2, 256, ib, 0, _lib.LAYOUT_REF)
     else:
         raise RuntimeError(f"unknown layout {layout!r}")

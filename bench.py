@@ -33,7 +33,8 @@ each rank owns N/G output columns and the fp16 output is assembled on every rank
 The line ends with the compact per-configuration table (``shapes``); long per-kernel detail is under ``detail``.
 
 ``--profile-case NAME --launches n [--path p]`` runs n launches of one configuration and exits: the command to
-put under a profiler.
+put under a profiler (p: a product route, or ``dequant`` / ``dequant_ref`` / ``e2e_ref`` for the dequantisation kernels
+and the product on data in the reference's format).
 
 ``--impl reference`` times the reference's torch path restated for CPU (oracle/vq_oracle.py) on
 the host cores, same metric and workload, bounded sample per step.
@@ -685,8 +686,20 @@ def main():
         sc = CONFIGS[args.profile_case]
         x, idx, cb = make_inputs(sc, seed=0, device="cuda")
         y = None
+        if args.path in ("dequant_ref", "e2e_ref"):
+            # the configuration's M, K and N in the reference's own format: index matrix [K, N/2], a codebook per 8 outputs
+            g = torch.Generator(device="cuda").manual_seed(0)
+            w = torch.randint(0, 256, (sc.K, sc.N // 2), device="cuda", generator=g, dtype=torch.int32).to(torch.uint8)
+            cbr = (torch.randn(sc.N // 8, 256, 2, device="cuda", generator=g) * 0.02).half()
         for _ in range(args.launches):
-            y = V.vq_gemm(x, idx, cb, rows_per_codebook=sc.rows_per_codebook, layout="bl", path=args.path)
+            if args.path == "dequant":
+                y = V.dequant(idx, cb, rows_per_codebook=sc.rows_per_codebook)
+            elif args.path == "dequant_ref":
+                y = V.dequant(w, cbr, layout="ref")
+            elif args.path == "e2e_ref":
+                y = V.e2e_gemm(x, w, cbr)
+            else:
+                y = V.vq_gemm(x, idx, cb, rows_per_codebook=sc.rows_per_codebook, layout="bl", path=args.path)
         torch.cuda.synchronize()
         if V.device_status() != 0:
             raise SystemExit("device status word set")

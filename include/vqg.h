@@ -49,6 +49,11 @@ enum {
 
 enum { VQG_LAYOUT_BL = 0, VQG_LAYOUT_REF = 1 };
 
+/* idx_bytes value for 12-bit indices packed two to three bytes (bytes [a & 255, (a >> 8) | ((b & 15) << 4),
+ * b >> 4] for the pair a, b -- what vqg_pack12 writes).  1.5 bits per weight at v = 8 instead of the 2 bits
+ * of uint16 storage.  No counterpart in the reference (uint8 indices only). */
+#define VQG_IDX_PACKED12 12
+
 /* kernel selection for vqg_gemm_path(); VQG_PATH_AUTO is what vqg_gemm() uses */
 enum {
   VQG_PATH_AUTO = 0,
@@ -90,7 +95,10 @@ VQG_API int vqg_auto_path(int M, int N, int K, int v, int C, int idx_bytes, int 
  * (reference bind.cpp:3,7; host launchers strategy_2/bsz128/src.cu:255-316 and siblings).
  *   N                  output columns (BL: rows of idx; REF: 2*Nq)
  *   v, C               sub-vector length and codebook entries (REF: v=2, C=256)
- *   idx_bytes          1 (uint8) or 2 (uint16)
+ *   idx_bytes          1 (uint8), 2 (uint16), or VQG_IDX_PACKED12 (vqg_gemm, vqg_gemm_path, vqg_dequant,
+ *                      vqg_workspace_bytes, vqg_auto_path only; BL layout): two 12-bit indices in three
+ *                      bytes as vqg_pack12 writes them, K/v even, C <= 4096; a row of the index matrix
+ *                      is K/v * 3/2 bytes
  *   rows_per_codebook  BL: output rows sharing a codebook, 0 = one codebook for the matrix
  *                      REF: ignored (8 output columns per codebook)
  *   stream             cudaStream_t (NULL = legacy default stream, as the reference uses)

@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_PKG, "libvqg_b200.so")
 
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_LAUNCH, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE, ERR_NO_MEMORY = range(9)
 LAYOUT_BL, LAYOUT_REF = 0, 1
+IDX_PACKED12 = 12      # idx_bytes value: two 12-bit indices in three bytes
 PATH_AUTO, PATH_GENERIC, PATH_DECODE, PATH_TENSOR, PATH_TWO_PHASE, PATH_TENSOR_PAIR, PATH_TENSOR_TS, PATH_SMALL_TS = range(8)
 PATHS = {"auto": PATH_AUTO, "generic": PATH_GENERIC, "decode": PATH_DECODE, "tensor": PATH_TENSOR,
          "two_phase": PATH_TWO_PHASE, "tensor_pair": PATH_TENSOR_PAIR, "tensor_ts": PATH_TENSOR_TS, "small_ts": PATH_SMALL_TS}

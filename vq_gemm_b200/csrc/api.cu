@@ -66,8 +66,10 @@ namespace {
 
 bool aligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; }
 
+// `packed_ok`: the entry point also takes VQG_IDX_PACKED12 (two 12-bit indices in three bytes); only the plain
+// product and the dequantisation do.
 int check_common(const void* x, const void* idx, const void* cb, const void* y, int M, int N, int K, int v, int C,
-                 int idx_bytes, int layout) {
+                 int idx_bytes, int layout, bool packed_ok = false) {
   if (M < 0 || N < 0 || K < 0) return VQG_ERR_BAD_ARG;
   if (layout != VQG_LAYOUT_BL && layout != VQG_LAYOUT_REF) return VQG_ERR_BAD_ARG;
   if (M == 0 || N == 0) return VQG_OK;
@@ -78,6 +80,11 @@ int check_common(const void* x, const void* idx, const void* cb, const void* y, 
     if (N % 8 != 0) return VQG_ERR_BAD_ARG;  // 4 index columns (8 outputs) per codebook
   } else {
     if (v < 1 || C < 1) return VQG_ERR_BAD_ARG;
+    if (idx_bytes == VQG_IDX_PACKED12) {
+      if (!packed_ok) return VQG_ERR_UNSUPPORTED;
+      if (K % v != 0 || (K / v) % 2 != 0 || C > 4096) return VQG_ERR_BAD_ARG;   // pairs never straddle rows
+      return VQG_OK;
+    }
     if (idx_bytes != 1 && idx_bytes != 2) return VQG_ERR_UNSUPPORTED;
     if (K % v != 0) return VQG_ERR_BAD_ARG;
     if (idx_bytes == 1 && C > 256) return VQG_ERR_BAD_ARG;
@@ -106,6 +113,13 @@ int auto_path(const Problem& p, int layout) {
     return dense_supported(p.M, p.N, p.K) && p.M >= 32 ? VQG_PATH_TWO_PHASE : VQG_PATH_GENERIC;
   }
   if (p.K == 0) return VQG_PATH_GENERIC;
+  if (p.idx_bytes == VQG_IDX_PACKED12) {
+    // packed indices: the small-batch tensor-memory kernel unpacks them itself; larger batches dequantise first
+    if (p.M <= 128 && small_ts_supported(p)) return VQG_PATH_SMALL_TS;
+    if (dense_supported(p.M, p.N, p.K) && (p.v == 2 || p.v == 4 || p.v == 8) && aligned(p.cb, static_cast<size_t>(2 * p.v)))
+      return VQG_PATH_TWO_PHASE;
+    return VQG_PATH_GENERIC;
+  }
   // Measured routing (B200, CUDA-graph replay over index buffers larger than L2).  Register-level decode kernel:
   // fastest up to 8 batch rows on every matrix tried (4 MB ... 29 MB of indices, 256- and 4096-entry codebooks), and
   // up to 16 rows while K fits one chunk of its warps (K <= 4096) and the codebook its replicated image (C4 weights,
@@ -225,7 +239,7 @@ size_t vqg_workspace_bytes(int M, int N, int K, int v, int C, int idx_bytes, int
 int vqg_gemm_path(const void* x, const void* idx, const void* codebook, void* y, int M, int N, int K, int v, int C,
                   int idx_bytes, int rows_per_codebook, int layout, int path, void* workspace,
                   size_t workspace_bytes, void* stream) {
-  const int st = check_common(x, idx, codebook, y, M, N, K, v, C, idx_bytes, layout);
+  const int st = check_common(x, idx, codebook, y, M, N, K, v, C, idx_bytes, layout, /*packed_ok=*/true);
   if (st != VQG_OK) return st;
   Problem p = make_problem(x, idx, codebook, y, M, N, K, v, C, idx_bytes, rows_per_codebook, N);
   return run(p, layout, path, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
@@ -250,9 +264,15 @@ int vqg_dequant(const void* idx, const void* codebook, void* w_out, int N, int K
   }
   if (layout != VQG_LAYOUT_BL) return VQG_ERR_BAD_ARG;
   if (v < 1 || C < 1 || K % v != 0) return VQG_ERR_BAD_ARG;
-  if (idx_bytes != 1 && idx_bytes != 2) return VQG_ERR_UNSUPPORTED;
-  if (idx_bytes == 1 && C > 256) return VQG_ERR_BAD_ARG;
-  if (!aligned(w_out, 16) || !aligned(codebook, 16) || !aligned(idx, static_cast<size_t>(idx_bytes))) return VQG_ERR_BAD_ARG;
+  if (idx_bytes == VQG_IDX_PACKED12) {
+    if ((K / v) % 2 != 0 || C > 4096) return VQG_ERR_BAD_ARG;
+  } else {
+    if (idx_bytes != 1 && idx_bytes != 2) return VQG_ERR_UNSUPPORTED;
+    if (idx_bytes == 1 && C > 256) return VQG_ERR_BAD_ARG;
+  }
+  if (!aligned(w_out, 16) || !aligned(codebook, 16) ||
+      !aligned(idx, idx_bytes == VQG_IDX_PACKED12 ? 1 : static_cast<size_t>(idx_bytes)))
+    return VQG_ERR_BAD_ARG;
   const int rpc = (rows_per_codebook <= 0 || rows_per_codebook > N) ? N : rows_per_codebook;
   return launch_dequant_bl(idx, static_cast<const __half*>(codebook), static_cast<__half*>(w_out), N, K, v, C,
                            idx_bytes, rpc, s);

@@ -190,9 +190,85 @@ static bool launch_stream(const void* idx, const __half* cb, __half* w, int N, i
   return true;
 }
 
+// Packed 12-bit indices (two in three bytes): one thread per pair, i.e. three index bytes in and two entries
+// (4V bytes, contiguous) out; a warp reads 96 contiguous bytes and writes 64 V.  Same block schedule and images
+// as the streaming kernel above (rows are whole numbers of pairs, so a row range is a flat range of pairs).
+template <int V>
+__global__ void __launch_bounds__(512) dequant_bl_packed12_kernel(const uint8_t* __restrict__ idx, const __half* __restrict__ cb,
+                                                                  __half* __restrict__ w, int N, int K, int C, int rows_per_cb,
+                                                                  int reps) {
+  using E = typename Entry<V>::T;
+  constexpr int U = 4;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  E* img = reinterpret_cast<E*>(smem_raw);
+  const int JP = K / V / 2;                    // pairs per row
+  const int img_entries = C * reps;
+  const int row_lo = static_cast<int>(static_cast<long long>(N) * blockIdx.x / gridDim.x);
+  const int row_hi = static_cast<int>(static_cast<long long>(N) * (blockIdx.x + 1) / gridDim.x);
+  const E* mine = img + (threadIdx.x & (reps - 1));
+  const int nt = blockDim.x;
+  for (int r0 = row_lo; r0 < row_hi;) {
+    const int g = r0 / rows_per_cb;
+    const int r1 = min(row_hi, (g + 1) * rows_per_cb);
+    __syncthreads();
+    const E* src = reinterpret_cast<const E*>(cb) + static_cast<size_t>(g) * C;
+    for (int e = threadIdx.x; e < img_entries; e += nt) img[e] = __ldg(src + e / reps);
+    __syncthreads();
+    const long long total = static_cast<long long>(r1 - r0) * JP;
+    const uint8_t* ip = idx + static_cast<size_t>(r0) * JP * 3;
+    E* op = reinterpret_cast<E*>(w + static_cast<size_t>(r0) * K);
+    for (long long i0 = threadIdx.x; i0 < total; i0 += static_cast<long long>(U) * nt) {
+      uint32_t b[U][3];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + static_cast<long long>(u) * nt;
+        if (i < total) {
+          b[u][0] = __ldg(ip + 3 * i); b[u][1] = __ldg(ip + 3 * i + 1); b[u][2] = __ldg(ip + 3 * i + 2);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + static_cast<long long>(u) * nt;
+        if (i < total) {
+          const uint32_t c0 = b[u][0] | ((b[u][1] & 15u) << 8), c1 = (b[u][1] >> 4) | (b[u][2] << 4);
+          // 12 bits can name more entries than the codebook has: such an index (malformed input) reads entry 0
+          // instead of running past the image
+          __stcs(op + 2 * i, mine[(c0 < static_cast<uint32_t>(C) ? c0 : 0u) * reps]);
+          __stcs(op + 2 * i + 1, mine[(c1 < static_cast<uint32_t>(C) ? c1 : 0u) * reps]);
+        }
+      }
+    }
+    r0 = r1;
+  }
+}
+
+static int launch_packed12(const uint8_t* idx, const __half* cb, __half* w, int N, int K, int v, int C, int rows_per_cb,
+                           cudaStream_t s) {
+  if (!(v == 2 || v == 4 || v == 8) || (K / v) % 2 != 0 || C > 4096) return VQG_ERR_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(w) % (2 * v) || reinterpret_cast<uintptr_t>(cb) % (2 * v)) return VQG_ERR_BAD_ARG;
+  const size_t one = static_cast<size_t>(C) * v * 2;
+  int reps = 64 / v;
+  while (reps > 1 && one * reps > 72 * 1024) reps >>= 1;
+  const size_t smem = one * reps;
+  int blocks = 148 * 2;
+  if (blocks > N) blocks = N;
+#define VQG_DQP(V_)                                                                                           \
+  do {                                                                                                        \
+    auto k = dequant_bl_packed12_kernel<V_>;                                                                  \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    k<<<blocks, 512, smem, s>>>(idx, cb, w, N, K, C, rows_per_cb, reps);                                      \
+  } while (0)
+  if (v == 2) VQG_DQP(2); else if (v == 4) VQG_DQP(4); else VQG_DQP(8);
+#undef VQG_DQP
+  count_launch();
+  return cuda_status(cudaGetLastError());
+}
+
 int launch_dequant_bl(const void* idx, const __half* cb, __half* w, int N, int K, int v, int C,
                       int idx_bytes, int rows_per_cb, cudaStream_t s) {
   if (N == 0 || K == 0) return VQG_OK;
+  if (idx_bytes == VQG_IDX_PACKED12)
+    return launch_packed12(static_cast<const uint8_t*>(idx), cb, w, N, K, v, C, rows_per_cb, s);
   // the kernels read a codebook entry (2v bytes) and write it with one access, and read indices by their own width
   const uintptr_t entry = static_cast<uintptr_t>(2) * static_cast<uintptr_t>(v > 0 ? v : 1);
   if (reinterpret_cast<uintptr_t>(cb) % entry || reinterpret_cast<uintptr_t>(w) % entry ||
@@ -524,7 +600,13 @@ __global__ void __launch_bounds__(256) generic_vq_gemm_kernel(Problem p) {
         if (n < p.N) {
           if (LAYOUT == VQG_LAYOUT_BL) {
             const size_t ii = static_cast<size_t>(n) * J + k / p.v;
-            const int c = p.idx_bytes == 1 ? idx8[ii] : idx16[ii];
+            int c;
+            if (p.idx_bytes == VQG_IDX_PACKED12) {
+              const uint8_t* b = idx8 + 3 * (ii >> 1);
+              c = (ii & 1) ? ((b[1] >> 4) | (b[2] << 4)) : (b[0] | ((b[1] & 15) << 8));
+            } else {
+              c = p.idx_bytes == 1 ? idx8[ii] : idx16[ii];
+            }
             const int g = n / p.rows_per_cb;
             __half w = p.cb[(static_cast<size_t>(g) * p.C + c) * p.v + (k % p.v)];
             // residual stages: the fp16 running sum of the stages' entries (each addition rounded to fp16)

@@ -123,7 +123,8 @@ __device__ __forceinline__ int cta_of_stage(int s, int q, int r) {
   return s < big ? s / (q + 1) : r + (s - big) / q;
 }
 
-// V: sub-vector length; IB: index bytes; NB: batch columns of the MMA (16..128); REPL: replicated image.
+// V: sub-vector length; IB: index bytes (12: two 12-bit indices packed in three bytes); NB: batch columns of the MMA
+// (16..128); REPL: replicated image.
 template <int V, int IB, int NB, bool REPL, int KS>
 __global__ void __launch_bounds__(kThreads, 1)
 vq_small_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallParams p) {
@@ -132,7 +133,7 @@ vq_small_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallParams
   constexpr int ENTRY_LOG2 = (V == 4) ? 3 : 4;
   constexpr int REP_LOG2 = REPL ? (7 - ENTRY_LOG2) : 0;
   constexpr int ENTRY_SHIFT = ENTRY_LOG2 + REP_LOG2;
-  constexpr int BPS = (BK / V) * IB;                    // index bytes per row and sub-step: 16, 8 or 16
+  constexpr int BPS = IB == 12 ? (BK / V) * 3 / 2 : (BK / V) * IB;   // index bytes per row and sub-step: 16, 8, 16 or 12
   constexpr int WPS = BPS / 4;                          // 32-bit words of indices per sub-step
   // kind::f16, A = B = fp16, D = fp32, both K-major, M = 128, N = NB
   constexpr uint32_t kIdesc = (1u << 4) | (static_cast<uint32_t>(NB >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
@@ -348,7 +349,7 @@ vq_small_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallParams
     const int j = dw >> 2;                         // this warp takes sub-steps j, j+4, j+8, ... of the CTA's sequence
     const int rrow = quarter * 32 + lane;          // weight row inside the tile = TMEM lane
     const int tix = dw * 32 + lane;                // 0..511 for cooperative copies
-    const size_t J = static_cast<size_t>(p.K / V) * IB;   // index bytes per weight row
+    const size_t J = IB == 12 ? static_cast<size_t>(p.K / V) * 3 / 2 : static_cast<size_t>(p.K / V) * IB;   // index bytes per weight row
     unsigned char* image = base_ptr + L::kImage;
     const uint32_t img = base + L::kImage + ((lane & ((1 << REP_LOG2) - 1)) << ENTRY_LOG2);
     const uint32_t a_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -399,6 +400,9 @@ vq_small_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallParams
           if constexpr (WPS == 4) {
             const uint4 v = __ldcs(reinterpret_cast<const uint4*>(src));
             dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+          } else if constexpr (WPS == 3) {               // packed: 12 bytes, 4-byte aligned
+            const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src);
+            dst[0] = __ldcs(s32); dst[1] = __ldcs(s32 + 1); dst[2] = __ldcs(s32 + 2);
           } else {
             const uint2 v = __ldcs(reinterpret_cast<const uint2*>(src));
             dst[0] = v.x; dst[1] = v.y;
@@ -426,8 +430,17 @@ vq_small_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallParams
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
               uint32_t c0;
-              if constexpr (IB == 1) c0 = (w[e >> 2] >> (8 * (e & 3))) & 0xffu;
-              else c0 = (w[e >> 1] >> (16 * (e & 1))) & 0xffffu;
+              if constexpr (IB == 1) {
+                c0 = (w[e >> 2] >> (8 * (e & 3))) & 0xffu;
+              } else if constexpr (IB == 2) {
+                c0 = (w[e >> 1] >> (16 * (e & 1))) & 0xffffu;
+              } else {                                    // index e sits at bit 12 e of the 96 bits
+                constexpr int kNoWord = WPS - 1;
+                const int word = (12 * e) >> 5, sh = (12 * e) & 31;
+                const uint32_t hi = word < kNoWord ? w[word + 1] : 0u;
+                c0 = __funnelshift_r(w[word], hi, sh) & 0xfffu;
+                if (p.C < 4096) c0 = c0 < static_cast<uint32_t>(p.C) ? c0 : 0u;   // 12 bits can name more entries than the image holds
+              }
               asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                            : "=r"(a[4 * e]), "=r"(a[4 * e + 1]), "=r"(a[4 * e + 2]), "=r"(a[4 * e + 3])
                            : "r"(img + (c0 << ENTRY_SHIFT)));
@@ -501,7 +514,8 @@ struct Plan { int ntiles, ksteps, grid, q, r, max_slots; bool repl; int nb; int 
 bool make_plan(const Problem& p, Plan& pl) {
   if (p.M < 1 || p.M > 128 || p.N < 1 || p.K < 128) return false;
   if (p.K % 128 != 0 || p.N % 128 != 0) return false;
-  const bool combo = (p.v == 4 && p.idx_bytes == 1) || (p.v == 8 && p.idx_bytes == 1) || (p.v == 8 && p.idx_bytes == 2);
+  const bool combo = (p.v == 4 && p.idx_bytes == 1) || (p.v == 8 && p.idx_bytes == 1) || (p.v == 8 && p.idx_bytes == 2) ||
+                     (p.v == 8 && p.idx_bytes == VQG_IDX_PACKED12);
   if (!combo) return false;
   if (p.idx_bytes == 1 && p.C > 256) return false;
   if (p.C < 1 || p.C > 4096) return false;
@@ -510,7 +524,7 @@ bool make_plan(const Problem& p, Plan& pl) {
   if (reinterpret_cast<uintptr_t>(p.x) % 16 || reinterpret_cast<uintptr_t>(p.idx) % 16 ||
       reinterpret_cast<uintptr_t>(p.cb) % 16)
     return false;
-  pl.repl = p.C <= 256;
+  pl.repl = p.C <= 256 && p.idx_bytes != VQG_IDX_PACKED12;   // packed indices: one instance, unreplicated image
   if (!pl.repl && p.v != 8) return false;       // large codebooks only with 16-byte entries (64 KiB image)
   pl.nb = p.M <= 16 ? 16 : (p.M <= 32 ? 32 : (p.M <= 64 ? 64 : 128));
   pl.ntiles = p.N / 128;
@@ -595,6 +609,7 @@ int launch_small_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s)
     if (p.idx_bytes == 1) return VQG_SMALL_NB(8, 1, true, 4);
     return VQG_SMALL_NB(8, 2, true, 4);
   }
+  if (p.idx_bytes == VQG_IDX_PACKED12) return VQG_SMALL_NB(8, 12, false, 2);
   if (p.v == 4) return VQG_SMALL_NB(4, 1, true, 2);
   if (p.idx_bytes == 1) return VQG_SMALL_NB(8, 1, true, 2);
   return pl.repl ? VQG_SMALL_NB(8, 2, true, 2) : VQG_SMALL_NB(8, 2, false, 2);

@@ -68,22 +68,45 @@ def _stream_ptr(dev) -> int:
     return torch.cuda.current_stream(dev).cuda_stream
 
 
+def auto_path(M: int, N: int, K: int, v: int, C: int, index_bits: int = 8, rows_per_codebook: int = 0, layout: str = "bl") -> str:
+    """Name of the kernel route the library picks by itself for a problem (``vqg_auto_path``)."""
+    ib = {8: 1, 16: 2, 12: _lib.IDX_PACKED12}[index_bits]
+    code = _lib.load().vqg_auto_path(M, N, K, v, C, ib, rows_per_codebook, _lib.LAYOUT_BL if layout == "bl" else _lib.LAYOUT_REF)
+    return {val: name for name, val in _lib.PATHS.items()}.get(code, str(code))
+
+
+def _packed12(indices: torch.Tensor, index_bits: Optional[int]) -> bool:
+    if index_bits in (None, 8, 16):
+        return False
+    if index_bits != 12:
+        raise RuntimeError("index_bits must be 8, 16 or 12 (packed)")
+    if indices.dtype != torch.uint8 or indices.dim() != 2 or indices.shape[1] % 3:
+        raise RuntimeError("packed 12-bit indices are a uint8 [N, K/v * 3/2] tensor (quantize.pack12)")
+    return True
+
+
 def vq_gemm(x: torch.Tensor, indices: torch.Tensor, codebook: torch.Tensor, *, rows_per_codebook: Optional[int] = None,
-            layout: str = "auto", path: str = "auto", out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Y = X @ dequant(indices, codebook)^T, fp16 in and out, fp32 accumulation."""
+            layout: str = "auto", path: str = "auto", out: Optional[torch.Tensor] = None,
+            index_bits: Optional[int] = None) -> torch.Tensor:
+    """Y = X @ dequant(indices, codebook)^T, fp16 in and out, fp32 accumulation.
+    ``index_bits=12``: `indices` holds 12-bit indices packed two to three bytes (``quantize.pack12``)."""
     lib = _lib.load()
     dev = _require_cuda(x, indices, codebook)
     if x.dtype != torch.float16 or codebook.dtype != torch.float16:
         raise RuntimeError("x and codebook must be float16")
+    packed = _packed12(indices, index_bits)
     if layout == "auto":
-        layout = infer_layout(x, indices, codebook)
+        layout = "bl" if packed else infer_layout(x, indices, codebook)
     M, K = x.shape
-    ib = _idx_bytes(indices)
+    ib = _lib.IDX_PACKED12 if packed else _idx_bytes(indices)
+    if packed and layout != "bl":
+        raise RuntimeError("packed indices exist in the generalised format only")
     if layout == "bl":
         N = indices.shape[0]
         cb3 = codebook if codebook.dim() == 3 else codebook.unsqueeze(0)
         G, C, v = cb3.shape
-        if indices.shape[1] * v != K:
+        J = indices.shape[1] * 2 // 3 if packed else indices.shape[1]
+        if J * v != K:
             raise RuntimeError(f"indices [N, K/v] = {tuple(indices.shape)} does not match K={K}, v={v}")
         if rows_per_codebook is None:
             if G == 1:
@@ -254,17 +277,23 @@ def gemm(input: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 
 def dequant(indices: torch.Tensor, codebook: torch.Tensor, *, rows_per_codebook: Optional[int] = None,
-            layout: str = "bl", out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Dequantised weights: ``[N, K]`` for the generalised format, ``[K, 2*Nq]`` for the reference's."""
+            layout: str = "bl", out: Optional[torch.Tensor] = None, index_bits: Optional[int] = None) -> torch.Tensor:
+    """Dequantised weights: ``[N, K]`` for the generalised format, ``[K, 2*Nq]`` for the reference's.
+    ``index_bits=12``: packed indices as in :func:`vq_gemm`."""
     lib = _lib.load()
     dev = _require_cuda(indices, codebook)
     if codebook.dtype != torch.float16:
         raise RuntimeError("codebook must be float16")
-    ib = _idx_bytes(indices)
+    packed = _packed12(indices, index_bits)
+    ib = _lib.IDX_PACKED12 if packed else _idx_bytes(indices)
+    if packed and layout != "bl":
+        raise RuntimeError("packed indices exist in the generalised format only")
     if layout == "bl":
         cb3 = codebook if codebook.dim() == 3 else codebook.unsqueeze(0)
         G, C, v = cb3.shape
         N, J = indices.shape
+        if packed:
+            J = J * 2 // 3
         K = J * v
         if rows_per_codebook is None:
             rows_per_codebook = 0 if G == 1 else N // G

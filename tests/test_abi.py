@@ -89,6 +89,13 @@ def test_bad_arguments_are_rejected_without_cuda(lib):
     assert lib.vqg_dequant(odd, p, p, 8, 8, 4, 300, 2, 0, 0, null) == _lib.ERR_BAD_ARG
     assert lib.vqg_dequant(p, off8, p, 8, 8, 8, 256, 1, 0, 0, null) == _lib.ERR_BAD_ARG
     assert lib.vqg_dequant(p, p, off8, 8, 8, 8, 256, 1, 0, 0, null) == _lib.ERR_BAD_ARG
+    # packed 12-bit indices: whole pairs per row, at most 4096 entries; only the plain product and dequant take them
+    PK = _lib.IDX_PACKED12
+    assert call(p, p, p, p, 1, 8, 24, 8, 4096, PK, 0, 0, null, 0, null) == _lib.ERR_BAD_ARG       # K/v = 3 is odd
+    assert call(p, p, p, p, 1, 8, 32, 8, 5000, PK, 0, 0, null, 0, null) == _lib.ERR_BAD_ARG
+    assert call(p, p, p, p, 1, 8, 32, 8, 4096, PK, 0, 1, null, 0, null) == _lib.ERR_UNSUPPORTED   # not in the reference's format
+    assert lib.vqg_dequant(p, p, p, 8, 24, 8, 4096, PK, 0, 0, null) == _lib.ERR_BAD_ARG
+    assert lib.vqg_gemm_swiglu(p, p, p, p, 1, 8, 32, 8, 4096, PK, 0, null, 0, null) == _lib.ERR_UNSUPPORTED
     assert lib.vqg_device_status(None) == _lib.ERR_BAD_ARG
     arr = (ctypes.c_void_p * 2)(4096, 8192)
     assert lib.vqg_gemm_sharded(p, p, p, arr, 2, 2, 1, 8, 8, 4, 256, 1, 0, null, 0, null) == _lib.ERR_BAD_ARG
@@ -123,4 +130,9 @@ def test_routing_of_the_benchmark_configurations(lib):
     assert auto(128, 28672, 8192, 8, 256, 1, 128, 0) == P["tensor_ts"]
     assert auto(130, 96, 192, 4, 256, 1, 32, 0) == P["two_phase"]        # ragged K: dequantise, then the dense kernel
     assert auto(130, 96, 192, 3, 256, 1, 32, 0) == P["generic"]          # odd sub-vector length: CUDA-core kernel
+    PK = _lib.IDX_PACKED12
+    assert auto(16, 8192, 8192, 8, 4096, PK, 0, 0) == P["small_ts"]      # C3 with its indices packed
+    assert auto(2048, 8192, 8192, 8, 4096, PK, 0, 0) == P["two_phase"]
+    assert auto(16, 8192, 8192, 4, 4096, PK, 0, 0) == P["two_phase"]     # v = 4 has no packed tensor-memory instance
+    assert auto(3, 100, 48, 4, 4096, PK, 0, 0) == P["generic"]
     assert auto(2048, 1280, 4096, 2, 256, 1, 0, 1) == P["two_phase"]     # the reference's own format

@@ -683,6 +683,8 @@ def main():
     ap.add_argument("--workload", default="c5_mlp70b")
     ap.add_argument("--mode", default="auto", choices=["auto", "peer", "multicast", "nccl"],
                     help="how the N-sharded output is assembled (auto: the faster of peer stores and multimem stores)")
+    ap.add_argument("--lead-cols", type=int, default=0,
+                    help="columns of a rank's block issued as a small first launch in the N-sharded mode (0: one launch per step)")
     ap.add_argument("--no-shapes", action="store_true", help="skip the per-configuration table")
     ap.add_argument("--no-mlp", action="store_true", help="skip the tensor-parallel MLP measurement")
     ap.add_argument("--no-baselines", action="store_true",
@@ -779,7 +781,7 @@ def main():
             if has_mc:
                 # a short trial of both: 10 timed steps each after 3 warm-up steps, max over ranks
                 for cand in ("peer", "multicast"):
-                    trial = ShardedVQGemm(shape.M, shape.N, mode=cand, device=dev)
+                    trial = ShardedVQGemm(shape.M, shape.N, mode=cand, device=dev, lead_cols=args.lead_cols)
                     tms = _time_loop(lambda: trial(x, idx, cb, rpc), 10, 3, barrier)
                     tt = torch.tensor([tms], device=dev, dtype=torch.float64)
                     dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -788,7 +790,7 @@ def main():
                 mode = min(gather_modes, key=gather_modes.get)
     if world == 1 and mode == "auto":
         mode = "peer"
-    op = ShardedVQGemm(shape.M, shape.N, mode=mode, device=dev)
+    op = ShardedVQGemm(shape.M, shape.N, mode=mode, device=dev, lead_cols=args.lead_cols)
 
     # clock warm-up: the SM clock idles at a few hundred MHz
     a = torch.randn(4096, 4096, device=dev, dtype=torch.float16)
@@ -844,7 +846,7 @@ def main():
         # inputs (X, indices, codebooks) from pinned host memory and its output block back to pinned memory.
         # With G ranks on one host every rank copies only its M/G rows of X in and the ranks all-gather X over
         # NVLink (ShardedVQGemm.gather_x), so the host link carries X once per step, not G times.
-        ops = [op, ShardedVQGemm(shape.M, shape.N, mode=mode, device=dev)]
+        ops = [op, ShardedVQGemm(shape.M, shape.N, mode=mode, device=dev, lead_cols=args.lead_cols)]
         y_h = [torch.empty((shape.M, n_local), dtype=torch.float16).pin_memory() for _ in range(2)]
         ins = [(torch.empty_like(x), torch.empty_like(idx), torch.empty_like(cb)) for _ in range(2)]
         shard_x = world > 1 and shape.M % world == 0
@@ -931,7 +933,7 @@ def main():
         try:
             from oracle import vq_oracle as O
             y_fused = op(x, idx, cb, rpc).clone()
-            ref_op = ShardedVQGemm(shape.M, shape.N, mode="nccl", device=dev)
+            ref_op = ShardedVQGemm(shape.M, shape.N, mode="nccl", device=dev, lead_cols=args.lead_cols)
             y_nccl = ref_op(x, idx, cb, rpc)
             torch.cuda.synchronize()
             same = bool(torch.equal(y_fused.view(torch.int16), y_nccl.view(torch.int16)))
@@ -1002,6 +1004,7 @@ def main():
             multi["ingress_ms_at_link"] = ingress / multi["link_gbs"] / 1e6
             multi["step_lower_bound_ms"] = max(kms, multi["ingress_ms_at_link"])
             multi["step_over_bound"] = ms / multi["step_lower_bound_ms"]
+        multi["lead_cols"] = op._lead(rpc)      # columns issued as a small first launch (0: one launch per step)
         multi["kernel_alone_ms"] = kms
         multi["exposed_gather_ms"] = ms - kms
         line["multi_gpu"] = multi

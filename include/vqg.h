@@ -156,6 +156,19 @@ VQG_API int vqg_gemm_sharded_mc(const void* x, const void* idx, const void* code
                         int M, int N_local, int K, int v, int C, int idx_bytes, int rows_per_codebook,
                         void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same product for a SLAB of this rank's columns: output columns [col0, col0 + N_cols) of a Y with ld_y
+ * columns on every rank (col0 and ld_y multiples of 8); idx / codebook are the shard of exactly those columns.
+ * For callers that hand a rank's block over in pieces (their consumer starts on the first columns while the rest
+ * is computed).  Launches of one step share the workspace and follow one another in stream order.  As a way
+ * to start the NVLink stream earlier (a small first slab) it did not pay: on 2 GPUs a 512-column first launch
+ * made the C5-shaped step 15 % slower.  vqg_gemm_sharded_mc is this call with col0 = rank * N_local, ld_y = nranks *
+ * N_local.  No reference counterpart. */
+VQG_API int vqg_gemm_sharded_cols(const void* x, const void* idx, const void* codebook,
+                          void* const* y_peers, void* y_multicast, int rank, int nranks,
+                          int M, int N_cols, int K, int v, int C, int idx_bytes, int rows_per_codebook,
+                          long long col0, long long ld_y,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
 /* Barrier across the ranks of a sharded product, to be enqueued after vqg_gemm_sharded* (or
  * vqg_gemm_rowparallel) on the same stream: when it completes on a rank, every rank's stores into this rank's
  * buffers have landed.  flag_ptrs[r] (HOST array of nranks DEVICE pointers) is rank r's flag array: nranks

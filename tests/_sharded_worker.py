@@ -81,6 +81,27 @@ def main():
             if not (same and tol):
                 ok = False
                 print(f"rank {rank}: MISMATCH mode={mode} shape={(M, K, N, v)} bitwise={same} tol={tol}", flush=True)
+    if cases:
+        # a block issued as two launches (a 256-column first slab): every fused mode equals the NCCL mode bit for bit
+        # (which computes in the same two launches) and the oracle within the tolerance
+        M, K, N, v, C, rpc = 256, 512, 1024 * world, 8, 256, 128
+        x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=9)
+        idx_l, cb_l = shard_weights(idx, cb, world, rank, rpc)
+        ref = None
+        for mode in ["nccl"] + [m for m in modes if m != "nccl"]:
+            op = ShardedVQGemm(M, N, mode=mode, device=dev, lead_cols=256)
+            assert op._lead(rpc) == 256
+            for _ in range(2):
+                y = op(x.to(dev), idx_l.to(dev), cb_l.to(dev), rpc)
+            torch.cuda.synchronize()
+            if ref is None:
+                ref = y.clone()
+                if not O.check_tolerance(y.cpu(), O.vq_gemm_bl(x, idx, cb, rpc))["ok"]:
+                    ok = False
+                    print(f"rank {rank}: slab launches out of tolerance", flush=True)
+            elif not torch.equal(y.view(torch.int16), ref.view(torch.int16)):
+                ok = False
+                print(f"rank {rank}: slab launches MISMATCH mode={mode}", flush=True)
     ok = ok and V.device_status() == 0
     t = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)

@@ -56,6 +56,44 @@ def test_column_block_with_leading_dimension():
     assert torch.equal(bits(y), bits(other))
 
 
+@pytest.mark.parametrize("M,K,N,v,rpc,slabs", [
+    (2048, 1024, 2048, 8, 128, (512, 1536)),     # prefill kernel, a small first slab and the rest
+    (64, 512, 1024, 4, 128, (256, 256, 512)),
+    (8, 512, 768, 8, 0, (256, 512)),             # single codebook: every slab uses the same one
+])
+def test_column_slabs_of_one_block(M, K, N, v, rpc, slabs):
+    # vqg_gemm_sharded_cols: the block handed over in column slabs with its own leading dimension and a "peer"
+    # copy; every slab equals the stand-alone product of the same columns bit for bit
+    import ctypes
+    from vq_gemm_b200 import _lib
+    lib = _lib.load()
+    x, idx, cb = O.make_bl_inputs(M, K, N, v, 256, rpc, seed=M + N)
+    xd = x.cuda()
+    y = torch.zeros(M, N + 64, dtype=torch.float16, device="cuda")     # wider than the block: ld_y = N + 64, col0 = 32
+    peer = torch.zeros_like(y)
+    arr = (ctypes.c_void_p * 2)(y.data_ptr(), peer.data_ptr())
+    nbytes = max(lib.vqg_workspace_bytes(M, n, K, v, 256, 1, rpc, 0, 0) for n in slabs)
+    ws = torch.zeros(max(nbytes, 1), dtype=torch.uint8, device="cuda")
+    c0 = 0
+    for n in slabs:
+        idx_s = idx[c0:c0 + n].contiguous().cuda()
+        cb_s = (cb[c0 // rpc:(c0 + n) // rpc] if rpc else cb).contiguous().cuda()
+        st = lib.vqg_gemm_sharded_cols(xd.data_ptr(), idx_s.data_ptr(), cb_s.data_ptr(), arr, None, 0, 2, M, n, K, v, 256, 1, rpc,
+                                       32 + c0, N + 64, ws.data_ptr() if nbytes else None, nbytes,
+                                       torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+        alone = V.vq_gemm(xd, idx_s, cb_s, rows_per_codebook=rpc, layout="bl")
+        torch.cuda.synchronize()
+        assert torch.equal(bits(y[:, 32 + c0:32 + c0 + n]), bits(alone))
+        c0 += n
+    assert torch.equal(bits(y), bits(peer))
+    assert float(y[:, :32].abs().max()) == 0 and float(y[:, 32 + N:].abs().max()) == 0     # nothing outside the block
+    assert_within_tolerance(y[:, 32:32 + N].cpu(), O.vq_gemm_bl(x, idx, cb, rpc))
+    bad = lib.vqg_gemm_sharded_cols(xd.data_ptr(), idx_s.data_ptr(), cb_s.data_ptr(), arr, None, 0, 2, M, n, K, v, 256, 1, rpc,
+                                    N, N + 64, None, 0, None)
+    assert bad == _lib.ERR_BAD_ARG                                      # the slab would run past the leading dimension
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_two_ranks_gather_through_the_switch_equals_single_gpu():
     # the multimem-store epilogue (NVLS multicast mapping of the symmetric buffers), where the fabric offers it;

@@ -33,6 +33,8 @@ SIGNATURES = {
                          + [c_void_p, c_size_t, c_void_p]),
     "vqg_gemm_sharded_mc": (c_int, [c_void_p] * 3 + [POINTER(c_void_p), c_void_p, c_int, c_int] + [c_int] * 7
                             + [c_void_p, c_size_t, c_void_p]),
+    "vqg_gemm_sharded_cols": (c_int, [c_void_p] * 3 + [POINTER(c_void_p), c_void_p, c_int, c_int] + [c_int] * 7
+                              + [c_longlong, c_longlong, c_void_p, c_size_t, c_void_p]),
     "vqg_rank_barrier": (c_int, [POINTER(c_void_p), c_int, c_int, c_uint, c_longlong, c_void_p]),
     "vqg_residual_workspace_bytes": (c_size_t, [c_int] * 8),
     "vqg_gemm_residual": (c_int, [c_void_p] * 4 + [c_int] * 8 + [c_void_p, c_size_t, c_void_p]),

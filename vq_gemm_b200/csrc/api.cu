@@ -324,19 +324,19 @@ int vqg_rank_barrier(void* const* flag_ptrs, int rank, int nranks, unsigned epoc
   return launch_rank_barrier(f, rank, nranks, epoch, limit_cycles, static_cast<cudaStream_t>(stream));
 }
 
-int vqg_gemm_sharded_mc(const void* x, const void* idx, const void* codebook, void* const* y_peers, void* y_multicast,
-                        int rank, int nranks, int M, int N_local, int K, int v, int C, int idx_bytes,
-                        int rows_per_codebook, void* workspace, size_t workspace_bytes, void* stream) {
+int vqg_gemm_sharded_cols(const void* x, const void* idx, const void* codebook, void* const* y_peers, void* y_multicast,
+                          int rank, int nranks, int M, int N_cols, int K, int v, int C, int idx_bytes,
+                          int rows_per_codebook, long long col0, long long ld_y, void* workspace, size_t workspace_bytes,
+                          void* stream) {
   if (nranks < 1 || nranks > 8 || rank < 0 || rank >= nranks || !y_peers) return VQG_ERR_BAD_ARG;
+  if (col0 < 0 || N_cols < 0 || ld_y < col0 + N_cols || col0 % 8 != 0 || ld_y % 8 != 0) return VQG_ERR_BAD_ARG;
   if (y_multicast && !aligned(y_multicast, 16)) return VQG_ERR_BAD_ARG;
   for (int r = 0; r < nranks; ++r)
     if (!y_peers[r]) return VQG_ERR_BAD_ARG;
-  const long long ld = static_cast<long long>(nranks) * N_local;
-  const size_t col0 = static_cast<size_t>(rank) * N_local;
   void* y_local = static_cast<__half*>(y_peers[rank]) + col0;
-  const int st = check_common(x, idx, codebook, y_local, M, N_local, K, v, C, idx_bytes, VQG_LAYOUT_BL);
+  const int st = check_common(x, idx, codebook, y_local, M, N_cols, K, v, C, idx_bytes, VQG_LAYOUT_BL);
   if (st != VQG_OK) return st;
-  Problem p = make_problem(x, idx, codebook, y_local, M, N_local, K, v, C, idx_bytes, rows_per_codebook, ld);
+  Problem p = make_problem(x, idx, codebook, y_local, M, N_cols, K, v, C, idx_bytes, rows_per_codebook, ld_y);
   for (int r = 0; r < nranks; ++r)
     if (r != rank) p.peer_y[p.n_peers++] = static_cast<__half*>(y_peers[r]) + col0;
   // through the switch only where the kernel that will run has the multimem epilogue (the prefill kernel);
@@ -344,6 +344,15 @@ int vqg_gemm_sharded_mc(const void* x, const void* idx, const void* codebook, vo
   if (y_multicast && nranks > 1 && auto_path(p, VQG_LAYOUT_BL) == VQG_PATH_TENSOR_TS)
     p.mc_y = static_cast<__half*>(y_multicast) + col0;
   return run(p, VQG_LAYOUT_BL, VQG_PATH_AUTO, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int vqg_gemm_sharded_mc(const void* x, const void* idx, const void* codebook, void* const* y_peers, void* y_multicast,
+                        int rank, int nranks, int M, int N_local, int K, int v, int C, int idx_bytes,
+                        int rows_per_codebook, void* workspace, size_t workspace_bytes, void* stream) {
+  if (nranks < 1 || nranks > 8 || rank < 0 || rank >= nranks || N_local < 0) return VQG_ERR_BAD_ARG;
+  return vqg_gemm_sharded_cols(x, idx, codebook, y_peers, y_multicast, rank, nranks, M, N_local, K, v, C, idx_bytes,
+                               rows_per_codebook, static_cast<long long>(rank) * N_local,
+                               static_cast<long long>(nranks) * N_local, workspace, workspace_bytes, stream);
 }
 
 namespace {

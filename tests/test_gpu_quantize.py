@@ -36,6 +36,24 @@ def test_assign_and_update_match_the_rules_bit_for_bit(N, K, v, C, rpc):
     assert V.device_status() == 0
 
 
+@pytest.mark.parametrize("value", [65504.0, -65504.0, 5.9604645e-08, 0.333251953125])
+def test_update_is_exact_at_the_limits_of_its_counters(value):
+    # every sub-vector of a group names entry 0 and every weight is the same extreme value: the per-round 32-bit
+    # counters of the accumulation reach their largest possible contents (2048 x the largest high part, or the
+    # largest low part); the mean must come back as the value itself
+    N, K, v, C, rpc = 64, 4096, 4, 256, 64
+    w = torch.full((N, K), value, dtype=torch.float16)
+    w[1, 5] = -w[1, 5]                                   # one element of the other sign
+    idx = torch.zeros(N, K // v, dtype=torch.uint8)
+    idx[3, 7] = 9                                        # one sub-vector elsewhere: entry 9 becomes that sub-vector
+    cb = torch.zeros(1, C, v, dtype=torch.float16)
+    cbd = cb.cuda()
+    VQ.kmeans_update(w.cuda(), idx.cuda(), cbd, rpc)
+    ref_cb = Q.update(w.numpy(), idx.numpy(), cb.numpy(), rpc)
+    assert np.array_equal(cbd.cpu().numpy().view(np.int16), ref_cb.view(np.int16))
+    assert float(cbd[0, 9, 0]) == float(w[0, 0]) and V.device_status() == 0
+
+
 def test_kmeans_pipeline_equals_oracle_and_feeds_the_product():
     N, K, v, C, rpc = 256, 512, 8, 256, 128
     w = _weights(N, K, seed=9)

@@ -11,7 +11,8 @@
 //            whose indices otherwise sit in uint16 with four unused bits each.
 //
 // All three are CUDA-core kernels: the distance search is bound by the fp32 pipe (3v lane operations per
-// (sub-vector, entry) pair), the update by shared-memory atomics, the packers by HBM.
+// (sub-vector, entry) pair), the update by shared-memory atomics (native 32-bit ones where the accumulators fit,
+// see accumulate_split_kernel), the packers by HBM.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -159,6 +160,76 @@ accumulate_kernel(const __half* __restrict__ w, const IdxT* __restrict__ idx, un
   }
 }
 
+// The same sums with native 32-bit shared-memory atomics (64-bit ones are compare-and-swap loops): a value's
+// fixed-point form f (|f| < 2^40) is split into a signed low part lo in [-2^20, 2^20) and hi = (f - lo) / 2^21,
+// each added into its own 32-bit counter.  hi is zero for |value| < 1/16, i.e. for nearly every weight of a real
+// layer, and then costs nothing.  A CTA works in rounds of kRound = 2048 sub-vectors -- after which a counter holds
+// at most 2048 * 2^20 = 2^31 in magnitude, exactly what fits -- and folds the counters into 64-bit totals (one owner
+// thread per address, no atomics) between rounds.  The counters are laid out [dimension][entry], so that a warp's
+// atomics on one dimension spread over all banks.  Exact and order-independent like the rule asks.
+constexpr int kRound = 2048;
+template <int V, typename IdxT>
+__global__ void __launch_bounds__(kAccThreads)
+accumulate_split_kernel(const __half* __restrict__ w, const IdxT* __restrict__ idx, unsigned long long* __restrict__ sums,
+                        unsigned int* __restrict__ counts, int N, int K, int C, int rows_per_cb) {
+  extern __shared__ unsigned long long s_tot[];   // [C][V] totals, then lo [C][V], hi [C][V], counts [C] (32-bit each)
+  const int CV = C * V;
+  int* s_lo = reinterpret_cast<int*>(s_tot + CV);
+  int* s_hi = s_lo + CV;
+  unsigned int* s_cnt = reinterpret_cast<unsigned int*>(s_hi + CV);
+  const int g = blockIdx.y;
+  for (int i = threadIdx.x; i < CV; i += kAccThreads) { s_tot[i] = 0ull; s_lo[i] = 0; s_hi[i] = 0; }
+  for (int i = threadIdx.x; i < C; i += kAccThreads) s_cnt[i] = 0u;
+  __syncthreads();
+  const int J = K / V;
+  const int row0 = g * rows_per_cb;
+  const int rows = min(rows_per_cb, N - row0);
+  const long long total = static_cast<long long>(rows) * J;
+  const long long base = static_cast<long long>(row0) * J;
+  constexpr int U = kRound / kAccThreads;          // sub-vectors per thread and round
+  for (long long s0 = static_cast<long long>(blockIdx.x) * kRound; s0 < total; s0 += static_cast<long long>(gridDim.x) * kRound) {
+    int c[U];
+    float x[U][V];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long sv = s0 + u * kAccThreads + threadIdx.x;
+      c[u] = C;                                    // "nothing": beyond the range, or a foreign index
+      if (sv < total) {
+        c[u] = static_cast<int>(idx[base + sv]);
+        load_sub<V>(w + (base + sv) * V, x[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (c[u] < C) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          const long long f = static_cast<long long>(x[u][i] * 16777216.0f);
+          const int lo = static_cast<int>((f + (1ll << 20)) & ((1ll << 21) - 1)) - (1 << 20);
+          const int hi = static_cast<int>((f - lo) >> 21);
+          atomicAdd(&s_lo[i * C + c[u]], lo);
+          if (hi != 0) atomicAdd(&s_hi[i * C + c[u]], hi);
+        }
+        atomicAdd(&s_cnt[c[u]], 1u);
+      }
+    }
+    __syncthreads();
+    for (int a = threadIdx.x; a < CV; a += kAccThreads) {      // a = i * C + c in the counters, c * V + i in the totals
+      const long long add = static_cast<long long>(s_hi[a]) * (1ll << 21) + static_cast<long long>(s_lo[a]);
+      s_tot[(a % C) * V + a / C] += static_cast<unsigned long long>(add);
+      s_lo[a] = 0;
+      s_hi[a] = 0;
+    }
+    __syncthreads();
+  }
+  unsigned long long* gs = sums + static_cast<size_t>(g) * CV;
+  unsigned int* gc = counts + static_cast<size_t>(g) * C;
+  for (int i = threadIdx.x; i < CV; i += kAccThreads)
+    if (s_tot[i] != 0ull) atomicAdd(&gs[i], s_tot[i]);
+  for (int i = threadIdx.x; i < C; i += kAccThreads)
+    if (s_cnt[i] != 0u) atomicAdd(&gc[i], s_cnt[i]);
+}
+
 __global__ void finalize_kernel(__half* __restrict__ cb, const unsigned long long* __restrict__ sums,
                                 const unsigned int* __restrict__ counts, long long entries, int V) {
   const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;   // (g, c)
@@ -263,6 +334,8 @@ int launch_quantize_update(const __half* w, const void* idx, __half* cb, void* w
   if (cudaMemsetAsync(ws, 0, need, s) != cudaSuccess) return VQG_ERR_LAUNCH;
   const size_t smem = static_cast<size_t>(C) * v * sizeof(unsigned long long) + static_cast<size_t>(C) * sizeof(unsigned int);
   const bool in_smem = smem <= 160 * 1024;
+  const size_t smem_split = static_cast<size_t>(C) * v * 16 + static_cast<size_t>(C) * sizeof(unsigned int);
+  const bool split = smem_split <= 200 * 1024;
   const long long per_group = static_cast<long long>(rpc) * (K / v);
   long long chunks = (per_group + 16LL * kAccThreads - 1) / (16LL * kAccThreads);
   const long long want = (2LL * sm_count_q() + G - 1) / G;
@@ -271,7 +344,13 @@ int launch_quantize_update(const __half* w, const void* idx, __half* cb, void* w
   const dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(G));
 #define VQG_ACC(VV, TT)                                                                                              \
   do {                                                                                                               \
-    if (in_smem) {                                                                                                   \
+    if (split) {                                                                                                     \
+      if (cudaFuncSetAttribute(accumulate_split_kernel<VV, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                               static_cast<int>(smem_split)) != cudaSuccess)                                         \
+        return VQG_ERR_LAUNCH;                                                                                       \
+      accumulate_split_kernel<VV, TT><<<grid, kAccThreads, smem_split, s>>>(w, static_cast<const TT*>(idx), sums, counts, \
+                                                                            N, K, C, rpc);                            \
+    } else if (in_smem) {                                                                                            \
       if (cudaFuncSetAttribute(accumulate_kernel<VV, TT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                                static_cast<int>(smem)) != cudaSuccess)                                               \
         return VQG_ERR_LAUNCH;                                                                                       \

@@ -451,7 +451,8 @@ def _quantizer(peaks, clocks_mhz):
     # search: per (sub-vector, entry) pair v subtractions, v multiplications, v additions, none fused
     lane_ops = 3.0 * v * C * (N * K / v)
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    fp32_peak = sms * 128 * clocks_mhz * 1e6          # one fp32 operation per lane and cycle (no FMA by rule)
+    # two fp32 operations per lane and cycle: packed .f32x2 instructions, still one rounding per operation (no FMA by rule)
+    fp32_peak = sms * 128 * 2 * clocks_mhz * 1e6
     idx12 = torch.randint(0, 4096, (8192, 8192), device="cuda").to(torch.int16)
     packed = VQ.pack12(idx12)
     t_pack = timed(lambda: VQ.pack12(idx12))
@@ -461,8 +462,9 @@ def _quantizer(peaks, clocks_mhz):
             "assign": {"ms": t_assign, "subvectors_per_s": (N * K / v) / t_assign * 1e3,
                        "roofline": {"bound": "fp32", "achieved": lane_ops / t_assign / 1e6, "peak": fp32_peak / 1e9,
                                     "unit": "Gop/s", "frac": lane_ops / (t_assign * 1e-3) / fp32_peak,
-                                    "peak_source": "SMs x 128 lanes x max SM clock; unfused sub/mul/add by the parity rule"}},
-            "kmeans_update": {"ms": t_update, "gbs": (N * K * 2 + N * K / v) / t_update / 1e6},
+                                    "peak_source": "SMs x 128 lanes x 2 (packed f32x2) x max SM clock; unfused sub/mul/add by the parity rule"}},
+            "kmeans_update": {"ms": t_update, "gbs": (N * K * 2 + N * K / v) / t_update / 1e6,
+                              "frac_of_hbm": (N * K * 2 + N * K / v) / t_update / 1e6 / peaks["hbm_gbs"]},
             "pack12": {"ms": t_pack, "gbs": pack_bytes / t_pack / 1e6, "frac_of_hbm": pack_bytes / t_pack / 1e6 / peaks["hbm_gbs"]},
             "unpack12": {"ms": t_unpack, "gbs": pack_bytes / t_unpack / 1e6,
                          "frac_of_hbm": pack_bytes / t_unpack / 1e6 / peaks["hbm_gbs"]}}

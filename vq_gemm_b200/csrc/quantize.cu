@@ -107,6 +107,89 @@ assign_kernel(const __half* __restrict__ w, const __half* __restrict__ cb, IdxT*
   }
 }
 
+// The same search with Blackwell's packed fp32 arithmetic (sub / mul / add .f32x2: two IEEE operations per
+// instruction, each rounded exactly like its scalar form, so the results are the same bits): a thread searches
+// four sub-vectors as two packed pairs; the codebook sits in shared memory with every value doubled -- (e, e) -- so
+// that an entry's operands arrive as ready 64-bit pairs.  Needs C * V * 8 bytes of shared memory.
+__device__ __forceinline__ unsigned long long f2_sub(unsigned long long a, unsigned long long b) {
+  unsigned long long r; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r;
+}
+__device__ __forceinline__ unsigned long long f2_mul(unsigned long long a, unsigned long long b) {
+  unsigned long long r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r;
+}
+__device__ __forceinline__ unsigned long long f2_add(unsigned long long a, unsigned long long b) {
+  unsigned long long r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r;
+}
+__device__ __forceinline__ unsigned long long f2_pack(float lo, float hi) {
+  return static_cast<unsigned long long>(__float_as_uint(lo)) | (static_cast<unsigned long long>(__float_as_uint(hi)) << 32);
+}
+
+constexpr int kPairsPerThread = 2;     // packed pairs (four sub-vectors) per thread
+template <int V, typename IdxT>
+__global__ void __launch_bounds__(kAssignThreads)
+assign_packed_kernel(const __half* __restrict__ w, const __half* __restrict__ cb, IdxT* __restrict__ idx, int N, int K, int C,
+                     int rows_per_cb) {
+  extern __shared__ __align__(16) unsigned long long s_cb2[];   // [C][V] pairs (e, e)
+  const int g = blockIdx.y;
+  const __half* cbg = cb + static_cast<size_t>(g) * C * V;
+  for (int i = threadIdx.x; i < C * V; i += kAssignThreads) {
+    const float e = __half2float(cbg[i]);
+    s_cb2[i] = f2_pack(e, e);
+  }
+  __syncthreads();
+  const int J = K / V;
+  const int row0 = g * rows_per_cb;
+  const int rows = min(rows_per_cb, N - row0);
+  const long long total = static_cast<long long>(rows) * J;
+  const long long base = static_cast<long long>(row0) * J;
+  constexpr int SUBS = 2 * kPairsPerThread;
+  const long long stride = static_cast<long long>(gridDim.x) * kAssignThreads * SUBS;
+  for (long long s0 = static_cast<long long>(blockIdx.x) * kAssignThreads * SUBS; s0 < total; s0 += stride) {
+    long long pos[SUBS];
+    unsigned long long x2[kPairsPerThread][V];
+#pragma unroll
+    for (int p = 0; p < kPairsPerThread; ++p) {
+      float xa[V], xb[V];
+      pos[2 * p] = s0 + (2 * p) * kAssignThreads + threadIdx.x;
+      pos[2 * p + 1] = s0 + (2 * p + 1) * kAssignThreads + threadIdx.x;
+#pragma unroll
+      for (int i = 0; i < V; ++i) { xa[i] = 0.f; xb[i] = 0.f; }
+      if (pos[2 * p] < total) load_sub<V>(w + (base + pos[2 * p]) * V, xa);
+      if (pos[2 * p + 1] < total) load_sub<V>(w + (base + pos[2 * p + 1]) * V, xb);
+#pragma unroll
+      for (int i = 0; i < V; ++i) x2[p][i] = f2_pack(xa[i], xb[i]);
+    }
+    float best[SUBS];
+    int arg[SUBS];
+#pragma unroll
+    for (int u = 0; u < SUBS; ++u) { best[u] = __int_as_float(0x7f800000); arg[u] = 0; }
+#pragma unroll 2
+    for (int c = 0; c < C; ++c) {
+      unsigned long long e2[V];
+#pragma unroll
+      for (int i = 0; i < V; i += 2) {
+        const ulonglong2 q = *reinterpret_cast<const ulonglong2*>(s_cb2 + c * V + i);
+        e2[i] = q.x; e2[i + 1] = q.y;
+      }
+#pragma unroll
+      for (int p = 0; p < kPairsPerThread; ++p) {
+        unsigned long long d2 = 0ull;              // (+0, +0)
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          const unsigned long long t = f2_sub(x2[p][i], e2[i]);
+          d2 = f2_add(d2, f2_mul(t, t));
+        }
+        const float da = __uint_as_float(static_cast<unsigned int>(d2)), db = __uint_as_float(static_cast<unsigned int>(d2 >> 32));
+        if (da < best[2 * p]) { best[2 * p] = da; arg[2 * p] = c; }           // strict: the lowest index wins a tie
+        if (db < best[2 * p + 1]) { best[2 * p + 1] = db; arg[2 * p + 1] = c; }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < SUBS; ++u)
+      if (pos[u] < total) idx[base + pos[u]] = static_cast<IdxT>(arg[u]);
+  }
+}
+
 constexpr int kAccThreads = 256;
 
 // value * 2^24 as a two's-complement 64-bit integer: exact for every finite fp16 (|value| <= 65504, smallest
@@ -294,10 +377,11 @@ int launch_quantize_assign(const __half* w, const __half* cb, void* idx, int N, 
   if (!quantize_args_ok(w, N, K, v, C, idx_bytes)) return VQG_ERR_UNSUPPORTED;
   const int rpc = (rows_per_cb <= 0 || rows_per_cb > N) ? N : rows_per_cb;
   const int G = groups_of(N, rpc);
-  const size_t smem = static_cast<size_t>(C) * v * sizeof(float);
+  const bool packed = static_cast<size_t>(C) * v * 8 <= 200 * 1024;      // the doubled codebook fits: packed fp32 arithmetic
+  const size_t smem = static_cast<size_t>(C) * v * (packed ? 8 : sizeof(float));
   if (smem > 200 * 1024) return VQG_ERR_UNSUPPORTED;
   const long long per_group = static_cast<long long>(rpc) * (K / v);
-  const long long per_cta = static_cast<long long>(kAssignThreads) * kSubPerThread;
+  const long long per_cta = static_cast<long long>(kAssignThreads) * (packed ? 2 * kPairsPerThread : kSubPerThread);
   long long chunks = (per_group + per_cta - 1) / per_cta;
   const long long want = (4LL * sm_count_q() + G - 1) / G;     // about four CTAs per SM in total
   if (chunks > want) chunks = want;
@@ -305,10 +389,10 @@ int launch_quantize_assign(const __half* w, const __half* cb, void* idx, int N, 
   const dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(G));
 #define VQG_ASSIGN(VV, TT)                                                                                       \
   do {                                                                                                           \
-    if (cudaFuncSetAttribute(assign_kernel<VV, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
-                             static_cast<int>(smem)) != cudaSuccess)                                             \
+    auto kern = packed ? assign_packed_kernel<VV, TT> : assign_kernel<VV, TT>;                                   \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) \
       return VQG_ERR_LAUNCH;                                                                                     \
-    assign_kernel<VV, TT><<<grid, kAssignThreads, smem, s>>>(w, cb, static_cast<TT*>(idx), N, K, C, rpc);        \
+    kern<<<grid, kAssignThreads, smem, s>>>(w, cb, static_cast<TT*>(idx), N, K, C, rpc);                         \
   } while (0)
   if (idx_bytes == 1) {
     if (v == 8) VQG_ASSIGN(8, unsigned char); else if (v == 4) VQG_ASSIGN(4, unsigned char); else VQG_ASSIGN(2, unsigned char);

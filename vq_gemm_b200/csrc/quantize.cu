@@ -109,7 +109,7 @@ assign_kernel(const __half* __restrict__ w, const __half* __restrict__ cb, IdxT*
 
 // The same search with Blackwell's packed fp32 arithmetic (sub / mul / add .f32x2: two IEEE operations per
 // instruction, each rounded exactly like its scalar form, so the results are the same bits): a thread searches
-// four sub-vectors as two packed pairs; the codebook sits in shared memory with every value doubled -- (e, e) -- so
+// eight sub-vectors as four packed pairs; the codebook sits in shared memory with every value doubled -- (e, e) -- so
 // that an entry's operands arrive as ready 64-bit pairs.  Needs C * V * 8 bytes of shared memory.
 __device__ __forceinline__ unsigned long long f2_sub(unsigned long long a, unsigned long long b) {
   unsigned long long r; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r;
@@ -124,7 +124,7 @@ __device__ __forceinline__ unsigned long long f2_pack(float lo, float hi) {
   return static_cast<unsigned long long>(__float_as_uint(lo)) | (static_cast<unsigned long long>(__float_as_uint(hi)) << 32);
 }
 
-constexpr int kPairsPerThread = 2;     // packed pairs (four sub-vectors) per thread
+constexpr int kPairsPerThread = 4;     // packed pairs (eight sub-vectors) per thread
 template <int V, typename IdxT>
 __global__ void __launch_bounds__(kAssignThreads)
 assign_packed_kernel(const __half* __restrict__ w, const __half* __restrict__ cb, IdxT* __restrict__ idx, int N, int K, int C,

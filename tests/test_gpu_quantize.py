@@ -105,6 +105,16 @@ def test_pack12_round_trip_and_layout():
     assert torch.equal(VQ.unpack12(packed).cpu(), idx)
     with pytest.raises(RuntimeError):
         VQ.pack12(idx[:, :3].contiguous().cuda())
+    # a count that leaves a tail behind the 16-index groups, and buffers that are only 4-byte aligned (the wide
+    # kernels want 16 / 8 bytes and are not used then)
+    for n, shift in ((16 * 37 + 6, 0), (16 * 5, 2), (10, 0), (4096, 6)):
+        flat = torch.randint(0, 4096, (n + shift,), generator=g).to(torch.int16)
+        buf = flat.cuda()
+        view = buf[shift:]
+        assert view.data_ptr() % 4 == 0
+        pk = VQ.pack12(view)
+        assert np.array_equal(pk.cpu().numpy(), Q.pack12(flat[shift:].numpy()[None])[0])
+        assert torch.equal(VQ.unpack12(pk).cpu(), flat[shift:])
 
 
 def test_product_enqueued_right_behind_the_quantiser_sees_the_new_weights():

@@ -349,6 +349,52 @@ __global__ void unpack12_kernel(const unsigned char* __restrict__ in, uint16_t* 
   }
 }
 
+// Wide forms: a thread moves 16 indices -- 32 bytes of uint16 (two 16-byte accesses) against 24 packed bytes
+// (three 8-byte accesses); both sides 16- / 8-byte aligned, the tail (fewer than 16 indices) goes to the kernels above.
+__global__ void __launch_bounds__(256) pack12_wide_kernel(const uint4* __restrict__ in, uint2* __restrict__ out, long long groups) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < groups;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint4 a = __ldcs(in + 2 * i), b = __ldcs(in + 2 * i + 1);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint32_t p[8];                       // 24 bits each: the pair (lo12, hi12) of one input word
+#pragma unroll
+    for (int j = 0; j < 8; ++j) p[j] = (w[j] & 0xfffu) | (((w[j] >> 16) & 0xfffu) << 12);
+    // eight 24-bit groups -> six 32-bit words
+    uint32_t o[6];
+    o[0] = p[0] | (p[1] << 24);
+    o[1] = (p[1] >> 8) | (p[2] << 16);
+    o[2] = (p[2] >> 16) | (p[3] << 8);
+    o[3] = p[4] | (p[5] << 24);
+    o[4] = (p[5] >> 8) | (p[6] << 16);
+    o[5] = (p[6] >> 16) | (p[7] << 8);
+    __stcs(out + 3 * i, make_uint2(o[0], o[1]));
+    __stcs(out + 3 * i + 1, make_uint2(o[2], o[3]));
+    __stcs(out + 3 * i + 2, make_uint2(o[4], o[5]));
+  }
+}
+
+__global__ void __launch_bounds__(256) unpack12_wide_kernel(const uint2* __restrict__ in, uint4* __restrict__ out, long long groups) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < groups;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint2 a = __ldcs(in + 3 * i), b = __ldcs(in + 3 * i + 1), c = __ldcs(in + 3 * i + 2);
+    const uint32_t o[6] = {a.x, a.y, b.x, b.y, c.x, c.y};
+    uint32_t p[8];
+    p[0] = o[0] & 0xffffffu;
+    p[1] = ((o[0] >> 24) | (o[1] << 8)) & 0xffffffu;
+    p[2] = ((o[1] >> 16) | (o[2] << 16)) & 0xffffffu;
+    p[3] = o[2] >> 8;
+    p[4] = o[3] & 0xffffffu;
+    p[5] = ((o[3] >> 24) | (o[4] << 8)) & 0xffffffu;
+    p[6] = ((o[4] >> 16) | (o[5] << 16)) & 0xffffffu;
+    p[7] = o[5] >> 8;
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) w[j] = (p[j] & 0xfffu) | ((p[j] >> 12) << 16);
+    __stcs(out + 2 * i, make_uint4(w[0], w[1], w[2], w[3]));
+    __stcs(out + 2 * i + 1, make_uint4(w[4], w[5], w[6], w[7]));
+  }
+}
+
 int groups_of(int N, int rows_per_cb) { return rows_per_cb >= N ? 1 : (N + rows_per_cb - 1) / rows_per_cb; }
 
 int sm_count_q() {
@@ -465,15 +511,32 @@ int launch_pack12(const void* in, void* out, long long values, bool pack, cudaSt
   if (values == 0) return VQG_OK;
   const void* two_byte_side = pack ? in : out;
   if (reinterpret_cast<uintptr_t>(two_byte_side) % 4 != 0) return VQG_ERR_BAD_ARG;
-  const long long pairs = values / 2;
-  long long blocks = (pairs + 255) / 256;
   const long long cap = 32LL * sm_count_q();
-  if (blocks > cap) blocks = cap;
-  if (pack)
-    pack12_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const uint16_t*>(in), static_cast<unsigned char*>(out), pairs);
-  else
-    unpack12_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const unsigned char*>(in), static_cast<uint16_t*>(out), pairs);
-  count_launch();
+  const unsigned char* packed_side = static_cast<const unsigned char*>(pack ? out : in);
+  long long done = 0;                                   // indices handled by the wide kernel
+  if (values >= 16 && reinterpret_cast<uintptr_t>(two_byte_side) % 16 == 0 && reinterpret_cast<uintptr_t>(packed_side) % 8 == 0) {
+    const long long groups = values / 16;
+    long long blocks = (groups + 255) / 256;
+    if (blocks > cap) blocks = cap;
+    if (pack)
+      pack12_wide_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const uint4*>(in), static_cast<uint2*>(out), groups);
+    else
+      unpack12_wide_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const uint2*>(in), static_cast<uint4*>(out), groups);
+    count_launch();
+    done = groups * 16;
+  }
+  const long long pairs = (values - done) / 2;
+  if (pairs > 0) {
+    long long blocks = (pairs + 255) / 256;
+    if (blocks > cap) blocks = cap;
+    const uint16_t* u16 = static_cast<const uint16_t*>(two_byte_side) + done;
+    const unsigned char* pk = packed_side + done / 2 * 3;
+    if (pack)
+      pack12_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(u16, const_cast<unsigned char*>(pk), pairs);
+    else
+      unpack12_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(pk, const_cast<uint16_t*>(u16), pairs);
+    count_launch();
+  }
   note_weights_written(s);
   return cuda_status(cudaGetLastError());
 }

@@ -178,3 +178,16 @@ def test_barrier_protocol_when_a_rank_leaves_between_steps():
     assert [e for e, ok, _ in log1] == [1, 2] and all(ok for _, ok, _ in log1) and st1 == 0
     assert [ok for _, ok, _ in log0] == [True, True, False, False]   # steps 3 and 4: the other rank never arrives
     assert st0 == 11 and len(log0) == 4                              # rank 0 noticed and still finished every step
+
+
+def test_lead_slab_is_whole_tiles_and_whole_codebook_groups():
+    from types import SimpleNamespace
+    from vq_gemm_b200.sharded import ShardedVQGemm
+    lead = lambda want, n_local, rpc: ShardedVQGemm._lead(SimpleNamespace(lead_cols=want, n_local=n_local), rpc)
+    assert lead(0, 14336, 128) == 0                      # off by default
+    assert lead(512, 14336, 128) == 512
+    assert lead(600, 14336, 128) == 512                  # rounded down to whole 256-column tiles
+    assert lead(512, 1024, 128) == 0                     # more than a quarter of the block: one launch
+    assert lead(512, 7168, 0) == 512                     # single codebook
+    assert lead(1024, 8192, 384) == 768                  # tiles of 256 and groups of 384 columns meet at 768
+    assert lead(256, 4096, 100) == 0                     # no common multiple inside the block

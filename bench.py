@@ -80,23 +80,60 @@ def _traffic(kernel: str, workload: str):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons of one GPU while a region runs."""
+    """Samples SM clock, power and clock-event reasons of one GPU while a region runs: NVML read-only queries from a
+    thread of this process every millisecond (the timed regions are a few milliseconds long), nvidia-smi polling
+    every 100 ms where NVML's Python binding is missing."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    BITS = (("sw_power_cap", 0x4), ("hw_slowdown", 0x8), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40))
 
-    def __init__(self, index: int, enabled: bool = True):
-        self.index, self.rows, self.proc, self.enabled = index, [], None, enabled
+    def __init__(self, index: int, enabled: bool = True, period_s: float = 0.001):
+        self.index, self.rows, self.proc, self.enabled, self.period_s = index, [], None, enabled, period_s
+        self.stop, self.t, self.source = threading.Event(), None, None
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:   # the CUDA device's own PCI address: CUDA_VISIBLE_DEVICES may renumber the GPUs
+            pr = torch.cuda.get_device_properties(self.index)
+            bus = "%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+            return pynvml, pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
+
+    def _poll_nvml(self, nv, h):
+        mx = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+        reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self.stop.is_set():
+            try:
+                clk = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                mask = int(reasons_fn(h))
+                self.rows.append([clk, mx, pw] + ["Active" if mask & bit else "Not Active" for _, bit in
+                                                  (self.BITS[1], self.BITS[3], self.BITS[2], self.BITS[0])])
+            except Exception:
+                pass
+            time.sleep(self.period_s)
 
     def __enter__(self):
         if not self.enabled:   # one sampler per job: the driver queries of eight pollers delay kernel launches
             return self
+        try:
+            nv, h = self._nvml_handle()
+            self.t = threading.Thread(target=self._poll_nvml, args=(nv, h), daemon=True)
+            self.t.start()
+            self.source = f"nvml, {self.period_s * 1e3:g} ms"
+            return self
+        except Exception:
+            pass
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
+            self.source = "nvidia-smi, 100 ms"
         except Exception:
             self.proc = None
         return self
@@ -106,12 +143,15 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def __exit__(self, *a):
+        self.stop.set()
         if self.proc:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except Exception:
                 self.proc.kill()
+        elif self.t is not None:
+            self.t.join(timeout=1)
 
     def summary(self):
         sm, mx, reasons = [], 0.0, set()
@@ -121,13 +161,13 @@ class ClockSampler:
             except Exception:
                 continue
             mx = max(mx, mxc)
-            if pw > 250.0:  # under load
+            if pw > 250.0 or clk > 1000.0:  # under load (the power reading lags a region of a few milliseconds)
                 sm.append(clk)
                 for name, flag in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
-                    if flag.lower().startswith("active"):
+                    if str(flag).lower().startswith("active"):
                         reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
-                "samples_under_load": len(sm)}
+                "samples_under_load": len(sm), "source": self.source}
 
 
 def _events():
@@ -329,7 +369,7 @@ def _sustained(V, shape, x, idx, cb, peaks, device_index, seconds=2.5):
         V.vq_gemm(x, idx, cb, rows_per_codebook=rpc, layout="bl", out=out)
     torch.cuda.synchronize()
     n = 0
-    with ClockSampler(device_index) as cs:
+    with ClockSampler(device_index, period_s=0.02) as cs:
         t0 = time.perf_counter()
         e0.record()
         while time.perf_counter() - t0 < seconds:

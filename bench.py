@@ -724,7 +724,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5_mlp70b")
     ap.add_argument("--mode", default="auto", choices=["auto", "peer", "multicast", "nccl"],
-                    help="how the N-sharded output is assembled (auto: the faster of peer stores and multimem stores)")
+                    help="how the N-sharded output is assembled (auto: peer stores; both fused modes are timed after the headline for the record)")
     ap.add_argument("--lead-cols", type=int, default=0,
                     help="columns of a rank's block issued as a small first launch in the N-sharded mode (0: one launch per step)")
     ap.add_argument("--no-shapes", action="store_true", help="skip the per-configuration table")

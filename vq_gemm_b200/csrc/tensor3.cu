@@ -404,6 +404,44 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             for (int j = 0; j < 32; ++j) col[j * 128] = __float2half_rn(__uint_as_float(r[j]));
           }
         };
+        if constexpr (!GATED) {
+          // The whole row is converted to fp16 in registers first (two batch columns per register) and tensor
+          // memory handed back before a single shared-memory store is issued: the stores queue behind the dequant
+          // warps' lookups, and every cycle they take before the release is a cycle the tensor pipe stands still.
+          uint32_t hp[BM / 2];
+          uint32_t qa[16], qb[16];                 // 16 columns per load: the row itself takes 128 registers
+          tmem_ld16_async(t_row, qa);
+#pragma unroll
+          for (int c = 0; c < BM / 16; c += 2) {
+            tmem_ld_wait16(qa);
+            tmem_ld16_async(t_row + (c + 1) * 16, qb);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const __half2 h = __floats2half2_rn(__uint_as_float(qa[2 * j]), __uint_as_float(qa[2 * j + 1]));
+              hp[c * 8 + j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            tmem_ld_wait16(qb);
+            if (c + 2 < BM / 16) {
+              tmem_ld16_async(t_row + (c + 2) * 16, qa);
+            } else {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive_remote(leader_acc_empty);
+              released = true;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const __half2 h = __floats2half2_rn(__uint_as_float(qb[2 * j]), __uint_as_float(qb[2 * j + 1]));
+              hp[(c + 1) * 8 + j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+          }
+          unsigned short* col = reinterpret_cast<unsigned short*>(stg) + quarter * 32 + lane;   // T[m][weight row]
+#pragma unroll
+          for (int q = 0; q < BM / 2; ++q) {
+            col[(2 * q) * 128] = static_cast<unsigned short>(hp[q] & 0xffffu);
+            col[(2 * q + 1) * 128] = static_cast<unsigned short>(hp[q] >> 16);
+          }
+        } else {
         tmem_ld32_async(t_row, ra);
 #pragma unroll 1
         for (int c = 0; c < BM / 32; c += 2) {
@@ -420,6 +458,7 @@ vq_tensor_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             released = true;
           }
           put(c + 1, rb);
+        }
         }
       } else {
         // a piece of a tile: the fp32 partial goes to this pair's slot (0 when the pair's range begins

@@ -63,7 +63,11 @@ def main():
     sys.path.insert(0, ROOT)
     from oracle import vq_oracle as O
 
-    bench, captured = import_reference_bench()
+    only = set(sys.argv[1:])          # fixture names to (re)write; none given: all of them
+    want = lambda tag: not only or tag in only
+    bench = captured = None
+    if not only or any(t.startswith("ref_") for t in only):
+        bench, captured = import_reference_bench()
 
     # REF-layout cases: (M, K, Nq, seed)
     for tag, (M, K, Nq, seed) in {
@@ -75,6 +79,8 @@ def main():
         # single codebook -- the one case in which the reference's own code pins the BL gather
         "ref_nq4_bridge": (16, 2048, 4, 11),
     }.items():
+        if not want(tag):
+            continue
         x, w, cb = O.make_ref_inputs(M, K, Nq, seed=seed)
         y = bench.vq_gemm_reference(x, w, cb)
         np.savez_compressed(
@@ -91,6 +97,8 @@ def main():
         "bl_v8_c4096_single": (16, 128, 48, 8, 4096, 0, 1),
         "bl_v8_c256_groups": (130, 128, 256, 8, 256, 128, 2),
     }.items():
+        if not want(tag):
+            continue
         x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=seed)
         wdec = O.dequant_bl_scalar(idx, cb, rpc)
         y = O.matmul_fp32acc(x, wdec)
@@ -105,11 +113,31 @@ def main():
 
     # residual (two-codebook) case, written by the scalar-loop statement of the rule: (M, K, N, v, C, rpc, stages, seed)
     for tag, (M, K, N, v, C, rpc, stages, seed) in {"bl_residual_v8_c256_s2": (20, 128, 256, 8, 256, 128, 2, 3)}.items():
+        if not want(tag):
+            continue
         x, idx, cb = O.make_residual_inputs(M, K, N, v, C, rpc, stages=stages, seed=seed)
         wdec = O.dequant_bl_residual_scalar(idx, cb, rpc)
         y = O.matmul_fp32acc(x, wdec)
         np.savez_compressed(os.path.join(HERE, f"{tag}.npz"), x=x.numpy(), idx=idx.numpy(), codebook=cb.numpy(),
                             w_decoded=wdec.numpy(), y=y.numpy(), meta=np.array([M, K, N, v, C, rpc, stages, seed]))
+        print(tag, "written", tuple(y.shape))
+
+    # 12-bit indices packed two to three bytes (little end first): the packing written out byte by byte here,
+    # the weights by the scalar-loop statement of the gather on the unpacked indices: (M, K, N, v, C, rpc, seed)
+    for tag, (M, K, N, v, C, rpc, seed) in {"bl_v8_c4096_packed12": (12, 128, 64, 8, 4096, 0, 5)}.items():
+        if not want(tag):
+            continue
+        x, idx, cb = O.make_bl_inputs(M, K, N, v, C, rpc, seed=seed, idx_dtype=torch.int16)
+        flat = idx.numpy().astype(np.int64).reshape(N, -1)
+        packed = np.zeros((N, flat.shape[1] * 3 // 2), dtype=np.uint8)
+        for n in range(N):
+            for j in range(0, flat.shape[1], 2):
+                a, b = int(flat[n, j]), int(flat[n, j + 1])
+                packed[n, 3 * (j // 2):3 * (j // 2) + 3] = [a & 255, (a >> 8) | ((b & 15) << 4), b >> 4]
+        wdec = O.dequant_bl_scalar(idx, cb, rpc)
+        y = O.matmul_fp32acc(x, wdec)
+        np.savez_compressed(os.path.join(HERE, f"{tag}.npz"), x=x.numpy(), idx=idx.numpy(), packed=packed, codebook=cb.numpy(),
+                            w_decoded=wdec.numpy(), y=y.numpy(), meta=np.array([M, K, N, v, C, rpc, seed]))
         print(tag, "written", tuple(y.shape))
 
 

@@ -62,6 +62,15 @@ def test_c3_shape_packed_whole_output():
     assert_within_tolerance(y.cpu(), O.vq_gemm_bl(x, idx, cb, 0))
 
 
+def test_golden_fixture():
+    from tests._util import load_golden
+    g = load_golden("bl_v8_c4096_packed12")
+    w = V.dequant(g["packed"].cuda(), g["codebook"].cuda(), rows_per_codebook=0, index_bits=12)
+    assert torch.equal(bits(w), bits(g["w_decoded"]))
+    y = V.vq_gemm(g["x"].cuda(), g["packed"].cuda(), g["codebook"].cuda(), index_bits=12)
+    assert_within_tolerance(y.cpu(), g["y"])
+
+
 def test_argument_checks():
     x, idx, cb = O.make_bl_inputs(4, 64, 32, 8, 4096, 0, seed=1, idx_dtype=torch.int16)
     pk = _packed(idx).cuda()

@@ -49,10 +49,21 @@ def test_bl_gather_matches_bytes_gathered_by_the_reference(golden_dir):
     assert torch.equal(b.view(torch.int16), g["w_decoded"][:64].view(torch.int16))
 
 
+def test_packed_index_fixture(golden_dir):
+    """The fixture's packed bytes (written byte by byte by its generator) against the numpy packer, both ways, and
+    the weights behind them."""
+    from oracle import quantize_oracle as Q
+    g = _load(os.path.join(golden_dir, "bl_v8_c4096_packed12.npz"))
+    assert np.array_equal(Q.pack12(g["idx"].numpy()), g["packed"].numpy())
+    assert np.array_equal(Q.unpack12(g["packed"].numpy()), g["idx"].numpy())
+    wdec = O.dequant_bl_layout(torch.from_numpy(Q.unpack12(g["packed"].numpy())), g["codebook"], 0)
+    assert torch.equal(wdec.view(torch.int16), g["w_decoded"].view(torch.int16))
+
+
 def test_golden_files_all_covered(golden_dir):
     tags = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(golden_dir, "*.npz")))
-    assert tags == ["bl_residual_v8_c256_s2", "bl_v4_c256_groups", "bl_v8_c256_groups", "bl_v8_c4096_single",
-                    "ref_nq4_bridge", "ref_ragged", "ref_small", "ref_two_tiles"]
+    assert tags == ["bl_residual_v8_c256_s2", "bl_v4_c256_groups", "bl_v8_c256_groups", "bl_v8_c4096_packed12",
+                    "bl_v8_c4096_single", "ref_nq4_bridge", "ref_ragged", "ref_small", "ref_two_tiles"]
 
 
 @pytest.mark.parametrize("N,K,v,C,rpc,dtype", [

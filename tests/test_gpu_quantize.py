@@ -21,6 +21,8 @@ def _weights(N, K, seed, sigma=0.05):
     (128, 128, 2, 256, 0),
     (200, 64, 4, 37, 128),       # ragged last group, odd codebook size
     (64, 256, 8, 4096, 0),       # 2-byte indices, single large codebook
+    (96, 256, 8, 1024, 0),       # 2-byte indices, codebook that still fits the packed search and the 32-bit counters
+    (512, 2048, 4, 256, 128),    # several accumulation rounds per block
 ])
 def test_assign_and_update_match_the_rules_bit_for_bit(N, K, v, C, rpc):
     w = _weights(N, K, seed=N + K + v)

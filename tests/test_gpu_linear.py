@@ -115,6 +115,20 @@ def test_residual_quantiser_lowers_the_error_stage_by_stage():
     assert torch.equal(i1, i2[0]) and torch.equal(bits(c1), bits(c2[0]))
 
 
+def test_packed_module_equals_the_int16_layer():
+    x, idx, cb = O.make_bl_inputs(40, 512, 256, 8, 4096, 0, seed=11, idx_dtype=torch.int16)
+    layer = VQLinear(idx, cb, 0).cuda()
+    packed = layer.pack()
+    assert packed.packed and packed.indices.shape == (256, 96) and packed.in_features == 512
+    y, yp = layer(x.cuda()), packed(x.reshape(2, 20, 512).cuda()).reshape(40, 256)
+    assert_within_tolerance(yp.cpu(), O.vq_gemm_bl(x, idx, cb, 0))
+    assert torch.equal(bits(packed.dequantized_weight()), bits(layer.dequantized_weight()))
+    assert float((y.float() - yp.float()).abs().max()) <= 2e-2 * (float(y.abs().max()) + 1)
+    torch.library.opcheck(torch.ops.vq_gemm_b200.vq_linear_packed12.default, (x.cuda(), packed.indices, cb.cuda(), 0),
+                          test_utils=("test_schema", "test_faketensor"))
+    assert set(packed.state_dict()) == {"indices", "codebook"} and "packed12=True" in repr(packed)
+
+
 def test_gated_module_and_operator():
     from vq_gemm_b200.linear import VQGatedUp
     x, idx, cb = O.make_bl_inputs(160, 512, 512, 8, 256, 128, seed=7, cb_sigma=0.05)

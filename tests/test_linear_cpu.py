@@ -42,6 +42,23 @@ def test_residual_module_bookkeeping():
         VQLinear(idx, cb[0], 128)
 
 
+def test_packed_module_bookkeeping_and_fake_rule():
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    pk = torch.zeros(64, 96, dtype=torch.uint8)              # 64 indices of 12 bits per row
+    cb = torch.zeros(1, 4096, 8, dtype=torch.float16)
+    layer = VQLinear(pk, cb, 0, index_bits=12)
+    assert layer.packed and (layer.in_features, layer.out_features) == (512, 64)
+    with pytest.raises(ValueError):
+        VQLinear(torch.zeros(64, 95, dtype=torch.uint8), cb, 0, index_bits=12)
+    with pytest.raises(ValueError):
+        VQLinear(pk, cb, 0, index_bits=10)
+    with FakeTensorMode():
+        x = torch.empty(5, 512, dtype=torch.float16, device="cuda")
+        y = torch.ops.vq_gemm_b200.vq_linear_packed12(x, torch.empty(64, 96, dtype=torch.uint8, device="cuda"),
+                                                       torch.empty(1, 4096, 8, dtype=torch.float16, device="cuda"), 0)
+        assert y.shape == (5, 64) and y.dtype == torch.float16
+
+
 def test_module_bookkeeping_and_checks():
     idx = torch.zeros(256, 64, dtype=torch.uint8)
     cb = torch.zeros(2, 256, 8, dtype=torch.float16)

@@ -48,6 +48,21 @@ def _(x, indices, codebook, rows_per_codebook):
     return x.new_empty((x.shape[0], indices.shape[1]))
 
 
+@torch.library.custom_op("vq_gemm_b200::vq_linear_packed12", mutates_args=(), device_types="cuda")
+def vq_linear_packed12(x: torch.Tensor, packed: torch.Tensor, codebook: torch.Tensor, rows_per_codebook: int) -> torch.Tensor:
+    """12-bit indices packed two to three bytes: x [M, K] fp16, packed [N, K/v * 3/2] uint8, codebook [G, C, v]."""
+    return ops.vq_gemm(x, packed, codebook, rows_per_codebook=rows_per_codebook, layout="bl", index_bits=12)
+
+
+@vq_linear_packed12.register_fake
+def _(x, packed, codebook, rows_per_codebook):
+    if x.dim() != 2 or packed.dim() != 2 or codebook.dim() != 3 or packed.shape[1] % 3:
+        raise RuntimeError("vq_linear_packed12 expects x [M, K], packed [N, K/v * 3/2], codebook [G, C, v]")
+    if packed.shape[1] * 2 // 3 * codebook.shape[2] != x.shape[1]:
+        raise RuntimeError("packed [N, K/v * 3/2] and codebook [G, C, v] do not match x [M, K]")
+    return x.new_empty((x.shape[0], packed.shape[0]))
+
+
 @torch.library.custom_op("vq_gemm_b200::vq_swiglu", mutates_args=(), device_types="cuda")
 def vq_swiglu(x: torch.Tensor, indices: torch.Tensor, codebook: torch.Tensor, rows_per_codebook: int) -> torch.Tensor:
     """x [M, K]; indices [2*N_out, K/v] with (gate, up) row pairs -> SiLU(x g^T) * (x u^T), [M, N_out] fp16."""
@@ -73,11 +88,20 @@ class VQLinear(nn.Module):
 
     Residual (multi-codebook) weights: ``indices`` [S, out_features, in_features / v] and ``codebook``
     [S, groups, C, v]; the weight is the running fp16 sum of the S stages' entries (``from_weight(stages=2)``).
+
+    ``index_bits=12``: ``indices`` is the uint8 [out_features, in_features / v * 3/2] tensor ``quantize.pack12``
+    makes of 12-bit indices (codebooks of up to 4096 entries at 1.5 bytes per index); ``pack()`` converts a layer
+    that holds them in int16.
     """
 
     def __init__(self, indices: torch.Tensor, codebook: torch.Tensor, rows_per_codebook: int = 0,
-                 bias: Optional[torch.Tensor] = None):
+                 bias: Optional[torch.Tensor] = None, index_bits: Optional[int] = None):
         super().__init__()
+        self.packed = index_bits == 12
+        if index_bits not in (None, 8, 16, 12):
+            raise ValueError("index_bits must be 8, 16 or 12 (packed)")
+        if self.packed and (indices.dim() != 2 or indices.dtype != torch.uint8 or indices.shape[1] % 3):
+            raise ValueError("packed indices must be a uint8 [N, K/v * 3/2] tensor")
         self.residual = indices.dim() == 3
         if self.residual:
             if codebook.dim() != 4 or codebook.shape[0] != indices.shape[0]:
@@ -93,7 +117,7 @@ class VQLinear(nn.Module):
             raise ValueError(f"{cb.shape[-3]} codebooks given, {groups} needed")
         self.out_features = N
         self.v = cb.shape[-1]
-        self.in_features = indices.shape[-1] * self.v
+        self.in_features = (indices.shape[-1] * 2 // 3 if self.packed else indices.shape[-1]) * self.v
         self.rows_per_codebook = int(rows_per_codebook)
         self.register_buffer("indices", indices.contiguous())
         self.register_buffer("codebook", cb.to(torch.float16).contiguous())
@@ -124,7 +148,8 @@ class VQLinear(nn.Module):
         x2 = x.reshape(-1, self.in_features)
         if x2.dtype != torch.float16:
             x2 = x2.to(torch.float16)
-        op = torch.ops.vq_gemm_b200.vq_linear_residual if self.residual else torch.ops.vq_gemm_b200.vq_linear
+        op = (torch.ops.vq_gemm_b200.vq_linear_residual if self.residual else
+              torch.ops.vq_gemm_b200.vq_linear_packed12 if self.packed else torch.ops.vq_gemm_b200.vq_linear)
         y = op(x2.contiguous(), self.indices, self.codebook, self.rows_per_codebook)
         if self.bias is not None:
             y = y + self.bias
@@ -134,12 +159,22 @@ class VQLinear(nn.Module):
         """The dense fp16 [out_features, in_features] weight this layer stands for (bit-exact gather)."""
         if self.residual:
             return ops.dequant_residual(self.indices, self.codebook, rows_per_codebook=self.rows_per_codebook)
-        return ops.dequant(self.indices, self.codebook, rows_per_codebook=self.rows_per_codebook)
+        return ops.dequant(self.indices, self.codebook, rows_per_codebook=self.rows_per_codebook,
+                           index_bits=12 if self.packed else None)
+
+    def pack(self) -> "VQLinear":
+        """The same layer with its 12-bit indices (held in int16, at most 4096 entries) packed two to three bytes."""
+        from .quantize import pack12
+        if self.packed:
+            return self
+        if self.residual or self.indices.dtype == torch.uint8 or self.codebook.shape[-2] > 4096:
+            raise RuntimeError("pack() is for plain weights with int16 indices and at most 4096 entries")
+        return VQLinear(pack12(self.indices), self.codebook, self.rows_per_codebook, self.bias, index_bits=12)
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, v={self.v}, "
                 f"entries={self.codebook.shape[-2]}, rows_per_codebook={self.rows_per_codebook}, "
-                f"stages={self.indices.shape[0] if self.residual else 1}, bias={self.bias is not None}")
+                f"stages={self.indices.shape[0] if self.residual else 1}, packed12={self.packed}, bias={self.bias is not None}")
 
 
 class VQGatedUp(nn.Module):

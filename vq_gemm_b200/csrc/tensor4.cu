@@ -400,9 +400,24 @@ vq_small_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallParams
           if constexpr (WPS == 4) {
             const uint4 v = __ldcs(reinterpret_cast<const uint4*>(src));
             dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
-          } else if constexpr (WPS == 3) {               // packed: 12 bytes, 4-byte aligned
+          } else if constexpr (WPS == 3) {               // packed: 12 bytes at a multiple of 4 (rows are multiples of 24 bytes)
             const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src);
-            dst[0] = __ldcs(s32); dst[1] = __ldcs(s32 + 1); dst[2] = __ldcs(s32 + 2);
+            // position inside an aligned 16-byte chunk (the same for every lane when K is a multiple of 256); the
+            // 16-byte load at position 0 reads 4 bytes past the 12 and is not used on a row's last sub-step
+            const uint32_t in16 = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(src) & 15);
+            if (in16 == 0 && (ks0 + t + 1) * BK < p.K) {                // inside one aligned chunk: one load
+              const uint4 q = __ldcs(reinterpret_cast<const uint4*>(src));
+              dst[0] = q.x; dst[1] = q.y; dst[2] = q.z;
+            } else if (in16 == 4) {
+              const uint4 q = __ldcs(reinterpret_cast<const uint4*>(src - 4));
+              dst[0] = q.y; dst[1] = q.z; dst[2] = q.w;
+            } else if ((in16 & 4) == 0) {                               // 8 + 4 bytes
+              const uint2 lo = __ldcs(reinterpret_cast<const uint2*>(src));
+              dst[0] = lo.x; dst[1] = lo.y; dst[2] = __ldcs(s32 + 2);
+            } else {                                                    // 4 + 8 bytes
+              const uint2 hi = __ldcs(reinterpret_cast<const uint2*>(src + 4));
+              dst[0] = __ldcs(s32); dst[1] = hi.x; dst[2] = hi.y;
+            }
           } else {
             const uint2 v = __ldcs(reinterpret_cast<const uint2*>(src));
             dst[0] = v.x; dst[1] = v.y;

@@ -35,6 +35,9 @@ def test_dequant_of_packed_indices_is_bit_exact(N, K, v, C, rpc):
     (1, 512, 2048, 8, 4096, 0, "small_ts"),
     (100, 256, 512, 8, 1000, 128, "small_ts"),
     (128, 384, 256, 8, 256, 128, "small_ts"),      # a small codebook in packed form still takes the unreplicated image
+    (16, 256, 384, 8, 4096, 0, "small_ts"),        # rows of 72 bytes: neighbouring rows sit differently in their 16-byte chunks
+    (3, 128, 128, 8, 512, 0, "small_ts"),          # one pipeline stage per row
+    (40, 640, 896, 8, 4096, 128, "small_ts"),
     (300, 512, 1024, 8, 4096, 0, "two_phase"),
     (64, 256, 256, 4, 2048, 0, "two_phase"),       # v = 4: no tensor-memory instance, dequantise first
     (5, 96, 40, 4, 3000, 0, "generic"),

@@ -105,6 +105,20 @@ def test_bl_streaming_form(N, K, v, C, rpc, dt, S):
         assert torch.equal(bits(w), bits(O.dequant_bl_residual(idx, cb, rpc)))
 
 
+@pytest.mark.parametrize("C,dt", [(100, torch.uint8), (1000, torch.int16)])
+def test_indices_beyond_the_codebook_read_its_last_entry(C, dt):
+    # malformed input: the streaming kernel keeps its lookups inside the shared-memory image
+    _, idx, cb = O.make_bl_inputs(1, 256, 128, 8, C, 0, seed=C, idx_dtype=dt)
+    bad = idx.clone()
+    bad[3, 5] = C + 7 if dt == torch.uint8 else 30000
+    bad[100, 0] = C
+    w = V.dequant(bad.cuda(), cb.cuda(), rows_per_codebook=0)
+    fixed = idx.clone()
+    fixed[3, 5] = C - 1
+    fixed[100, 0] = C - 1
+    assert torch.equal(bits(w), bits(O.dequant_bl_layout(fixed, cb, 0)))
+
+
 def test_empty():
     idx = torch.zeros(0, 16, dtype=torch.uint8).cuda()
     cb = torch.zeros(1, 256, 4, dtype=torch.float16).cuda()

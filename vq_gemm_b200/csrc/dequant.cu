@@ -64,15 +64,17 @@ template <> struct IdxWord<4, uint16_t> { using T = uint32_t; };
 template <> struct IdxWord<2, uint8_t> { using T = uint32_t; };
 template <> struct IdxWord<2, uint16_t> { using T = uint2; };
 
+// `cmax` = C - 1: an index beyond the codebook (malformed input) reads the last entry instead of running past
+// the image in shared memory.
 template <int V, typename IdxT, typename W>
-__device__ __forceinline__ uint4 lookup16(const typename Entry<V>::T* tab, W word, int reps) {
+__device__ __forceinline__ uint4 lookup16(const typename Entry<V>::T* tab, W word, int reps, uint32_t cmax) {
   if constexpr (V == 8) {
-    return tab[static_cast<uint32_t>(word) * reps];
+    return tab[min(static_cast<uint32_t>(word), cmax) * reps];
   } else if constexpr (V == 4) {
     uint32_t c0, c1;
     if constexpr (sizeof(IdxT) == 1) { c0 = word & 0xffu; c1 = word >> 8; }
     else { c0 = word & 0xffffu; c1 = word >> 16; }
-    const uint2 e0 = tab[c0 * reps], e1 = tab[c1 * reps];
+    const uint2 e0 = tab[min(c0, cmax) * reps], e1 = tab[min(c1, cmax) * reps];
     return make_uint4(e0.x, e0.y, e1.x, e1.y);
   } else {
     uint32_t c[4];
@@ -81,7 +83,8 @@ __device__ __forceinline__ uint4 lookup16(const typename Entry<V>::T* tab, W wor
     } else {
       c[0] = word.x & 0xffffu; c[1] = word.x >> 16; c[2] = word.y & 0xffffu; c[3] = word.y >> 16;
     }
-    return make_uint4(tab[c[0] * reps], tab[c[1] * reps], tab[c[2] * reps], tab[c[3] * reps]);
+    return make_uint4(tab[min(c[0], cmax) * reps], tab[min(c[1], cmax) * reps], tab[min(c[2], cmax) * reps],
+                      tab[min(c[3], cmax) * reps]);
   }
 }
 
@@ -106,6 +109,7 @@ __global__ void __launch_bounds__(512) dequant_bl_stream_kernel(const IdxT* __re
   const int row_hi = static_cast<int>(static_cast<long long>(N) * (blockIdx.x + 1) / gridDim.x);
   const E* mine = img + (threadIdx.x & (reps - 1));
   const int nt = blockDim.x;
+  const uint32_t cmax = static_cast<uint32_t>(C - 1);
   for (int r0 = row_lo; r0 < row_hi;) {
     const int g = r0 / rows_per_cb;
     const int r1 = min(row_hi, (g + 1) * rows_per_cb);
@@ -133,10 +137,10 @@ __global__ void __launch_bounds__(512) dequant_bl_stream_kernel(const IdxT* __re
       for (int u = 0; u < U; ++u) {
         const long long i = i0 + static_cast<long long>(u) * nt;
         if (i < total) {
-          uint4 out = lookup16<V, IdxT, W>(mine, word[u][0], reps);
+          uint4 out = lookup16<V, IdxT, W>(mine, word[u][0], reps, cmax);
 #pragma unroll
           for (int st = 1; st < STAGES; ++st) {
-            const uint4 e = lookup16<V, IdxT, W>(mine + static_cast<size_t>(st) * img_entries, word[u][st], reps);
+            const uint4 e = lookup16<V, IdxT, W>(mine + static_cast<size_t>(st) * img_entries, word[u][st], reps, cmax);
             out.x = hadd2_u32(out.x, e.x); out.y = hadd2_u32(out.y, e.y);
             out.z = hadd2_u32(out.z, e.z); out.w = hadd2_u32(out.w, e.w);
           }

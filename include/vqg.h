@@ -101,7 +101,8 @@ VQG_API int vqg_auto_path(int M, int N, int K, int v, int C, int idx_bytes, int 
  *                      is K/v * 3/2 bytes
  *   (every index must be below C: like the reference's kernels, the product kernels look entries up in a
  *   shared-memory image of the codebook without a range check -- a larger index is the caller's error and may
- *   end the launch with an illegal address; vqg_dequant and the packed forms clamp instead)
+ *   end the launch with an illegal address; vqg_dequant, the packed forms and the shape-agnostic kernel
+ *   read the codebook's last entry instead)
  *   rows_per_codebook  BL: output rows sharing a codebook, 0 = one codebook for the matrix
  *                      REF: ignored (8 output columns per codebook)
  *   stream             cudaStream_t (NULL = legacy default stream, as the reference uses)

@@ -119,6 +119,17 @@ def test_indices_beyond_the_codebook_read_its_last_entry(C, dt):
     assert torch.equal(bits(w), bits(O.dequant_bl_layout(fixed, cb, 0)))
 
 
+def test_indices_beyond_the_codebook_in_the_plain_kernels():
+    # K/v = 7 is not a whole number of 16-byte outputs: the plain dequant kernel; and the shape-agnostic product
+    x, idx, cb = O.make_bl_inputs(3, 14, 40, 2, 50, 0, seed=4)
+    bad, fixed = idx.clone(), idx.clone()
+    bad[7, 3], fixed[7, 3] = 250, 49
+    w = V.dequant(bad.cuda(), cb.cuda(), rows_per_codebook=0)
+    assert torch.equal(bits(w), bits(O.dequant_bl_layout(fixed, cb, 0)))
+    y = V.vq_gemm(x.cuda(), bad.cuda(), cb.cuda(), rows_per_codebook=0, path="generic")
+    assert O.check_tolerance(y.cpu(), O.vq_gemm_bl(x, fixed, cb, 0))["ok"]
+
+
 def test_empty():
     idx = torch.zeros(0, 16, dtype=torch.uint8).cuda()
     cb = torch.zeros(1, 256, 4, dtype=torch.float16).cuda()

@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(256) dequant_bl_kernel(const IdxT* __restrict_
   const IdxT* ip = idx + static_cast<size_t>(row0) * J;
   E* op = reinterpret_cast<E*>(w + static_cast<size_t>(row0) * K);
   for (long long i = threadIdx.x; i < total; i += blockDim.x) {
-    op[i] = table[ip[i]];
+    op[i] = table[min(static_cast<int>(ip[i]), C - 1)];   // an index beyond the codebook reads its last entry
   }
 }
 
@@ -544,9 +544,10 @@ __global__ void __launch_bounds__(256) dequant_bl_residual_kernel(const IdxT* __
     __half2 acc[V / 2];
 #pragma unroll
     for (int r = 0; r < V / 2; ++r)
-      acc[r] = reinterpret_cast<const __half2*>(cb + (static_cast<size_t>(g) * C + idx[e]) * V)[r];
+      acc[r] = reinterpret_cast<const __half2*>(cb + (static_cast<size_t>(g) * C + min(static_cast<int>(idx[e]), C - 1)) * V)[r];
     for (int st = 1; st < stages; ++st) {
-      const __half2* ent = reinterpret_cast<const __half2*>(cb + ((static_cast<size_t>(st) * groups + g) * C + idx[static_cast<size_t>(st) * total + e]) * V);
+      const int cs = min(static_cast<int>(idx[static_cast<size_t>(st) * total + e]), C - 1);
+      const __half2* ent = reinterpret_cast<const __half2*>(cb + ((static_cast<size_t>(st) * groups + g) * C + cs) * V);
 #pragma unroll
       for (int r = 0; r < V / 2; ++r) acc[r] = __hadd2(acc[r], ent[r]);
     }
@@ -611,13 +612,14 @@ __global__ void __launch_bounds__(256) generic_vq_gemm_kernel(Problem p) {
             } else {
               c = p.idx_bytes == 1 ? idx8[ii] : idx16[ii];
             }
+            c = min(c, p.C - 1);   // this kernel checks the range (the specialised ones trust the caller)
             const int g = n / p.rows_per_cb;
             __half w = p.cb[(static_cast<size_t>(g) * p.C + c) * p.v + (k % p.v)];
             // residual stages: the fp16 running sum of the stages' entries (each addition rounded to fp16)
             const int groups = (p.N + p.rows_per_cb - 1) / p.rows_per_cb;
             for (int st = 1; st < p.n_stages; ++st) {
               const size_t is = static_cast<size_t>(st) * p.N * J + ii;
-              const int cs = p.idx_bytes == 1 ? idx8[is] : idx16[is];
+              const int cs = min(static_cast<int>(p.idx_bytes == 1 ? idx8[is] : idx16[is]), p.C - 1);
               w = __hadd(w, p.cb[((static_cast<size_t>(st) * groups + g) * p.C + cs) * p.v + (k % p.v)]);
             }
             wv = __half2float(w);

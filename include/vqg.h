@@ -99,10 +99,9 @@ VQG_API int vqg_auto_path(int M, int N, int K, int v, int C, int idx_bytes, int 
  *                      vqg_workspace_bytes, vqg_auto_path only; BL layout): two 12-bit indices in three
  *                      bytes as vqg_pack12 writes them, K/v even, C <= 4096; a row of the index matrix
  *                      is K/v * 3/2 bytes
- *   (every index must be below C: like the reference's kernels, the product kernels look entries up in a
- *   shared-memory image of the codebook without a range check -- a larger index is the caller's error and may
- *   end the launch with an illegal address; vqg_dequant, the packed forms and the shape-agnostic kernel
- *   read the codebook's last entry instead)
+ *   (every index must be below C.  A larger one is the caller's error; the kernels keep it from addressing
+ *   past the codebook -- 16-bit and packed indices are clamped to the last entry, 8-bit ones stay inside the
+ *   256-entry image region -- so the result for that weight is meaningless but the launch completes)
  *   rows_per_codebook  BL: output rows sharing a codebook, 0 = one codebook for the matrix
  *                      REF: ignored (8 output columns per codebook)
  *   stream             cudaStream_t (NULL = legacy default stream, as the reference uses)

@@ -126,29 +126,31 @@ __device__ __forceinline__ uint2 lds64_tile(uint32_t addr) {
   return r;
 }
 
+// 16-bit indices are held below `cmax` + 1 = C (a larger one -- malformed input -- would address past the image
+// and end the launch); 8-bit ones cannot leave the 256-entry image region.
 template <int IB>
-__device__ __forceinline__ uint32_t idx_at(const uint32_t* w, int i) {
+__device__ __forceinline__ uint32_t idx_at(const uint32_t* w, int i, uint32_t cmax) {
   if constexpr (IB == 1) return __byte_perm(w[i >> 2], 0, 0x4440 + (i & 3));
-  else return __byte_perm(w[i >> 1], 0, (i & 1) ? 0x4432 : 0x4410);
+  else return min(__byte_perm(w[i >> 1], 0, (i & 1) ? 0x4432 : 0x4410), cmax);
 }
 
 // The products of one thread for 64 of its K values and one 8-row unit: `w` holds the indices of those K values,
 // `xf` the matching X fragment registers, `img` is the lane's replica inside the group's codebook image.
 template <int V, int IB, int FORM, int ENTRY_SHIFT>
 __device__ __forceinline__ void piece_mma(float (&acc)[4][4], const uint32_t* w, const uint32_t* xf,
-                                          uint32_t img, uint32_t epoch) {
+                                          uint32_t img, uint32_t epoch, uint32_t cmax) {
   if constexpr (FORM == 1) {
     if constexpr (V == 4) {
       uint2 e[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) e[i] = lds64(img + (idx_at<IB>(w, i) << ENTRY_SHIFT), epoch);
+      for (int i = 0; i < 16; ++i) e[i] = lds64(img + (idx_at<IB>(w, i, cmax) << ENTRY_SHIFT), epoch);
 #pragma unroll
       for (int q = 0; q < 8; ++q)
         mma_16816(acc[q & 3], e[2 * q].x, e[2 * q].y, e[2 * q + 1].x, e[2 * q + 1].y, xf[2 * q], xf[2 * q + 1]);
     } else {
       uint4 e[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) e[i] = lds128(img + (idx_at<IB>(w, i) << ENTRY_SHIFT), epoch);
+      for (int i = 0; i < 8; ++i) e[i] = lds128(img + (idx_at<IB>(w, i, cmax) << ENTRY_SHIFT), epoch);
 #pragma unroll
       for (int q = 0; q < 8; ++q) mma_16816(acc[q & 3], e[q].x, e[q].y, e[q].z, e[q].w, xf[2 * q], xf[2 * q + 1]);
     }
@@ -159,7 +161,7 @@ __device__ __forceinline__ void piece_mma(float (&acc)[4][4], const uint32_t* w,
       for (int hf = 0; hf < 2; ++hf) {   // two halves of 8 lookups keep the register count down
         uint2 e[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) e[i] = lds64(img + (idx_at<IB>(w, 8 * hf + i) << ENTRY_SHIFT), epoch);
+        for (int i = 0; i < 8; ++i) e[i] = lds64(img + (idx_at<IB>(w, 8 * hf + i, cmax) << ENTRY_SHIFT), epoch);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int ii = 8 * hf + i;
@@ -172,7 +174,7 @@ __device__ __forceinline__ void piece_mma(float (&acc)[4][4], const uint32_t* w,
       for (int hf = 0; hf < 2; ++hf) {   // two halves of 4 lookups keep the register count down
         uint4 e[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) e[i] = lds128(img + (idx_at<IB>(w, 4 * hf + i) << ENTRY_SHIFT), epoch);
+        for (int i = 0; i < 4; ++i) e[i] = lds128(img + (idx_at<IB>(w, 4 * hf + i, cmax) << ENTRY_SHIFT), epoch);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int ii = 4 * hf + i;
@@ -292,6 +294,7 @@ vq_decode_kernel(const __grid_constant__ CUtensorMap idx_map, const DecodeParams
   uint32_t c_parity = 0;
 
   const uint32_t img_bytes = static_cast<uint32_t>(p.C) << ENTRY_SHIFT;
+  const uint32_t cmax = static_cast<uint32_t>(p.C - 1);
   // this lane's replica inside an image (32-bit shared address of slot 0)
   const uint32_t img_lane = base + p.img_offset + ((lane & ((1 << REP_LOG2) - 1)) << ENTRY_LOG2);
   uint32_t epoch = 0;
@@ -487,7 +490,7 @@ vq_decode_kernel(const __grid_constant__ CUtensorMap idx_map, const DecodeParams
             for (int c = 0; c < 4; ++c) ch[a][c] = 0.f;
 #pragma unroll
           for (int pc = 0; pc < PIECES; ++pc)
-            piece_mma<V, IB, FORM, ENTRY_SHIFT>(ch, w + pc * W64, xf + pc * (XR / PIECES), img_s, epoch);
+            piece_mma<V, IB, FORM, ENTRY_SHIFT>(ch, w + pc * W64, xf + pc * (XR / PIECES), img_s, epoch, cmax);
           float acc[4];
 #pragma unroll
           for (int c = 0; c < 4; ++c) acc[c] = (ch[0][c] + ch[1][c]) + (ch[2][c] + ch[3][c]);
@@ -714,6 +717,12 @@ bool make_plan(const Problem& p, Plan& pl) {
   d.part_offset = static_cast<int>(d.img_offset + d.nslots * img_bytes);
   d.acc_offset = static_cast<int>(d.part_offset + part_bytes);
   pl.smem = d.acc_offset + acc_bytes + 1024;   // + alignment slack
+  if (p.idx_bytes == 1 && p.C < 256) {
+    // an 8-bit index beyond a small codebook (malformed input) must still address inside the block's shared
+    // memory: room for 256 entries behind the last image slot's base
+    const size_t reach = d.img_offset + (d.nslots - 1) * img_bytes + (img_bytes / p.C) * 256 + 1024;
+    if (pl.smem < reach) pl.smem = reach;
+  }
   if (pl.smem > 227 * 1024) return false;
 
   pl.ws_bytes = 0;

@@ -447,8 +447,8 @@ vq_small_ts_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallParams
               uint32_t c0;
               if constexpr (IB == 1) {
                 c0 = (w[e >> 2] >> (8 * (e & 3))) & 0xffu;
-              } else if constexpr (IB == 2) {
-                c0 = (w[e >> 1] >> (16 * (e & 1))) & 0xffffu;
+              } else if constexpr (IB == 2) {   // held below C: a larger index (malformed input) would address past the image
+                c0 = min((w[e >> 1] >> (16 * (e & 1))) & 0xffffu, static_cast<uint32_t>(p.C - 1));
               } else {                                    // index e sits at bit 12 e of the 96 bits
                 constexpr int kNoWord = WPS - 1;
                 const int word = (12 * e) >> 5, sh = (12 * e) & 31;
@@ -594,7 +594,9 @@ int launch_small_ts(const Problem& p, void* ws, size_t ws_bytes, cudaStream_t s)
   const size_t img = pl.repl ? static_cast<size_t>(p.C) * 128 : static_cast<size_t>(p.C) * entry;
   const bool dependent = !take_weights_written(s);   // not beside a kernel of this library that wrote the weights
   auto launch = [&](auto kernel, size_t x_bytes, int n_bars) -> int {
-    const size_t smem = x_bytes + ((img + 15) & ~static_cast<size_t>(15)) + (n_bars + 1) * 8 + 16 + 1024;
+    size_t smem = x_bytes + ((img + 15) & ~static_cast<size_t>(15)) + (n_bars + 1) * 8 + 16 + 1024;
+    // an 8-bit index beyond a small codebook (malformed input) must still address inside the block's shared memory
+    if (p.idx_bytes == 1 && p.C < 256 && smem < x_bytes + (img / p.C) * 256 + 1024) smem = x_bytes + (img / p.C) * 256 + 1024;
     if (smem > 227 * 1024) return VQG_ERR_UNSUPPORTED;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return VQG_ERR_LAUNCH;

@@ -30,7 +30,8 @@ each rank owns N/G output columns and the fp16 output is assembled on every rank
                fp32 and fp16 accumulation, in alternating blocks with this library's kernel.
 ``reference_cuda_kernels`` (N=1 only, when oracle/_ref holds them) the reference's own CUDA kernels rebuilt
                for sm_100a, on data in the reference's format, and this library on the same data.
-The line ends with the compact per-configuration table (``shapes``); long per-kernel detail is under ``detail``.
+The line ends with the compact records (``dequant``: the dequantisation kernels against the measured HBM bandwidth;
+``shapes``: the per-configuration table); long per-kernel detail is under ``detail``.
 
 ``--profile-case NAME --launches n [--path p]`` runs n launches of one configuration and exits: the command to
 put under a profiler (p: a product route, or ``dequant`` / ``dequant_ref`` / ``e2e_ref`` for the dequantisation kernels
@@ -1110,6 +1111,10 @@ def main():
             except Exception as e:
                 cub.append({"workload": name, "error": repr(e)})
         line["cublas"] = cub
+    if isinstance(detail.get("dequant"), list):
+        # compact copy for the tail of the line: the dequantisation kernels against the measured HBM bandwidth
+        line["dequant"] = [{"what": r["what"], "us": r["us"], "gbs": r["gbs"], "frac_of_hbm": r["frac_of_hbm"]}
+                           for r in detail["dequant"]]
     if shapes:
         line["shapes"] = shapes
     if rank == 0:
